@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the Cu32 dense-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input: by default the
+configuration the headline metric is quoted on, FP32-accurate matMul C = A*B at 8192^3
+(uniform[-1,1] inputs from a fixed seed).  With N GPUs every rank runs that same step on its
+own row block of an N-times-taller problem (rows of A and C sharded, B replicated): weak
+scaling, no data-path collective.  Rank 0 prints ONE JSON line.
+
+value      whole-job TFLOP/s (2*N*M*K per launch), inputs resident in HBM, timed with CUDA
+           events on the launching stream, max over ranks
+e2e        the same metric through the C-ABI call with HOST buffers: pinned host -> device
+           copies of A and B and the device -> host read of C are inside the timed region
+roofline   tensor bound: achieved FP32-accurate TFLOP/s against (measured bf16 peak / 2 for
+           TF32 / 3 products per term); `traffic` is the ncu DRAM-bytes figure recorded in
+           profiles/ for this kernel and workload (null until captured)
+cpu_baseline  the reference's CPU check loop timed on the host cores on a bounded row sample
+--impl reference   times that CPU loop alone (the reference has no other CPU implementation of
+           this path), all host threads, on the same configuration
+
+Other workloads (for profiling and the reports in profiles/): c1, c2_t1, c2_t2, c2_ragged,
+c3_qk, c3_pv, c4, c5.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "FP32-accurate matMul TFLOPS"
+UNIT = "TFLOP/s"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "basis": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "basis": "fallback"}
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU baseline (reference loops)
+def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, seconds_target: float = 12.0):
+    """Time the reference's CPU check loop (multiply*, Cuda_matMul/test.cuh:60-82) on a bounded
+    sample: every host thread runs the loop on its own block of `rows` output rows.  Returns
+    (TFLOP/s, cores, kind, sample description)."""
+    import numpy as np
+    from oracle import oracle as O
+    ref = O.ref_native("matmul")
+    kind = "reference" if ref is not None else "port"
+    cores = os.cpu_count() or 1
+    fp = ctypes.POINTER(ctypes.c_float)
+    names = {"AB": ("ref_cpu_multiply", "oracle_multiply"), "T1": ("ref_cpu_multiplyT1", "oracle_multiplyT1"),
+             "T2": ("ref_cpu_multiplyT2", "oracle_multiplyT2")}[form]
+    fn = getattr(ref, names[0]) if ref is not None else getattr(O.lib(), names[1])
+    # ~9 GFLOP/s per core for this loop order: size the row block for the target time
+    rows = int(max(4, min(N // cores, seconds_target * 9e9 / (2.0 * M * K))))
+    rows -= rows % 4
+    rows = max(rows, 4)
+    A = np.ascontiguousarray(A, dtype=np.float32)
+    B = np.ascontiguousarray(B, dtype=np.float32)
+    work = []
+    for t in range(cores):
+        r0 = (t * rows) % max(N - rows + 1, 1)
+        if form == "T1":   # A is [K, N]: a row block of C needs a column block of A
+            a = np.ascontiguousarray(A[:, r0:r0 + rows])
+        else:
+            a = np.ascontiguousarray(A[r0:r0 + rows])
+        c = np.zeros((rows, M), np.float32)
+        work.append((a, c))
+
+    def run(a, c):
+        fn(a.ctypes.data_as(fp), B.ctypes.data_as(fp), c.ctypes.data_as(fp), rows, M, K)
+    threads = [threading.Thread(target=run, args=w) for w in work]
+    t0 = time.perf_counter()
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    dt = time.perf_counter() - t0
+    flops = 2.0 * rows * M * K * cores
+    return flops / dt / 1e12, cores, kind, f"{cores} threads x {rows} output rows of the {N}x{M}x{K} problem ({dt:.1f} s)"
+
+
+# ------------------------------------------------------------------ workloads on the device
+class Workload:
+    """Builds device operands and returns `launch()` (enqueue one step on the current stream),
+    flops and algorithmic bytes per launch, plus host buffers for the end-to-end leg."""
+
+    def __init__(self, name, pkg, torch, rank):
+        self.name, self.pkg, self.torch = name, pkg, torch
+        W = pkg.workloads
+        mm, bm, cv = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_batchMatMul, pkg.cu32.Cuda_conv3D
+        st = lambda: [torch.cuda.current_stream().cuda_stream]
+        self.kernels_per_step = 1
+        self.cpu_case = None
+        if name in ("c1", "c2_ab", "c2_t1", "c2_t2", "c2_ragged", "c5"):
+            if name == "c1":
+                w = W.config1()
+            elif name == "c2_ragged":
+                w = W.config2_ragged("AB")
+            elif name == "c5":
+                w = W.config5(K=1048576 // 8)   # one GPU's K shard of the 8-GPU configuration
+            else:
+                w = W.config2({"c2_ab": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name])
+            self.hosts = [w.A.pin_memory(), w.B.pin_memory()]
+            self.dev_in = [torch.empty_like(h, device="cuda") for h in self.hosts]
+            for d, h in zip(self.dev_in, self.hosts):
+                d.copy_(h)
+            self.out = torch.empty((w.N, w.M), device="cuda")
+            fn = {"AB": mm.matMul, "T1": mm.matMulT1, "T2": mm.matMulT2}[w.form]
+            dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
+            if name == "c5":
+                gz = pkg.engine.matMulT1_gridZ(w.N, w.M, w.K, 148)
+                self.cbuf = torch.empty((gz - 1) * w.N * w.M, device="cuda")
+                self.kernels_per_step = 2
+
+                def launch():
+                    s = st()
+                    mm.matMulT1SK(s, 1, gz, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), self.cbuf.data_ptr(), w.N, w.M, w.K)
+                    mm.SKbuf_summary(s[0], self.cbuf.data_ptr(), dC.data_ptr(), gz - 1, w.N * w.M)
+                self.launch = launch
+            else:
+                self.launch = lambda: fn(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.N, w.M, w.K)
+            lg = getattr(w, "logical", (w.N, w.M, w.K))
+            self.flops = 2.0 * lg[0] * lg[1] * lg[2]
+            self.bytes = 4.0 * (lg[0] * lg[2] + lg[2] * lg[1] + lg[0] * lg[1])
+            self.desc = f"matMul {w.form} N={w.N} M={w.M} K={w.K}"
+            self.cpu_case = (w.form, w.N, w.M, w.K, w.A, w.B)
+            self.units = None
+        elif name in ("c3_qk", "c3_pv"):
+            w = W.config3()
+            if name == "c3_qk":
+                self.hosts = [w.Q.pin_memory(), w.K.pin_memory()]
+                self.dev_in = [h.cuda() for h in self.hosts]
+                self.out = torch.empty((w.Batch, w.L, w.L), device="cuda")
+                dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
+                self.launch = lambda: bm.batchMatMulT2(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.Batch, w.L, w.L, w.L, w.D)
+                self.desc = f"batchMatMulT2 Q*K^T Batch={w.Batch} {w.L}x{w.L}x{w.D}"
+            else:
+                g = torch.Generator().manual_seed(3003)
+                P = torch.softmax(torch.randn((w.Batch, w.L, w.L), generator=g), dim=-1)
+                self.hosts = [P.pin_memory(), w.V.pin_memory()]
+                self.dev_in = [h.cuda() for h in self.hosts]
+                self.out = torch.empty((w.Batch, w.L, w.D), device="cuda")
+                dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
+                self.launch = lambda: bm.batchMatMul(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.Batch, w.L, w.D, w.L, w.L)
+                self.desc = f"batchMatMul P*V Batch={w.Batch} {w.L}x{w.D}x{w.L}"
+            self.flops = w.flops_each
+            self.bytes = w.algorithmic_bytes_each
+        elif name == "c4":
+            w = W.config4()
+            d = w.dims
+            self.hosts = [w.X.pin_memory(), w.W.pin_memory()]
+            self.dev_in = [h.cuda() for h in self.hosts]
+            self.out = torch.empty((d["N"], d["OH"], d["OW"], d["OC"]), device="cuda")
+            self.cw = torch.empty(w.W.numel(), device="cuda")
+            dX, dW, dY = self.dev_in[0], self.dev_in[1], self.out
+            self.kernels_per_step = 2
+
+            def launch():
+                s = st()
+                cv.kernel_remode(s[0], dW.data_ptr(), self.cw.data_ptr(), d["FH"], d["FW"], d["OC"], d["IC"])
+                cv.conv3D_GemmR(s, 1, dX.data_ptr(), d["IH"], d["IW"], dW.data_ptr(), self.cw.data_ptr(), d["FH"], d["FW"],
+                                dY.data_ptr(), d["OH"], d["OW"], d["N"], d["IC"], d["OC"], w.sh, w.sw, w.ph, w.pw)
+            self.launch = launch
+            self.flops = w.flops
+            self.bytes = w.algorithmic_bytes
+            self.desc = f"conv3D_GemmR N={d['N']} {d['IH']}x{d['IW']}x{d['IC']} -> {d['OC']}, 3x3 s1 p1 (remode + GEMM)"
+            self.images = d["N"]
+        else:
+            raise SystemExit(f"unknown workload {name}")
+
+    def e2e_step(self):
+        """Host -> device copies of the inputs, the contraction, device -> host read of the result."""
+        for d, h in zip(self.dev_in, self.hosts):
+            d.copy_(h, non_blocking=True)
+        self.launch()
+        self.host_out.copy_(self.out, non_blocking=True)
+
+    def prepare_e2e(self):
+        self.host_out = self.torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        self.h2d = sum(h.numel() * 4 for h in self.hosts)
+        self.d2h = self.out.numel() * 4
+
+
+def time_steps(torch, dist, fn, steps, world):
+    """barrier + sync, `steps` launches bracketed by CUDA events on the current stream, sync +
+    barrier; returns the max over ranks of the elapsed milliseconds."""
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_ab")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+
+    if a.impl == "reference":
+        # The reference's own CPU implementation of this path: its check loops, all host threads.
+        if rank != 0:
+            return
+        w = pkg.workloads.config2("AB")
+        vals, cores, kind, sample = [], 1, "port", ""
+        for i in range(a.warmup + a.steps):
+            v, cores, kind, sample = cpu_reference_loop("AB", w.N, w.M, w.K, w.A.numpy(), w.B.numpy(), seconds_target=2.0)
+            if i >= a.warmup:
+                vals.append(v)
+        v = statistics.mean(vals)
+        flops = 2.0 * w.N * w.M * w.K
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": flops / (v * 1e12) * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "matMul AB N=8192 M=8192 K=8192 (config 2); each step times a bounded row sample, "
+                                   "ms_per_step extrapolates it to the full product"},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg.cu32.load()
+    pk = peaks()
+
+    wl = Workload(a.workload, pkg, torch, rank)
+    for _ in range(a.warmup):
+        wl.launch()
+    st = pkg.cu32.read_status()
+    if st != 0:
+        raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = time_steps(torch, dist, wl.launch, a.steps, world)
+    clocks = sampler.stop() if sampler else None
+    st = pkg.cu32.read_status()
+    if st != 0:
+        raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
+    ms_step = ms / a.steps
+    value = wl.flops * world / (ms_step * 1e-3) / 1e12
+
+    e2e = None
+    if not a.no_e2e:
+        wl.prepare_e2e()
+        for _ in range(2):
+            wl.e2e_step()
+        e2e_steps = max(3, min(a.steps, 10))
+        ms_e = time_steps(torch, dist, wl.e2e_step, e2e_steps, world) / e2e_steps
+        e2e = {"value": wl.flops * world / (ms_e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e,
+               "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    per_gpu = wl.flops / (ms_step * 1e-3) / 1e12
+    sustained = a.steps * ms_step > 1500.0
+    bf16 = pk["bf16_sustained"] if sustained else pk["bf16"]
+    ceiling = bf16 / 2.0 / 3.0
+    bound = "hbm" if a.workload.startswith("c3") else "tensor"
+    if bound == "tensor":
+        roof = {"bound": "tensor", "achieved": per_gpu, "peak": ceiling, "unit": "TFLOP/s", "frac": per_gpu / ceiling,
+                "traffic": None,
+                "peak_basis": f"{pk['basis']} bf16 {'sustained' if sustained else 'burst'} {bf16} TFLOP/s / 2 (TF32 rate) / 3 (hi*hi + hi*lo + lo*hi)"}
+    else:
+        gbs = wl.bytes / (ms_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                "traffic": None, "peak_basis": f"{pk['basis']} copy bandwidth"}
+
+    cpu = None
+    if world == 1 and not a.no_cpu_baseline and wl.cpu_case is not None:
+        form, N, M, K, A, B = wl.cpu_case
+        v, cores, kind, sample = cpu_reference_loop(form, N, M, K, A.numpy(), B.numpy())
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3",
+        "data": "synthetic",
+        "config": {"workload": wl.desc + (f"; {world} ranks, one row block each" if world > 1 else ""),
+                   "l2": "operands larger than L2 (no flush needed)" if wl.bytes > 126e6 else "L2 not flushed: operands fit in L2",
+                   "kc": pkg.cu32.get_tune("kc"), "tile": pkg.cu32.get_tune("tile")},
+        "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": a.steps * wl.kernels_per_step,
+        "clocks": clocks,
+    }
+    if hasattr(wl, "images"):
+        line["images_per_s"] = wl.images * world / (ms_step * 1e-3)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

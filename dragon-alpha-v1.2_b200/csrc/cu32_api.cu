@@ -1,0 +1,573 @@
+// C-ABI layer of libdragon_cu32.so: argument checking, mapping of the reference's
+// (N, M, K, pitch) conventions onto the contraction kernel, tensor-map encoding, and
+// the two bandwidth kernels of the path (split-K buffer summation, filter remode).
+//
+// Nothing here allocates device memory or keeps state between calls apart from
+// process-wide tuning integers; tensor maps are encoded on the host per call and
+// travel to the kernel as launch parameters.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/dragon_cu32.h"
+#include "gemm_launch.h"
+
+namespace dragon {
+
+// ------------------------------------------------------------------ tuning knobs
+static std::atomic<int> g_kc{1};
+static std::atomic<int> g_kc_fast{4};
+static std::atomic<int> g_tile{-1};
+
+static void load_env_once() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (const char* s = std::getenv("DRAGON_CU32_KC")) { int v = std::atoi(s); if (v >= 1) g_kc = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_KC_FAST")) { int v = std::atoi(s); if (v >= 1) g_kc_fast = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_TILE")) { int v = std::atoi(s); if (v >= -1 && v < TILE_COUNT) g_tile = v; }
+  });
+}
+
+// ------------------------------------------------------------------ device status word
+__device__ int g_status_word;
+
+static int* status_word_ptr(cudaError_t* err) {
+  // The symbol has one instance per device; cache its address per device ordinal.
+  static std::atomic<int*> cache[64];
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  int* p = cache[dev & 63].load(std::memory_order_acquire);
+  if (p) return p;
+  void* sym = nullptr;
+  *err = cudaGetSymbolAddress(&sym, g_status_word);
+  if (*err != cudaSuccess) return nullptr;
+  cache[dev & 63].store(static_cast<int*>(sym), std::memory_order_release);
+  return static_cast<int*>(sym);
+}
+
+// ------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
+static EncodeIm2colFn g_encode_im2col = nullptr;
+
+static bool load_driver_entry_points() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  });
+  return g_encode_tiled != nullptr;
+}
+
+// 3-D FP32 map (inner, outer, batch), 128-byte swizzle, zero fill outside the extents.
+static int make_map3(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                     uint64_t pitch1_floats, uint64_t pitch2_floats, uint32_t b0, uint32_t b1) {
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {pitch1_floats * 4, pitch2_floats * 4};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
+                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? CU32_OK : CU32_E_TENSORMAP;
+}
+
+// One contraction, BLAS letters: C[M,N] = A * B over K.
+struct GemmCall {
+  const float* A; const float* B; float* C; float* Cbuf;
+  int M, N, K;              // logical extents of the operands
+  int n_store;              // columns of C written (>= N; columns N.. come out 0)
+  long long lda, ldb, ldc;  // row pitches in floats
+  bool a_mn, b_mn;          // operand stored with its M / N axis contiguous
+  int batch; long long sA, sB, sC;
+  int gz;                   // split-K slices (1 = none)
+  bool x3;                  // FP32-accurate (true) or single-pass TF32
+  cudaStream_t stream;
+};
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int pick_tile(int M, int N) {
+  const int forced = g_tile.load();
+  if (forced >= 0) return forced;
+  (void)M;
+  if (N <= 64) return TILE_1x64;
+  return TILE_1x128;
+}
+
+static int run_gemm(const GemmCall& c) {
+  load_env_once();
+  if (!c.A || !c.B || !c.C) return CU32_E_NULL;
+  if (c.gz > 1 && !c.Cbuf) return CU32_E_NULL;
+  if (c.M <= 0 || c.N <= 0 || c.K <= 0 || c.batch <= 0 || c.gz < 1 || c.gz > 65535) return CU32_E_DIM;
+  if ((c.lda & 3) || (c.ldb & 3) || (c.sA & 3) || (c.sB & 3) || !aligned16(c.A) || !aligned16(c.B))
+    return CU32_E_ALIGN;
+  if (!load_driver_entry_points()) return CU32_E_DRIVER;
+
+  const int tile = pick_tile(c.M, c.n_store);
+  const int ctas = tile_ctas(tile), bn = tile_bn(tile);
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc;
+  const uint64_t nb = static_cast<uint64_t>(c.batch);
+  // A
+  if (c.a_mn) rc = make_map3(&p.tmA, c.A, c.M, c.K, nb, c.lda, c.sA ? c.sA : c.lda * c.K, 32, 32);
+  else        rc = make_map3(&p.tmA, c.A, c.K, c.M, nb, c.lda, c.sA ? c.sA : c.lda * c.M, 32, 128);
+  if (rc) return rc;
+  // B
+  if (c.b_mn) rc = make_map3(&p.tmB, c.B, c.N, c.K, nb, c.ldb, c.sB ? c.sB : c.ldb * c.K, 32, 32);
+  else        rc = make_map3(&p.tmB, c.B, c.K, c.N, nb, c.ldb, c.sB ? c.sB : c.ldb * c.N, 32, bn / ctas);
+  if (rc) return rc;
+
+  p.C = c.C;
+  p.Cbuf = c.Cbuf;
+  p.ldc = c.ldc;
+  p.c_stride = c.sC;
+  p.M = c.M;
+  p.N = c.n_store;
+  p.nkb_total = (c.K + 31) / 32;
+  p.tiles_m = (c.M + 128 * ctas - 1) / (128 * ctas);
+  p.tiles_n = (c.n_store + bn - 1) / bn;
+  p.gz = c.gz;
+  p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
+  p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
+  cudaError_t e;
+  p.status = status_word_ptr(&e);
+  if (!p.status) return static_cast<int>(e);
+
+  // blockIdx.z carries the batch index or the split-K slice; at most 65535 per launch.
+  const int zs = c.gz > 1 ? c.gz : c.batch;
+  for (int z0 = 0; z0 < zs; z0 += 65535) {
+    const int nz = zs - z0 < 65535 ? zs - z0 : 65535;
+    GemmParams q = p;
+    if (z0 > 0) {  // only reachable for batch > 65535: re-encode the maps at the batch offset
+      const float* A2 = c.A + static_cast<long long>(z0) * c.sA;
+      const float* B2 = c.B + static_cast<long long>(z0) * c.sB;
+      if (c.a_mn) rc = make_map3(&q.tmA, A2, c.M, c.K, nz, c.lda, c.sA, 32, 32);
+      else        rc = make_map3(&q.tmA, A2, c.K, c.M, nz, c.lda, c.sA, 32, 128);
+      if (rc) return rc;
+      if (c.b_mn) rc = make_map3(&q.tmB, B2, c.N, c.K, nz, c.ldb, c.sB, 32, 32);
+      else        rc = make_map3(&q.tmB, B2, c.K, c.N, nz, c.ldb, c.sB, 32, bn / ctas);
+      if (rc) return rc;
+      q.C = c.C + static_cast<long long>(z0) * c.sC;
+    }
+    if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, q, nz, c.stream);
+    else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, q, nz, c.stream);
+    else if (!c.a_mn)           e = launch_gemm_kk(tile, c.x3, false, q, nz, c.stream);
+    else return CU32_E_ARG;
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  e = cudaPeekAtLastError();
+  return static_cast<int>(e);
+}
+
+static int check_streams(const int64_t* streams, int length, cudaStream_t* s0) {
+  if (!streams || length < 1 || length > 10) return CU32_E_STREAMS;
+  *s0 = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(streams[0]));
+  return CU32_OK;
+}
+
+// ------------------------------------------------------------------ matMul family
+enum MatForm { FORM_AB, FORM_T1, FORM_T2 };
+
+static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length, int GridZ,
+                      const float* dA, const float* dB, float* dC, float* dCbuf, int N, int M, int K) {
+  cudaStream_t st;
+  if (int rc = check_streams(streams, length, &st)) return rc;
+  if (N <= 0 || M <= 0 || K <= 0) return CU32_E_DIM;
+  if (GridZ < 1) return CU32_E_ARG;
+  GemmCall c{};
+  c.A = dA; c.B = dB; c.C = dC; c.Cbuf = dCbuf;
+  c.M = N; c.N = M; c.K = K; c.n_store = M;
+  c.ldc = M;
+  c.batch = 1; c.sA = 0; c.sB = 0;
+  c.sC = static_cast<long long>(N) * M;  // distance between split-K partial buffers
+  c.gz = GridZ; c.x3 = x3; c.stream = st;
+  switch (form) {
+    case FORM_AB: c.a_mn = false; c.lda = K; c.b_mn = true;  c.ldb = M; break;
+    case FORM_T1: c.a_mn = true;  c.lda = N; c.b_mn = true;  c.ldb = M; break;
+    case FORM_T2: c.a_mn = false; c.lda = K; c.b_mn = false; c.ldb = K; break;
+  }
+  return run_gemm(c);
+}
+
+// ------------------------------------------------------------------ split-K buffer summation
+// C += sum_p Cbuf[p], Kahan-compensated, 4 floats per thread per step.
+__global__ void skbuf_summary_kernel(const float* __restrict__ Cbuf, float* __restrict__ C, int part,
+                                     long long sizeC) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < sizeC;
+       i += stride) {
+    if (i + 3 < sizeC) {
+      float4 sum = *reinterpret_cast<const float4*>(C + i);
+      float4 comp = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < part; ++p) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(Cbuf + static_cast<long long>(p) * sizeC + i));
+        float y, t;
+        y = v.x - comp.x; t = sum.x + y; comp.x = (t - sum.x) - y; sum.x = t;
+        y = v.y - comp.y; t = sum.y + y; comp.y = (t - sum.y) - y; sum.y = t;
+        y = v.z - comp.z; t = sum.z + y; comp.z = (t - sum.z) - y; sum.z = t;
+        y = v.w - comp.w; t = sum.w + y; comp.w = (t - sum.w) - y; sum.w = t;
+      }
+      *reinterpret_cast<float4*>(C + i) = sum;
+    } else {
+      for (long long j = i; j < sizeC; ++j) {
+        float sum = C[j], comp = 0.f;
+        for (int p = 0; p < part; ++p) {
+          const float y = Cbuf[static_cast<long long>(p) * sizeC + j] - comp;
+          const float t = sum + y;
+          comp = (t - sum) - y;
+          sum = t;
+        }
+        C[j] = sum;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ filter remode
+// CW[g][oc] = W[oc][g], g = (fh, fw, ic) flattened: a [OC x G] -> [G x OC] transpose
+// through a padded 32x32 shared-memory tile (coalesced on both sides).
+__global__ void remode_kernel(const float* __restrict__ W, float* __restrict__ CW, int OC, int G) {
+  __shared__ float tile[32][33];
+  const int g0 = blockIdx.x * 32, oc0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int oc = oc0 + r, g = g0 + threadIdx.x;
+    tile[r][threadIdx.x] = (oc < OC && g < G) ? W[static_cast<long long>(oc) * G + g] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int g = g0 + r, oc = oc0 + threadIdx.x;
+    if (g < G && oc < OC) CW[static_cast<long long>(g) * OC + oc] = tile[threadIdx.x][r];
+  }
+}
+
+// ------------------------------------------------------------------ convolution
+static int conv_any(bool x3, const int64_t* streams, int length, const float* dX, int IH, int IW,
+                    const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
+                    int sh, int sw, int ph, int pw) {
+  load_env_once();
+  cudaStream_t st;
+  if (int rc = check_streams(streams, length, &st)) return rc;
+  if (!dX || !dW || !dY) return CU32_E_NULL;
+  if (IH <= 0 || IW <= 0 || FH <= 0 || FW <= 0 || OH <= 0 || OW <= 0 || N <= 0 || IC <= 0 || OC <= 0 ||
+      sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+    return CU32_E_DIM;
+  if ((IC & 3) || !aligned16(dX) || !aligned16(dW)) return CU32_E_ALIGN;
+  const long long GM = static_cast<long long>(N) * OH * OW;
+  const long long GK = static_cast<long long>(FH) * FW * IC;
+  if (GM >= (1LL << 31) || GK >= (1LL << 31) || static_cast<long long>(N) * IH * IW * IC >= (1LL << 31))
+    return CU32_E_DIM;
+  if (!load_driver_entry_points()) return CU32_E_DRIVER;
+
+  // 1x1 / stride 1 / no padding with matching extents is a plain contraction Y[GM,OC] = X[GM,IC] * W[OC,IC]^T.
+  if (FH == 1 && FW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && OH == IH && OW == IW) {
+    GemmCall c{};
+    c.A = dX; c.B = dW; c.C = dY; c.Cbuf = nullptr;
+    c.M = static_cast<int>(GM); c.N = OC; c.K = IC; c.n_store = OC;
+    c.lda = IC; c.ldb = IC; c.ldc = OC; c.a_mn = false; c.b_mn = false;
+    c.batch = 1; c.sA = 0; c.sB = 0; c.sC = 0; c.gz = 1; c.x3 = x3; c.stream = st;
+    return run_gemm(c);
+  }
+
+  if (!g_encode_im2col) return CU32_E_DRIVER;
+  // The im2col tensor map walks "base pixels" (the top-left input pixel of each output
+  // position) inside the box [lower, extent - 1 + upper] with the convolution stride;
+  // the filter tap is added per load as an offset.  Corners must fit 8 signed bits and
+  // offsets 8 unsigned bits for two spatial dimensions.
+  const int lower_w = -pw, lower_h = -ph;
+  const int upper_w = lower_w + (OW - 1) * sw - (IW - 1);
+  const int upper_h = lower_h + (OH - 1) * sh - (IH - 1);
+  if (lower_w < -128 || lower_h < -128 || upper_w < -128 || upper_w > 127 || upper_h < -128 ||
+      upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8)
+    return CU32_E_GEOMETRY;
+
+  const int tile = pick_tile(static_cast<int>(GM), OC);
+  const int ctas = tile_ctas(tile), bn = tile_bn(tile);
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  {
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(IC), static_cast<cuuint64_t>(IW),
+                          static_cast<cuuint64_t>(IH), static_cast<cuuint64_t>(N)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(IC) * 4, static_cast<cuuint64_t>(IW) * IC * 4,
+                             static_cast<cuuint64_t>(IH) * IW * IC * 4};
+    int lower[2] = {lower_w, lower_h};
+    int upper[2] = {upper_w, upper_h};
+    cuuint32_t trav[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
+    CUresult r = g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dX), dims,
+                                 strides, lower, upper, /*channelsPerPixel=*/32, /*pixelsPerColumn=*/128,
+                                 trav, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+    // Drivers up to CUDA 13.1 set a descriptor flag that mis-handles im2col maps over
+    // tensors smaller than 128 KiB; NVIDIA's CUTLASS clears bit 21 of the second 64-bit
+    // word in that case (cute/atom/copy_traits_sm90_im2col.hpp), and so does this.
+    int drv = 0;
+    if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
+        static_cast<long long>(N) * IH * IW * IC * 4 < 131072)
+      reinterpret_cast<uint64_t*>(&p.tmA)[1] &= ~(1ULL << 21);
+  }
+  // Filters W[OC][FH*FW*IC]: reduction axis contiguous.
+  if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas)) return rc;
+
+  p.C = dY; p.Cbuf = nullptr; p.ldc = OC; p.c_stride = 0;
+  p.M = static_cast<int>(GM); p.N = OC;
+  p.conv_icb = (IC + 31) / 32;
+  p.nkb_total = FH * FW * p.conv_icb;
+  p.tiles_m = static_cast<int>((GM + 128 * ctas - 1) / (128 * ctas));
+  p.tiles_n = (OC + bn - 1) / bn;
+  p.gz = 1;
+  p.kc = x3 ? g_kc.load() : g_kc_fast.load();
+  p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
+  p.conv_OW = OW; p.conv_OH = OH; p.conv_FW = FW; p.conv_IC = IC;
+  p.conv_sw = sw; p.conv_sh = sh; p.conv_pw = pw; p.conv_ph = ph;
+  cudaError_t e;
+  p.status = status_word_ptr(&e);
+  if (!p.status) return static_cast<int>(e);
+  e = launch_gemm_kk(tile, x3, true, p, 1, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+}  // namespace dragon
+
+using namespace dragon;
+
+// ==================================================================== exported C ABI
+extern "C" {
+
+int cu32_matMul(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_AB, true, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+int cu32_matMulT1(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_T1, true, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+int cu32_matMulT2(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_T2, true, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+int cu32_matMulSK(const int64_t* s, int n, int GZ, const float* A, const float* B, float* C, float* Cbuf,
+                  int N, int M, int K) {
+  return matmul_any(FORM_AB, true, s, n, GZ, A, B, C, Cbuf, N, M, K);
+}
+int cu32_matMulT1SK(const int64_t* s, int n, int GZ, const float* A, const float* B, float* C,
+                    float* Cbuf, int N, int M, int K) {
+  return matmul_any(FORM_T1, true, s, n, GZ, A, B, C, Cbuf, N, M, K);
+}
+int cu32_matMulT2SK(const int64_t* s, int n, int GZ, const float* A, const float* B, float* C,
+                    float* Cbuf, int N, int M, int K) {
+  return matmul_any(FORM_T2, true, s, n, GZ, A, B, C, Cbuf, N, M, K);
+}
+int cu32_matMul_mma(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_AB, false, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+int cu32_matMulT1_mma(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_T1, false, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+int cu32_matMulT2_mma(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
+  return matmul_any(FORM_T2, false, s, n, 1, A, B, C, nullptr, N, M, K);
+}
+
+int cu32_SKbuf_summary(int64_t stream, const float* dCbuf, float* dC, int part, int sizeC) {
+  if (!dC || (part > 0 && !dCbuf)) return CU32_E_NULL;
+  if (part < 0 || sizeC <= 0) return CU32_E_DIM;
+  if (!aligned16(dC) || !aligned16(dCbuf) || (sizeC & 3)) return CU32_E_ALIGN;
+  if (part == 0) return CU32_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
+  const int threads = 256;
+  long long blocks = (static_cast<long long>(sizeC) / 4 + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  skbuf_summary_kernel<<<static_cast<unsigned>(blocks), threads, 0, st>>>(dCbuf, dC, part, sizeC);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+// ---- batched
+static int bmm_any(int form, bool x3, const int64_t* s, int n, const float* A, const float* B, float* C,
+                   int Batch, int d0, int d1, int d2, int d3) {
+  cudaStream_t st;
+  if (int rc = check_streams(s, n, &st)) return rc;
+  if (Batch <= 0 || d0 <= 0 || d1 <= 0 || d2 <= 0 || d3 <= 0) return CU32_E_DIM;
+  GemmCall c{};
+  c.A = A; c.B = B; c.C = C; c.Cbuf = nullptr;
+  c.batch = Batch; c.gz = 1; c.x3 = x3; c.stream = st;
+  if (form == FORM_AB) {            // (Batch, N, M, BK, AK)
+    const int N = d0, M = d1, BK = d2, AK = d3;
+    if (AK < BK) return CU32_E_DIM;
+    c.M = N; c.N = M; c.K = BK; c.n_store = M;
+    c.a_mn = false; c.lda = AK; c.sA = static_cast<long long>(N) * AK;
+    c.b_mn = true;  c.ldb = M;  c.sB = static_cast<long long>(BK) * M;
+    c.ldc = M; c.sC = static_cast<long long>(N) * M;
+  } else if (form == FORM_T1) {     // (Batch, CN, AN, M, K)
+    const int CN = d0, AN = d1, M = d2, K = d3;
+    if (AN < CN) return CU32_E_DIM;
+    c.M = CN; c.N = M; c.K = K; c.n_store = M;
+    c.a_mn = true; c.lda = AN; c.sA = static_cast<long long>(K) * AN;
+    c.b_mn = true; c.ldb = M;  c.sB = static_cast<long long>(K) * M;
+    c.ldc = M; c.sC = static_cast<long long>(CN) * M;
+  } else {                          // (Batch, N, CM, BM, K)
+    const int N = d0, CM = d1, BM = d2, K = d3;
+    if (CM < BM) return CU32_E_DIM;
+    c.M = N; c.N = BM; c.K = K; c.n_store = CM;
+    c.a_mn = false; c.lda = K; c.sA = static_cast<long long>(N) * K;
+    c.b_mn = false; c.ldb = K; c.sB = static_cast<long long>(BM) * K;
+    c.ldc = CM; c.sC = static_cast<long long>(N) * CM;
+  }
+  return run_gemm(c);
+}
+
+int cu32_batchMatMul(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int N,
+                     int M, int BK, int AK) {
+  return bmm_any(FORM_AB, true, s, n, A, B, C, Batch, N, M, BK, AK);
+}
+int cu32_batchMatMul_texture(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch,
+                             int N, int M, int BK, int AK) {
+  return bmm_any(FORM_AB, true, s, n, A, B, C, Batch, N, M, BK, AK);
+}
+int cu32_batchMatMulT1(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int CN,
+                       int AN, int M, int K) {
+  return bmm_any(FORM_T1, true, s, n, A, B, C, Batch, CN, AN, M, K);
+}
+int cu32_batchMatMulT2(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int N,
+                       int CM, int BM, int K) {
+  return bmm_any(FORM_T2, true, s, n, A, B, C, Batch, N, CM, BM, K);
+}
+int cu32_batchMatMulT2_texture(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch,
+                               int N, int CM, int BM, int K) {
+  return bmm_any(FORM_T2, true, s, n, A, B, C, Batch, N, CM, BM, K);
+}
+int cu32_batchMatMul_mma(int useTexture, const int64_t* s, int n, const float* A, const float* B, float* C,
+                         int Batch, int N, int M, int BK, int AK) {
+  (void)useTexture;
+  return bmm_any(FORM_AB, false, s, n, A, B, C, Batch, N, M, BK, AK);
+}
+int cu32_batchMatMulT1_mma(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch,
+                           int CN, int AN, int M, int K) {
+  return bmm_any(FORM_T1, false, s, n, A, B, C, Batch, CN, AN, M, K);
+}
+int cu32_batchMatMulT2_mma(int useTexture, const int64_t* s, int n, const float* A, const float* B, float* C,
+                           int Batch, int N, int CM, int BM, int K) {
+  (void)useTexture;
+  return bmm_any(FORM_T2, false, s, n, A, B, C, Batch, N, CM, BM, K);
+}
+
+// ---- convolution
+int cu32_kernel_remode(int64_t stream, const float* dW, float* dCW, int FH, int FW, int OC, int IC) {
+  if (!dW || !dCW) return CU32_E_NULL;
+  if (FH <= 0 || FW <= 0 || OC <= 0 || IC <= 0) return CU32_E_DIM;
+  const long long G = static_cast<long long>(FH) * FW * IC;
+  if (G >= (1LL << 31) || G * OC >= (1LL << 31)) return CU32_E_DIM;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
+  dim3 grid(static_cast<unsigned>((G + 31) / 32), static_cast<unsigned>((OC + 31) / 32));
+  if (grid.y > 65535) return CU32_E_DIM;
+  remode_kernel<<<grid, dim3(32, 8), 0, st>>>(dW, dCW, OC, static_cast<int>(G));
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+int cu32_conv3D_GemmR(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                      const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC,
+                      int sh, int sw, int ph, int pw) {
+  (void)CW;  // the tensor-map path reads W[OC][FH*FW*IC] directly; CW is the reference's operand layout
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmR_texture(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                              const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC,
+                              int OC, int sh, int sw, int ph, int pw) {
+  (void)CW;
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmR_SGM(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                          const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC,
+                          int sh, int sw, int ph, int pw, int GM_slice) {
+  (void)CW;
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmR_texture_SGM(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                                  const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC,
+                                  int OC, int sh, int sw, int ph, int pw, int GM_slice) {
+  (void)CW;
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmR_W1(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                         const float* CW, float* Y, int N, int IC, int OC) {
+  (void)CW;
+  return conv_any(true, s, n, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
+}
+int cu32_conv3D_GemmR_W1_SGM(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                             const float* CW, float* Y, int N, int IC, int OC, int GM_slice) {
+  (void)CW;
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return conv_any(true, s, n, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
+}
+int cu32_conv3D(const int64_t* s, int n, const float* X, int IH, int IW, const float* W, int FH, int FW,
+                float* Y, int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_texture(const int64_t* s, int n, const float* X, int IH, int IW, const float* W, int FH,
+                        int FW, float* Y, int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph,
+                        int pw) {
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_np(const int64_t* s, int n, const float* X, int IH, int IW, const float* W, int FH, int FW,
+                   float* Y, int OH, int OW, int N, int IC, int OC, int sh, int sw) {
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, 0, 0);
+}
+int cu32_conv3D_W1(const int64_t* s, int n, const float* X, int IH, int IW, const float* W, float* Y, int N,
+                   int IC, int OC) {
+  return conv_any(true, s, n, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
+}
+
+// ---- library control
+int cu32_tune(const char* key, int value) {
+  load_env_once();
+  if (!key) return CU32_E_ARG;
+  if (!std::strcmp(key, "kc")) { if (value < 1) return CU32_E_ARG; g_kc = value; return CU32_OK; }
+  if (!std::strcmp(key, "kc_fast")) { if (value < 1) return CU32_E_ARG; g_kc_fast = value; return CU32_OK; }
+  if (!std::strcmp(key, "tile")) { if (value < -1 || value >= TILE_COUNT) return CU32_E_ARG; g_tile = value; return CU32_OK; }
+  return CU32_E_ARG;
+}
+int cu32_get_tune(const char* key, int* value) {
+  load_env_once();
+  if (!key || !value) return CU32_E_ARG;
+  if (!std::strcmp(key, "kc")) { *value = g_kc; return CU32_OK; }
+  if (!std::strcmp(key, "kc_fast")) { *value = g_kc_fast; return CU32_OK; }
+  if (!std::strcmp(key, "tile")) { *value = g_tile; return CU32_OK; }
+  return CU32_E_ARG;
+}
+int cu32_read_status(int* status) {
+  if (!status) return CU32_E_NULL;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpyFromSymbol(status, g_status_word, sizeof(int));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int zero = 0;
+  e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
+  return static_cast<int>(e);
+}
+const char* cu32_version(void) { return "dragon_cu32 0.1 sm_100a"; }
+
+}  // extern "C"

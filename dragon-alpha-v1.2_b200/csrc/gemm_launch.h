@@ -1,0 +1,86 @@
+// Host-side launch interface between the C-ABI layer and the kernel
+// instantiations (one translation unit per operand-layout pair, so they build
+// in parallel).
+#pragma once
+#include <cuda_runtime.h>
+#include "gemm_tf32.cuh"
+
+namespace dragon {
+
+// Tile configurations: CTAs per tile x columns per tile.  A tile has 128 rows per CTA.
+enum TileCfg : int {
+  TILE_1x64 = 0,   // 128 x 64, one CTA   (narrow outputs)
+  TILE_1x128 = 1,  // 128 x 128, one CTA
+  TILE_1x256 = 2,  // 128 x 256, one CTA
+  TILE_2x128 = 3,  // 256 x 128, CTA pair
+  TILE_2x256 = 4,  // 256 x 256, CTA pair
+  TILE_COUNT = 5
+};
+
+inline int tile_ctas(int cfg) { return cfg >= TILE_2x128 ? 2 : 1; }
+inline int tile_bn(int cfg) {
+  switch (cfg) {
+    case TILE_1x64: return 64;
+    case TILE_1x128: case TILE_2x128: return 128;
+    default: return 256;
+  }
+}
+
+// Operand layouts.  "K" = the reduction axis is contiguous in memory, "N" = the
+// row/column (M or N) axis is contiguous.
+//   KK : A[M][K], B[N][K]   (matMulT2, batchMatMulT2, convolution with OCxFHxFWxIC filters)
+//   KN : A[M][K], B[K][N]   (matMul, batchMatMul)
+//   NN : A[K][M], B[K][N]   (matMulT1, batchMatMulT1)
+cudaError_t launch_gemm_kk(int tile_cfg, bool x3, bool im2col, const GemmParams& p, int grid_z,
+                           cudaStream_t stream);
+cudaError_t launch_gemm_kn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
+cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
+
+// Shared-memory bytes one stage of the given configuration uses (for reporting).
+int gemm_stage_bytes(int tile_cfg, bool x3);
+int gemm_stages(int tile_cfg, bool x3);
+
+template <class Cfg>
+cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
+  auto kernel = gemm_tf32_kernel<Cfg>;
+  // Opt in to the large dynamic shared-memory carve-out once per device.
+  static unsigned long long configured_devices = 0ULL;  // bit per device ordinal
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = 1ULL << (dev & 63);
+  if (!(__atomic_load_n(&configured_devices, __ATOMIC_ACQUIRE) & bit)) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM);
+    if (e != cudaSuccess) return e;
+    __atomic_fetch_or(&configured_devices, bit, __ATOMIC_RELEASE);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.tiles_m) * p.tiles_n * Cfg::CTAS, 1, grid_z);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  cfg.numAttrs = 0;
+  if (Cfg::CTAS == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+// Expands to the switch over tile configurations for one layout pair.
+#define DRAGON_DISPATCH_TILES(A_MN, B_MN, X3, IM2COL)                                          \
+  switch (tile_cfg) {                                                                          \
+    case TILE_1x64:  return launch_one<GemmCfg<64, 1, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream);  \
+    case TILE_1x128: return launch_one<GemmCfg<128, 1, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
+    case TILE_1x256: return launch_one<GemmCfg<256, 1, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
+    case TILE_2x128: return launch_one<GemmCfg<128, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
+    case TILE_2x256: return launch_one<GemmCfg<256, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
+    default: return cudaErrorInvalidValue;                                                     \
+  }
+
+}  // namespace dragon

@@ -1,0 +1,416 @@
+// FP32-accurate dense contraction on Blackwell tensor cores.
+//
+//   C[M,N] = A[M,K] * B[K,N]      (FP32 in, FP32 out, BLAS letters)
+//
+// One kernel template covers every entry point of the Cu32 matMul / batchMatMul /
+// implicit-GEMM convolution family: the operand "major-ness" (which axis is
+// contiguous in memory) is a template flag per operand, the batch index or the
+// split-K slice rides on blockIdx.z, and the A operand can be gathered from an
+// NHWC feature map by an im2col-mode tensor map.
+//
+// Arithmetic.  Each FP32 input x is split in shared memory into
+//     hi = tf32_round(x)          lo = tf32_round(x - hi)
+// and the product is formed as  lo*hi + hi*lo + hi*hi  on tcgen05.mma kind::tf32
+// (the lo*lo term, below 2^-22 relative, is dropped).  The tensor core
+// accumulates in FP32 inside TMEM for `kc` k-blocks (one "chunk"); drain warps
+// then add the chunk to FP32 register accumulators with round-to-nearest adds,
+// so the length of any in-TMEM accumulation chain is bounded regardless of K.
+//
+// Roles inside a CTA of 16 warps:
+//   warp 0        TMA producer      global -> shared (raw FP32 tiles, 128B swizzle)
+//   warp 1        MMA issuer        one thread issues tcgen05.mma, commits to mbarriers
+//   warps 2..7    splitters         shared -> shared: raw -> (hi in place, lo beside it)
+//   warps 8..15   drainers          TMEM -> registers (sum of chunks) -> global
+// With CTAS == 2 two CTAs of a cluster form one 256-row tile: each loads and
+// splits its own half of A and of B, the even CTA issues cta_group::2 MMAs, and
+// each CTA drains its own 128 TMEM lanes.
+//
+// Every mbarrier wait is bounded (see sm100_ptx.cuh).  A role that gives up
+// records (role, stage, iteration) in the status word, raises the CTA's abort
+// flag, and all roles fall through to the common exit, which frees TMEM.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace dragon {
+
+struct GemmParams {
+  CUtensorMap tmA;      // K-major A: dims (K, M, batch), box (32, 128, 1)
+                        // MN-major A: dims (M, K, batch), box (32, 32, 1)
+                        // im2col A: NHWC dims (C, W, H, N), 32 channels x 128 pixels
+  CUtensorMap tmB;      // K-major B: dims (K, N, batch), box (32, BN/CTAS, 1)
+                        // MN-major B: dims (N, K, batch), box (32, 32, 1)
+  float* C;             // output of batch 0 / split-K slice 0
+  float* Cbuf;          // split-K: outputs of slices 1..gz-1, c_stride floats apart
+  long long ldc;        // row pitch of C in floats
+  long long c_stride;   // floats between consecutive batches (or Cbuf slices)
+  int M, N;             // rows / columns of C to store
+  int nkb_total;        // k-blocks of 32 in the whole reduction (before split-K)
+  int tiles_m, tiles_n; // tile grid; a tile is (128*CTAS) x BN
+  int gz;               // > 1: blockIdx.z is a split-K slice; else a batch index
+  int kc;               // k-blocks accumulated in TMEM before a drain (>= 1)
+  int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
+  int* status;          // device word, 0 = ok; first give-up code otherwise
+  // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
+  // The reduction index runs over (fh, fw, ic) with every filter tap padded to
+  // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
+  int conv_OW, conv_OH, conv_FW, conv_IC, conv_icb, conv_sw, conv_sh, conv_pw, conv_ph;
+};
+
+enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5 };
+
+template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false>
+struct GemmCfg {
+  static constexpr int BN = BN_, CTAS = CTAS_;
+  static constexpr bool A_MN = A_MN_, B_MN = B_MN_, X3 = X3_, IM2COL = IM2COL_;
+  static constexpr int BM = 128;            // rows of A (and TMEM lanes) per CTA
+  static constexpr int BK = 32;             // one 128-byte swizzle row of FP32
+  static constexpr int BN_CTA = BN / CTAS;  // B columns staged per CTA
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN_CTA * BK * 4;
+  static constexpr int HI_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = HI_BYTES * (X3 ? 2 : 1);
+  static constexpr int SMEM_BUDGET = 220 * 1024;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two chunk buffers
+  static constexpr int THREADS = 512;
+  static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;
+  static constexpr int DRAIN_WARP0 = 8, DRAIN_WARPS = 8;
+  static constexpr int CW = BN / 2;          // columns per drain warp
+  static constexpr bool REALLOC = CW > 64;   // drainers need > 128 registers
+  static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
+  static_assert(STAGES >= 2, "stages");
+  static_assert(!(IM2COL && A_MN), "im2col A is K-major");
+};
+
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
+  using namespace ptx;
+  constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, STAGES = Cfg::STAGES, CW = Cfg::CW;
+  constexpr bool X3 = Cfg::X3;
+  constexpr bool RELAY = X3 || CTAS == 2;  // MMA waits on the splitters' barrier
+
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full_tma[8];
+  __shared__ __align__(8) uint64_t bar_full_split[8];
+  __shared__ __align__(8) uint64_t bar_empty[8];
+  __shared__ __align__(8) uint64_t bar_tmem_full[2];
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+
+  const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+
+  // ---- tile and k-range of this CTA (pair)
+  const int tile = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  constexpr int GROUP = 8;  // m-tiles swept together so concurrently resident tiles share operands in L2
+  const int per_group = GROUP * p.tiles_n;
+  const int g_first = (tile / per_group) * GROUP;
+  const int g_size = min(p.tiles_m - g_first, GROUP);
+  const int tm = g_first + (tile % per_group) % g_size;
+  const int tn = (tile % per_group) / g_size;
+
+  const int z = blockIdx.z;
+  const int nkb_total = p.nkb_total;
+  int kb0 = 0, nkb = nkb_total, batch = z;
+  float* out = p.C;
+  if (p.gz > 1) {
+    kb0 = static_cast<int>((static_cast<long long>(z) * nkb_total) / p.gz);
+    nkb = static_cast<int>((static_cast<long long>(z + 1) * nkb_total) / p.gz) - kb0;
+    batch = 0;
+    if (z > 0) out = p.Cbuf + static_cast<long long>(z - 1) * p.c_stride;
+  } else {
+    out = p.C + static_cast<long long>(z) * p.c_stride;
+  }
+  const int kc = p.kc;
+  const int row0 = (tm * CTAS + static_cast<int>(rank)) * Cfg::BM;  // first A row of this CTA
+  const int col0 = tn * BN;                                         // first C column of the tile
+  const int bcol0 = col0 + static_cast<int>(rank) * Cfg::BN_CTA;    // first B column staged here
+
+  auto give_up = [&](int role, int a, int b) {
+    abort_flag = 1;
+    atomicCAS(p.status, 0, (role << 24) | ((a & 0xFF) << 16) | (b & 0xFFFF));
+  };
+
+  // ---- one-time setup
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(smem_u32(&bar_full_tma[s]), 1);
+      mbar_init(smem_u32(&bar_full_split[s]), Cfg::SPLIT_WARPS * CTAS);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+      mbar_init(smem_u32(&bar_tmem_empty[b]), Cfg::DRAIN_WARPS * CTAS);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmA);
+    tma_prefetch_desc(&p.tmB);
+  }
+  if (warp == 2) {
+    tmem_alloc<CTAS>(smem_u32(&tmem_base_slot), Cfg::TMEM_COLS);
+    tmem_relinquish<CTAS>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (CTAS == 2) cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  // Barrier addresses on the CTA that issues the MMAs (rank 0).
+  auto leader_addr = [&](const uint64_t* bar) -> uint32_t {
+    return (CTAS == 2) ? mapa(smem_u32(bar), 0u) : smem_u32(bar);
+  };
+
+  // Warps 0..7 (two warpgroups) run the data-movement roles on a small register
+  // budget; warps 8..15 hold the FP32 accumulators.  With 256-column tiles the
+  // accumulators alone need 128 registers per thread, so registers are moved
+  // from the first two warpgroups to the last two.
+  if (warp < Cfg::DRAIN_WARP0) {
+  if (Cfg::REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
+          give_up(ROLE_TMA, s, i);
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full_tma[s]);
+        mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
+        int k0 = (kb0 + i) * Cfg::BK;
+        const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
+        const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+        if (Cfg::IM2COL) {
+          // k-block -> (filter tap, block of 32 channels inside the tap)
+          const int tap = (kb0 + i) / p.conv_icb;
+          const int ic0 = ((kb0 + i) - tap * p.conv_icb) * Cfg::BK;
+          const int fh = tap / p.conv_FW;
+          const int fw = tap - fh * p.conv_FW;
+          k0 = tap * p.conv_IC + ic0;  // position in the filter's (fh, fw, ic) axis
+          // row0 addresses output pixel (n, oh, ow); the run of 128 pixels wraps
+          // over rows and images inside the tensor map's traversal box.
+          const int ohw = p.conv_OH * p.conv_OW;
+          const int n = row0 / ohw;
+          const int r = row0 - n * ohw;
+          const int oh = r / p.conv_OW;
+          const int ow = r - oh * p.conv_OW;
+          tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
+                             oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
+                             static_cast<uint16_t>(fh));
+        } else if (Cfg::A_MN) {
+#pragma unroll
+          for (int j = 0; j < Cfg::BM / 32; ++j)
+            tma_load_3d(a_dst + j * 4096, &p.tmA, full, row0 + 32 * j, k0, batch);
+        } else {
+          tma_load_3d(a_dst, &p.tmA, full, k0, row0, batch);
+        }
+        if (Cfg::B_MN) {
+#pragma unroll
+          for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
+            tma_load_3d(b_dst + j * 4096, &p.tmB, full, bcol0 + 32 * j, k0, batch);
+        } else {
+          tma_load_3d(b_dst, &p.tmB, full, k0, bcol0, batch);
+        }
+        issued = i + 1;
+      }
+      if (abort_flag) {
+        // Let copies already in flight land before shared memory is released:
+        // wait (bounded) for the barrier of every stage still outstanding.
+        for (int i = max(0, issued - STAGES); i < issued; ++i) {
+          const int s = i % STAGES;
+          const uint32_t ph = (i / STAGES) & 1;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(smem_u32(&bar_full_tma[s]), ph) && clock64() - t0 < 20000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN, Cfg::B_MN);
+      constexpr uint32_t A_LBO = Cfg::A_MN ? 4096u : 16u;
+      constexpr uint32_t B_LBO = Cfg::B_MN ? 4096u : 16u;
+      constexpr uint32_t A_KSTEP = Cfg::A_MN ? 1024u : 32u;  // bytes per 8 elements of K
+      constexpr uint32_t B_KSTEP = Cfg::B_MN ? 1024u : 32u;
+      int buf = 0;
+      uint32_t empty_parity[2] = {1u, 1u};
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
+        if (!mbar_wait<CTAS == 2>(ready, ph, &abort_flag)) {
+          give_up(ROLE_MMA, s, i);
+          break;
+        }
+        const bool chunk_start = (i % kc) == 0;
+        if (chunk_start) {
+          if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[buf]), empty_parity[buf], &abort_flag)) {
+            give_up(ROLE_MMA_TMEM, buf, i);
+            break;
+          }
+          empty_parity[buf] ^= 1u;
+        }
+        tc_fence_after();
+        const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
+        const uint32_t b_hi = a_hi + Cfg::A_BYTES;
+        const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
+#pragma unroll
+        for (int j = 0; j < Cfg::BK / 8; ++j) {
+          const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, 1024u);
+          const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, 1024u);
+          const uint32_t first = (chunk_start && j == 0) ? 0u : 1u;
+          if (X3) {
+            const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, 1024u);
+            const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, 1024u);
+            umma_tf32<CTAS>(d, da_lo, db_hi, idesc, first);  // small terms first
+            umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, 1u);
+          } else {
+            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, first);
+          }
+        }
+        // The stage may be refilled once these MMAs have read it.
+        umma_commit<CTAS>(smem_u32(&bar_empty[s]));
+        if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_empty[s]), 1u));
+        if (((i + 1) % kc) == 0 || i + 1 == nkb) {
+          umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
+          if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_tmem_full[buf]), 1u));
+          buf ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ splitters
+    if (RELAY) {
+      const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;
+      constexpr int NST = Cfg::SPLIT_WARPS * 32;
+      constexpr int NVEC = Cfg::HI_BYTES / 16;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
+          if (lane == 0) give_up(ROLE_SPLIT, s, i);
+          break;
+        }
+        if (X3) {
+          const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
+#pragma unroll 4
+          for (int v = st; v < NVEC; v += NST) {
+            const uint32_t addr = hi_base + v * 16;
+            const float4 x = lds128(addr);
+            float4 h, l;
+            h.x = rn_tf32(x.x); h.y = rn_tf32(x.y); h.z = rn_tf32(x.z); h.w = rn_tf32(x.w);
+            l.x = rn_tf32(x.x - h.x); l.y = rn_tf32(x.y - h.y);
+            l.z = rn_tf32(x.z - h.z); l.w = rn_tf32(x.w - h.w);
+            sts128(addr, h);
+            sts128(addr + Cfg::HI_BYTES, l);
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2 && rank != 0)
+            mbar_arrive_cluster(leader_addr(&bar_full_split[s]));
+          else
+            mbar_arrive(smem_u32(&bar_full_split[s]));
+        }
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------ drainers
+    if (Cfg::REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    const int q = warp & 3;                              // TMEM lane quarter this warp may read
+    const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
+    float acc[CW];
+#pragma unroll
+    for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
+    const int nchunks = (nkb + kc - 1) / kc;
+    bool ok = true;
+    for (int c = 0; c < nchunks; ++c) {
+      const int buf = c & 1;
+      const uint32_t par = (c >> 1) & 1;
+      if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
+        if (lane == 0) give_up(ROLE_DRAIN, buf, c);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                          static_cast<uint32_t>(buf * BN + h * CW);
+#pragma unroll
+      for (int g = 0; g < CW / 32; ++g) {
+        float t[32];
+        tmem_ld_32x32(t0 + g * 32, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[g * 32 + j] += t[j];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (CTAS == 2 && rank != 0)
+          mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
+        else
+          mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+      }
+    }
+    // ---- store this thread's row segment
+    const int row = row0 + q * 32 + lane;
+    if (ok && row < p.M) {
+      float* dst = out + static_cast<long long>(row) * p.ldc + col0 + h * CW;
+      const int ncols = p.N - (col0 + h * CW);  // columns left in this row segment
+      if (p.vec4_ok) {
+#pragma unroll
+        for (int j = 0; j < CW; j += 4) {
+          if (j + 3 < ncols) {
+            *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (j + e < ncols) dst[j + e] = acc[j + e];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; ++j)
+          if (j < ncols) dst[j] = acc[j];
+      }
+    }
+  }
+
+  // ---- common exit: everyone arrives here, also after a give-up
+  tc_fence_before();
+  __syncthreads();
+  if (CTAS == 2) cluster_sync();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace dragon

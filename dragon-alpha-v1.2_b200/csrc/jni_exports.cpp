@@ -1,0 +1,180 @@
+// JNI exports: the Java_z_dragon_engine_cuda_impl_math_Cuda_1* symbols that the
+// Java classes Cuda_matMul, Cuda_batchMatMul and Cuda_conv3D bind to, as thin
+// wrappers over the C ABI in include/dragon_cu32.h.
+//
+// Behaviour mirrors the reference wrappers (engine-cuda-base/Cuda_matMul/Cuda_matMul/A.cu,
+// Cuda_batchMatMul/.../A.cu, Cuda_conv3D/.../A.cu and JNITool.cuh): copy up to 10 stream
+// handles out of the long[] with GetLongArrayRegion, cast the jlong addresses to device
+// pointers, run the operation, and on a non-zero result construct
+// z.dragon.engine.cuda.impl.CudaException(int) and Throw it, returning normally.
+#ifdef DRAGON_USE_SYSTEM_JNI
+#include <jni.h>
+static inline jclass jni_FindClass(JNIEnv* env, const char* n) { return env->FindClass(n); }
+static inline jint jni_Throw(JNIEnv* env, jthrowable o) { return env->Throw(o); }
+static inline jobject jni_NewObjectA(JNIEnv* env, jclass c, jmethodID m, const jvalue* a) { return env->NewObjectA(c, m, a); }
+static inline jmethodID jni_GetMethodID(JNIEnv* env, jclass c, const char* n, const char* s) { return env->GetMethodID(c, n, s); }
+static inline void jni_GetLongArrayRegion(JNIEnv* env, jlongArray a, jint s, jint l, jlong* b) { env->GetLongArrayRegion(a, s, l, b); }
+#else
+#include "jni_min.h"
+#endif
+#include "../../include/dragon_cu32.h"
+
+namespace {
+
+void throw_cuda_exception(JNIEnv* env, int code) {
+  jclass cls = jni_FindClass(env, "z/dragon/engine/cuda/impl/CudaException");
+  if (!cls) return;  // FindClass has already raised NoClassDefFoundError
+  jmethodID ctor = jni_GetMethodID(env, cls, "<init>", "(I)V");
+  if (!ctor) return;
+  jvalue arg;
+  arg.i = code;
+  jobject ex = jni_NewObjectA(env, cls, ctor, &arg);
+  if (ex) jni_Throw(env, static_cast<jthrowable>(ex));
+}
+
+struct Streams {
+  int64_t h[10];
+  int n;
+  Streams(JNIEnv* env, jlongArray arr, jint length) : n(length) {
+    for (int i = 0; i < 10; ++i) h[i] = 0;
+    if (length >= 1 && length <= 10) {
+      jlong tmp[10];
+      jni_GetLongArrayRegion(env, arr, 0, length, tmp);
+      for (int i = 0; i < length; ++i) h[i] = tmp[i];
+    }
+  }
+};
+
+inline const float* cptr(jlong a) { return reinterpret_cast<const float*>(static_cast<intptr_t>(a)); }
+inline float* mptr(jlong a) { return reinterpret_cast<float*>(static_cast<intptr_t>(a)); }
+inline void done(JNIEnv* env, int rc) { if (rc != 0) throw_cuda_exception(env, rc); }
+
+}  // namespace
+
+#define JNAME(cls, method) Java_z_dragon_engine_cuda_impl_math_Cuda_1##cls##_##method
+
+extern "C" {
+
+// ---------------------------------------------------------------- Cuda_matMul
+JNIEXPORT void JNICALL JNAME(matMul, SKbuf_1summary)(JNIEnv* env, jclass, jlong stream, jlong dCbuf, jlong dC,
+                                                     jint part, jint sizeC) {
+  done(env, cu32_SKbuf_summary(stream, cptr(dCbuf), mptr(dC), part, sizeC));
+}
+#define MATMUL_PLAIN(jname, cname)                                                                  \
+  JNIEXPORT void JNICALL JNAME(matMul, jname)(JNIEnv* env, jclass, jlongArray streams, jint length, \
+                                              jlong dA, jlong dB, jlong dC, jint N, jint M, jint K) { \
+    Streams s(env, streams, length);                                                                \
+    done(env, cname(s.h, s.n, cptr(dA), cptr(dB), mptr(dC), N, M, K));                              \
+  }
+#define MATMUL_SK(jname, cname)                                                                     \
+  JNIEXPORT void JNICALL JNAME(matMul, jname)(JNIEnv* env, jclass, jlongArray streams, jint length, \
+                                              jint GridZ, jlong dA, jlong dB, jlong dC, jlong dCbuf, \
+                                              jint N, jint M, jint K) {                             \
+    Streams s(env, streams, length);                                                                \
+    done(env, cname(s.h, s.n, GridZ, cptr(dA), cptr(dB), mptr(dC), mptr(dCbuf), N, M, K));          \
+  }
+MATMUL_PLAIN(matMul, cu32_matMul)
+MATMUL_PLAIN(matMulT1, cu32_matMulT1)
+MATMUL_PLAIN(matMulT2, cu32_matMulT2)
+MATMUL_PLAIN(matMul_1mma, cu32_matMul_mma)
+MATMUL_PLAIN(matMulT1_1mma, cu32_matMulT1_mma)
+MATMUL_PLAIN(matMulT2_1mma, cu32_matMulT2_mma)
+MATMUL_SK(matMulSK, cu32_matMulSK)
+MATMUL_SK(matMulT1SK, cu32_matMulT1SK)
+MATMUL_SK(matMulT2SK, cu32_matMulT2SK)
+
+// ---------------------------------------------------------------- Cuda_batchMatMul
+#define BMM_PLAIN(jname, cname)                                                                          \
+  JNIEXPORT void JNICALL JNAME(batchMatMul, jname)(JNIEnv* env, jclass, jlongArray streams, jint length, \
+                                                   jlong dA, jlong dB, jlong dC, jint Batch, jint d0,    \
+                                                   jint d1, jint d2, jint d3) {                          \
+    Streams s(env, streams, length);                                                                     \
+    done(env, cname(s.h, s.n, cptr(dA), cptr(dB), mptr(dC), Batch, d0, d1, d2, d3));                     \
+  }
+#define BMM_TEX_FLAG(jname, cname)                                                                       \
+  JNIEXPORT void JNICALL JNAME(batchMatMul, jname)(JNIEnv* env, jclass, jboolean useTexture,             \
+                                                   jlongArray streams, jint length, jlong dA, jlong dB,  \
+                                                   jlong dC, jint Batch, jint d0, jint d1, jint d2,      \
+                                                   jint d3) {                                            \
+    Streams s(env, streams, length);                                                                     \
+    done(env, cname(useTexture ? 1 : 0, s.h, s.n, cptr(dA), cptr(dB), mptr(dC), Batch, d0, d1, d2, d3)); \
+  }
+BMM_PLAIN(batchMatMul, cu32_batchMatMul)
+BMM_PLAIN(batchMatMul_1texture, cu32_batchMatMul_texture)
+BMM_PLAIN(batchMatMulT1, cu32_batchMatMulT1)
+BMM_PLAIN(batchMatMulT2, cu32_batchMatMulT2)
+BMM_PLAIN(batchMatMulT2_1texture, cu32_batchMatMulT2_texture)
+BMM_PLAIN(batchMatMulT1_1mma, cu32_batchMatMulT1_mma)
+BMM_TEX_FLAG(batchMatMul_1mma, cu32_batchMatMul_mma)
+BMM_TEX_FLAG(batchMatMulT2_1mma, cu32_batchMatMulT2_mma)
+
+// ---------------------------------------------------------------- Cuda_conv3D
+JNIEXPORT void JNICALL JNAME(conv3D, kernel_1remode)(JNIEnv* env, jclass, jlong stream, jlong dW, jlong dCW,
+                                                     jint FH, jint FW, jint OC, jint IC) {
+  done(env, cu32_kernel_remode(stream, cptr(dW), mptr(dCW), FH, FW, OC, IC));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dX,
+                                             jint IH, jint IW, jlong dW, jint FH, jint FW, jlong dY, jint OH,
+                                             jint OW, jint N, jint IC, jint OC, jint sh, jint sw, jint ph,
+                                             jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D(s.h, s.n, cptr(dX), IH, IW, cptr(dW), FH, FW, mptr(dY), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1texture)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                      jlong dX, jint IH, jint IW, jlong dW, jint FH, jint FW,
+                                                      jlong dY, jint OH, jint OW, jint N, jint IC, jint OC,
+                                                      jint sh, jint sw, jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_texture(s.h, s.n, cptr(dX), IH, IW, cptr(dW), FH, FW, mptr(dY), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1np)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                 jlong dX, jint IH, jint IW, jlong dW, jint FH, jint FW,
+                                                 jlong dY, jint OH, jint OW, jint N, jint IC, jint OC,
+                                                 jint sh, jint sw) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_np(s.h, s.n, cptr(dX), IH, IW, cptr(dW), FH, FW, mptr(dY), OH, OW, N, IC, OC, sh, sw));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                 jlong dX, jint IH, jint IW, jlong dW, jlong dY, jint N,
+                                                 jint IC, jint OC) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_W1(s.h, s.n, cptr(dX), IH, IW, cptr(dW), mptr(dY), N, IC, OC));
+}
+#define CONV_GEMMR(jname, cname)                                                                          \
+  JNIEXPORT void JNICALL JNAME(conv3D, jname)(JNIEnv* env, jclass, jlongArray streams, jint length,       \
+                                              jlong dX, jint IH, jint IW, jlong dW, jlong dCW, jint FH,   \
+                                              jint FW, jlong dY, jint OH, jint OW, jint N, jint IC,       \
+                                              jint OC, jint sh, jint sw, jint ph, jint pw) {              \
+    Streams s(env, streams, length);                                                                      \
+    done(env, cname(s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW, mptr(dY), OH, OW, N, IC, OC, \
+                    sh, sw, ph, pw));                                                                     \
+  }
+#define CONV_GEMMR_SGM(jname, cname)                                                                      \
+  JNIEXPORT void JNICALL JNAME(conv3D, jname)(JNIEnv* env, jclass, jlongArray streams, jint length,       \
+                                              jlong dX, jint IH, jint IW, jlong dW, jlong dCW, jint FH,   \
+                                              jint FW, jlong dY, jint OH, jint OW, jint N, jint IC,       \
+                                              jint OC, jint sh, jint sw, jint ph, jint pw,                \
+                                              jint GM_slice) {                                            \
+    Streams s(env, streams, length);                                                                      \
+    done(env, cname(s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW, mptr(dY), OH, OW, N, IC, OC, \
+                    sh, sw, ph, pw, GM_slice));                                                           \
+  }
+CONV_GEMMR(conv3D_1GemmR, cu32_conv3D_GemmR)
+CONV_GEMMR(conv3D_1GemmR_1texture, cu32_conv3D_GemmR_texture)
+CONV_GEMMR_SGM(conv3D_1GemmR_1SGM, cu32_conv3D_GemmR_SGM)
+CONV_GEMMR_SGM(conv3D_1GemmR_1texture_1SGM, cu32_conv3D_GemmR_texture_SGM)
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmR_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                        jlong dX, jint IH, jint IW, jlong dW, jlong dCW,
+                                                        jlong dY, jint N, jint IC, jint OC) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_GemmR_W1(s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), mptr(dY), N, IC, OC));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmR_1W1_1SGM)(JNIEnv* env, jclass, jlongArray streams,
+                                                             jint length, jlong dX, jint IH, jint IW,
+                                                             jlong dW, jlong dCW, jlong dY, jint N, jint IC,
+                                                             jint OC, jint GM_slice) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_GemmR_W1_SGM(s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), mptr(dY), N, IC, OC, GM_slice));
+}
+
+}  // extern "C"

@@ -1,0 +1,367 @@
+"""ctypes binding of libdragon_cu32.so.
+
+The three classes mirror the Java classes of the reference that declare the natives
+(``z/dragon/engine/cuda/impl/math/Cuda_matMul.java``, ``Cuda_batchMatMul.java``,
+``Cuda_conv3D.java``): same static-method names, same argument order, device memory and
+streams passed as integers exactly as the Java side passes ``long`` addresses.  A non-zero
+return code raises :class:`CudaException`, the analogue of
+``z.dragon.engine.cuda.impl.CudaException``.
+
+There is no fallback: if the shared library is missing, loading fails with an error that
+says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, POINTER
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libdragon_cu32.so"
+
+ERROR_NAMES = {
+    -1: "CU32_E_NULL", -2: "CU32_E_DIM", -3: "CU32_E_STREAMS", -4: "CU32_E_ALIGN",
+    -5: "CU32_E_GEOMETRY", -6: "CU32_E_DRIVER", -7: "CU32_E_TENSORMAP", -8: "CU32_E_ARG",
+}
+
+TILE_NAMES = {0: "128x64", 1: "128x128", 2: "128x256", 3: "256x128 pair", 4: "256x256 pair"}
+
+
+class CudaException(RuntimeError):
+    """Raised for a non-zero return code (positive: cudaError_t, negative: CU32_E_*)."""
+
+    def __init__(self, code: int, where: str = ""):
+        self.code = code
+        name = ERROR_NAMES.get(code, f"cudaError {code}" if code > 0 else f"error {code}")
+        super().__init__(f"{where}: {name}" if where else name)
+
+
+_lib = None
+_fp = POINTER(c_float)
+_sp = POINTER(c_int64)
+
+
+def _sig(lib, name, argtypes):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = c_int
+    return fn
+
+
+# name -> ctypes argument types; also the list of symbols include/dragon_cu32.h declares.
+_I = c_int
+SIGNATURES = {
+    "cu32_matMul": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT1": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT2": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulSK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT1SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT2SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_SKbuf_summary": [c_int64, _fp, _fp, _I, _I],
+    "cu32_matMul_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT1_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_matMulT2_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_batchMatMul": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMul_texture": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMulT1": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMulT2": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMulT2_texture": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMul_mma": [_I, _sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMulT1_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_batchMatMulT2_mma": [_I, _sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I],
+    "cu32_kernel_remode": [c_int64, _fp, _fp, _I, _I, _I, _I],
+    "cu32_conv3D_GemmR": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_GemmR_texture": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_GemmR_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_conv3D_GemmR_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_conv3D_GemmR_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_conv3D_GemmR_W1_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_conv3D": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_texture": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_np": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_conv3D_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _I],
+    "cu32_tune": [c_char_p, _I],
+    "cu32_get_tune": [c_char_p, POINTER(c_int)],
+    "cu32_read_status": [POINTER(c_int)],
+}
+
+
+def load():
+    """Load libdragon_cu32.so (once) and declare every entry point's signature."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(needs nvcc); there is no CPU or PyTorch fallback for this library")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, args in SIGNATURES.items():
+        _sig(lib, name, args)
+    lib.cu32_version.argtypes = []
+    lib.cu32_version.restype = c_char_p
+    _lib = lib
+    return lib
+
+
+def _p(addr):
+    return ctypes.cast(ctypes.c_void_p(int(addr)), _fp)
+
+
+def _streams(streamArray, length):
+    arr = (c_int64 * 10)(*([int(s) for s in streamArray[:10]] + [0] * (10 - min(len(streamArray), 10))))
+    return arr, int(length)
+
+
+def _check(rc, where):
+    if rc != 0:
+        raise CudaException(rc, where)
+
+
+def tune(key: str, value: int) -> None:
+    _check(load().cu32_tune(key.encode(), int(value)), f"cu32_tune({key})")
+
+
+def get_tune(key: str) -> int:
+    v = c_int(0)
+    _check(load().cu32_get_tune(key.encode(), ctypes.byref(v)), f"cu32_get_tune({key})")
+    return v.value
+
+
+def read_status() -> int:
+    """Device give-up word (0 = every bounded wait completed).  Synchronises the device."""
+    v = c_int(0)
+    _check(load().cu32_read_status(ctypes.byref(v)), "cu32_read_status")
+    return v.value
+
+
+def decode_status(word: int) -> str:
+    if word == 0:
+        return "ok"
+    roles = {1: "tma-producer", 2: "splitter", 3: "mma(operands)", 4: "mma(tmem-buffer)", 5: "drainer"}
+    return f"{roles.get(word >> 24, word >> 24)} gave up at stage/buffer {(word >> 16) & 0xFF}, iteration {word & 0xFFFF}"
+
+
+def version() -> str:
+    return load().cu32_version().decode()
+
+
+class Cuda_matMul:
+    """Mirror of z.dragon.engine.cuda.impl.math.Cuda_matMul (natives + host helpers)."""
+
+    @staticmethod
+    def blockNum(N: int, M: int) -> int:
+        """Number of 128/64/.../4-wide blocks the reference's tiling cuts [N, M] into
+        (Cuda_matMul.java:18-38); input to the split-K decision."""
+        def count(x):
+            b = 0
+            if x > 127:
+                b += x >> 7
+            x &= 127
+            for w in (64, 32, 16, 8, 4):
+                if x == 0:
+                    break
+                if x >= w:
+                    b += 1
+                x &= w - 1
+            return b
+        return count(N) * count(M)
+
+    @staticmethod
+    def nstream(N: int, M: int) -> int:
+        """Streams the Java engine requests for an [N, M] output (Cuda_matMul.java:41-65)."""
+        def count(x):
+            if x & (x - 1) == 0:
+                return 1
+            s = 0
+            for w in (128, 64, 32, 16, 8, 4):
+                if x == 0:
+                    break
+                if x >= w:
+                    s += 1
+                x &= w - 1
+            return s
+        size = count(N) * count(M)
+        return size if size < 10 else 10
+
+    @staticmethod
+    def matMul(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMul(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMul")
+
+    @staticmethod
+    def matMulT1(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT1(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMulT1")
+
+    @staticmethod
+    def matMulT2(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT2(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMulT2")
+
+    @staticmethod
+    def matMul_mma(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMul_mma(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMul_mma")
+
+    @staticmethod
+    def matMulT1_mma(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT1_mma(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMulT1_mma")
+
+    @staticmethod
+    def matMulT2_mma(streamArray, length, dA, dB, dC, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT2_mma(s, n, _p(dA), _p(dB), _p(dC), N, M, K), "matMulT2_mma")
+
+    @staticmethod
+    def matMulSK(streamArray, length, GridZ, dA, dB, dC, dCbuf, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulSK(s, n, GridZ, _p(dA), _p(dB), _p(dC), _p(dCbuf), N, M, K), "matMulSK")
+
+    @staticmethod
+    def matMulT1SK(streamArray, length, GridZ, dA, dB, dC, dCbuf, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT1SK(s, n, GridZ, _p(dA), _p(dB), _p(dC), _p(dCbuf), N, M, K), "matMulT1SK")
+
+    @staticmethod
+    def matMulT2SK(streamArray, length, GridZ, dA, dB, dC, dCbuf, N, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMulT2SK(s, n, GridZ, _p(dA), _p(dB), _p(dC), _p(dCbuf), N, M, K), "matMulT2SK")
+
+    @staticmethod
+    def SKbuf_summary(stream, dCbuf, dC, part, sizeC):
+        _check(load().cu32_SKbuf_summary(int(stream), _p(dCbuf), _p(dC), part, sizeC), "SKbuf_summary")
+
+
+class Cuda_batchMatMul:
+    """Mirror of z.dragon.engine.cuda.impl.math.Cuda_batchMatMul."""
+
+    @staticmethod
+    def batchMatMul(streamArray, length, dA, dB, dC, Batch, N, M, BK, AK):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMul(s, n, _p(dA), _p(dB), _p(dC), Batch, N, M, BK, AK), "batchMatMul")
+
+    @staticmethod
+    def batchMatMul_texture(streamArray, length, dA, dB, dC, Batch, N, M, BK, AK):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMul_texture(s, n, _p(dA), _p(dB), _p(dC), Batch, N, M, BK, AK),
+               "batchMatMul_texture")
+
+    @staticmethod
+    def batchMatMul_mma(useTexture, streamArray, length, dA, dB, dC, Batch, N, M, BK, AK):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMul_mma(int(bool(useTexture)), s, n, _p(dA), _p(dB), _p(dC), Batch, N, M, BK, AK),
+               "batchMatMul_mma")
+
+    @staticmethod
+    def batchMatMulT1(streamArray, length, dA, dB, dC, Batch, CN, AN, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMulT1(s, n, _p(dA), _p(dB), _p(dC), Batch, CN, AN, M, K), "batchMatMulT1")
+
+    @staticmethod
+    def batchMatMulT1_mma(streamArray, length, dA, dB, dC, Batch, CN, AN, M, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMulT1_mma(s, n, _p(dA), _p(dB), _p(dC), Batch, CN, AN, M, K), "batchMatMulT1_mma")
+
+    @staticmethod
+    def batchMatMulT2(streamArray, length, dA, dB, dC, Batch, N, CM, BM, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMulT2(s, n, _p(dA), _p(dB), _p(dC), Batch, N, CM, BM, K), "batchMatMulT2")
+
+    @staticmethod
+    def batchMatMulT2_texture(streamArray, length, dA, dB, dC, Batch, N, CM, BM, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMulT2_texture(s, n, _p(dA), _p(dB), _p(dC), Batch, N, CM, BM, K),
+               "batchMatMulT2_texture")
+
+    @staticmethod
+    def batchMatMulT2_mma(useTexture, streamArray, length, dA, dB, dC, Batch, N, CM, BM, K):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_batchMatMulT2_mma(int(bool(useTexture)), s, n, _p(dA), _p(dB), _p(dC), Batch, N, CM, BM, K),
+               "batchMatMulT2_mma")
+
+
+class Cuda_conv3D:
+    """Mirror of the GEMM / GEMMR natives of z.dragon.engine.cuda.impl.math.Cuda_conv3D."""
+
+    @staticmethod
+    def kernel_remode(stream, dW, dCW, FH, FW, OC, IC):
+        _check(load().cu32_kernel_remode(int(stream), _p(dW), _p(dCW), FH, FW, OC, IC), "kernel_remode")
+
+    @staticmethod
+    def conv3D_GemmR(streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW, _p(dY), OH, OW, N, IC, OC,
+                                        sh, sw, ph, pw), "conv3D_GemmR")
+
+    @staticmethod
+    def conv3D_GemmR_texture(streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_texture(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW, _p(dY), OH, OW, N, IC,
+                                                OC, sh, sw, ph, pw), "conv3D_GemmR_texture")
+
+    @staticmethod
+    def conv3D_GemmR_SGM(streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw,
+                         GM_slice):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_SGM(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW, _p(dY), OH, OW, N, IC, OC,
+                                            sh, sw, ph, pw, GM_slice), "conv3D_GemmR_SGM")
+
+    @staticmethod
+    def conv3D_GemmR_texture_SGM(streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph,
+                                 pw, GM_slice):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_texture_SGM(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW, _p(dY), OH, OW, N,
+                                                    IC, OC, sh, sw, ph, pw, GM_slice), "conv3D_GemmR_texture_SGM")
+
+    @staticmethod
+    def conv3D_GemmR_W1(streamArray, length, dX, IH, IW, dW, dCW, dY, N, IC, OC):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_W1(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), _p(dY), N, IC, OC), "conv3D_GemmR_W1")
+
+    @staticmethod
+    def conv3D_GemmR_W1_SGM(streamArray, length, dX, IH, IW, dW, dCW, dY, N, IC, OC, GM_slice):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_W1_SGM(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), _p(dY), N, IC, OC, GM_slice),
+               "conv3D_GemmR_W1_SGM")
+
+    @staticmethod
+    def conv3D(streamArray, length, dX, IH, IW, dW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D(s, n, _p(dX), IH, IW, _p(dW), FH, FW, _p(dY), OH, OW, N, IC, OC, sh, sw, ph, pw),
+               "conv3D")
+
+    @staticmethod
+    def conv3D_texture(streamArray, length, dX, IH, IW, dW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_texture(s, n, _p(dX), IH, IW, _p(dW), FH, FW, _p(dY), OH, OW, N, IC, OC, sh, sw, ph,
+                                          pw), "conv3D_texture")
+
+    @staticmethod
+    def conv3D_np(streamArray, length, dX, IH, IW, dW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_np(s, n, _p(dX), IH, IW, _p(dW), FH, FW, _p(dY), OH, OW, N, IC, OC, sh, sw),
+               "conv3D_np")
+
+    @staticmethod
+    def conv3D_W1(streamArray, length, dX, IH, IW, dW, dY, N, IC, OC):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_W1(s, n, _p(dX), IH, IW, _p(dW), _p(dY), N, IC, OC), "conv3D_W1")
+
+    max_grid = 65535
+    grid_slice = 32768
+
+    @staticmethod
+    def GEMM_GM_slice(GN: int, GM: int, GK: int) -> int:
+        """Slice of GM the Java side passes to the _SGM natives when the reference's grid
+        would exceed 65535 blocks along GM (Cuda_conv3D.java:346-356); -1 = no slicing.
+        This library accepts the slice and ignores it (the result does not depend on it)."""
+        max_GM = (Cuda_conv3D.max_grid + 1) << 6
+        if GM < max_GM:
+            return -1
+        flag = GN > 127 and (GK & 7) == 0
+        bm = GM >> 7 if flag else GM >> 6
+        if bm <= Cuda_conv3D.max_grid:
+            return -1
+        return Cuda_conv3D.grid_slice << (7 if flag else 6)

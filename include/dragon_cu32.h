@@ -1,0 +1,192 @@
+/* C ABI of libdragon_cu32.so: the dense-contraction entry points of Dragon-Alpha's
+ * Cu32 GPU library (Cuda_matMul, Cuda_batchMatMul, and the GEMM / GEMMR forward
+ * convolution of Cuda_conv3D), implemented for NVIDIA B200 (sm_100a).
+ *
+ * One function per JNI native of the reference, same argument order and meaning;
+ * the JNI-only leading arguments (JNIEnv*, jclass) are dropped and the jlongArray
+ * of stream handles becomes `const int64_t* streams` (each element a cudaStream_t
+ * cast to a 64-bit integer, exactly what the Java side stores in its long[]).
+ * The library also exports the Java_z_dragon_engine_cuda_impl_math_* symbols
+ * themselves (thin wrappers over these functions), so a JVM can bind it directly.
+ *
+ * Conventions shared by all functions (identical to the reference natives):
+ *  - every pointer is a device pointer owned by the caller; nothing is allocated or
+ *    retained by the library; outputs are fully overwritten, inputs untouched;
+ *  - calls are asynchronous: work is enqueued on streams[0] and the function returns
+ *    without synchronising the device; `length` is the number of valid stream handles
+ *    (1..10);
+ *  - matrices are dense row-major FP32; letters follow the reference:
+ *    C[N,M] has N rows and M columns;
+ *  - every row pitch must be a multiple of 4 floats and every base pointer 16-byte
+ *    aligned (the Java engine pads all tensors this way);
+ *  - arithmetic: FP32 in, FP32 out.  The plain entry points are FP32-accurate (each
+ *    product is formed from a hi/lo TF32 split of both inputs, three tensor-core
+ *    products per term); the `_mma` entry points are the single-pass TF32 fast mode
+ *    the Java engine selects with its tf32 flag.
+ *
+ * Return value: 0 on success; a positive value is a cudaError_t reported by the CUDA
+ * runtime for this call; negative values are argument errors (CU32_E_*).  The JNI
+ * wrappers translate any non-zero value into z.dragon.engine.cuda.impl.CudaException.
+ */
+#ifndef DRAGON_CU32_H
+#define DRAGON_CU32_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CU32_API __attribute__((visibility("default")))
+#else
+#define CU32_API
+#endif
+
+#define CU32_OK 0
+#define CU32_E_NULL (-1)        /* a required pointer is null */
+#define CU32_E_DIM (-2)         /* a dimension is <= 0 or too large */
+#define CU32_E_STREAMS (-3)     /* length outside 1..10 or streams == NULL */
+#define CU32_E_ALIGN (-4)       /* pointer not 16-byte aligned or pitch % 4 != 0 */
+#define CU32_E_GEOMETRY (-5)    /* convolution geometry the tensor-map path cannot express */
+#define CU32_E_DRIVER (-6)      /* tensor-map encoder entry point not available in the driver */
+#define CU32_E_TENSORMAP (-7)   /* the driver rejected a tensor map */
+#define CU32_E_ARG (-8)         /* other invalid argument (e.g. GridZ < 1, unknown tuning key) */
+
+/* ------------------------------------------------------------------ Cuda_matMul
+ * Reference: source/engine-cuda-base/Cuda_matMul/Cuda_matMul/A.cu,
+ * Java natives: z/dragon/engine/cuda/impl/math/Cuda_matMul.java. */
+
+/* C[N,M] = A[N,K] * B[K,M].          replaces JNI matMul      (A.cu:41-56) */
+CU32_API int cu32_matMul(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                int N, int M, int K);
+/* C[N,M] = A[K,N]^T * B[K,M].        replaces JNI matMulT1    (A.cu:90-105) */
+CU32_API int cu32_matMulT1(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                  int N, int M, int K);
+/* C[N,M] = A[N,K] * B[M,K]^T.        replaces JNI matMulT2    (A.cu:139-154) */
+CU32_API int cu32_matMulT2(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                  int N, int M, int K);
+
+/* Split-K forms: K is cut into GridZ slices; slice 0 is written to C and slice z >= 1 to
+ * Cbuf[(z-1)*N*M ...]; the caller then sums them with cu32_SKbuf_summary.  Cbuf holds
+ * (GridZ-1)*N*M floats.  Slice boundaries are multiples of 32 (the reference cuts at
+ * multiples of 8, Cuda_matMul/micro.cuh:92); the sum over slices is the same product.
+ * replaces JNI matMulSK (A.cu:59-79), matMulT1SK (A.cu:108-128), matMulT2SK (A.cu:157-178) */
+CU32_API int cu32_matMulSK(const int64_t* streams, int length, int GridZ, const float* dA, const float* dB,
+                  float* dC, float* dCbuf, int N, int M, int K);
+CU32_API int cu32_matMulT1SK(const int64_t* streams, int length, int GridZ, const float* dA, const float* dB,
+                    float* dC, float* dCbuf, int N, int M, int K);
+CU32_API int cu32_matMulT2SK(const int64_t* streams, int length, int GridZ, const float* dA, const float* dB,
+                    float* dC, float* dCbuf, int N, int M, int K);
+
+/* C[i] += sum_{p < part} Cbuf[p*sizeC + i], compensated (Kahan) summation, in place.
+ * replaces JNI SKbuf_summary (A.cu:20-30, SKbufsum.cuh:29-81) */
+CU32_API int cu32_SKbuf_summary(int64_t stream, const float* dCbuf, float* dC, int part, int sizeC);
+
+/* Single-pass TF32 fast mode; declared by the Java class (Cuda_matMul.java:163-166, :278-282,
+ * :369-373) and called when the engine's tf32 flag is set; absent from the published C++. */
+CU32_API int cu32_matMul_mma(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                    int N, int M, int K);
+CU32_API int cu32_matMulT1_mma(const int64_t* streams, int length, const float* dA, const float* dB,
+                      float* dC, int N, int M, int K);
+CU32_API int cu32_matMulT2_mma(const int64_t* streams, int length, const float* dA, const float* dB,
+                      float* dC, int N, int M, int K);
+
+/* ------------------------------------------------------------------ Cuda_batchMatMul
+ * Reference: source/engine-cuda-base/Cuda_batchMatMul/Cuda_batchMatMul/A.cu. */
+
+/* C[b][N,M] = A[b][N,AK] * B[b][BK,M]; the reduction runs over BK, AK >= BK is A's pitch.
+ * replaces JNI batchMatMul (A.cu:20-39) and batchMatMul_texture (A.cu:42-62) */
+CU32_API int cu32_batchMatMul(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                     int Batch, int N, int M, int BK, int AK);
+CU32_API int cu32_batchMatMul_texture(const int64_t* streams, int length, const float* dA, const float* dB,
+                             float* dC, int Batch, int N, int M, int BK, int AK);
+/* C[b][CN,M] = A[b][K,AN]^T * B[b][K,M]; AN >= CN is A's pitch.
+ * replaces JNI batchMatMulT1 (A.cu:71-89) */
+CU32_API int cu32_batchMatMulT1(const int64_t* streams, int length, const float* dA, const float* dB,
+                       float* dC, int Batch, int CN, int AN, int M, int K);
+/* C[b][N,CM] = A[b][N,K] * B[b][BM,K]^T; CM >= BM is C's pitch, columns BM..CM-1 are written 0.
+ * replaces JNI batchMatMulT2 (A.cu:98-116) and batchMatMulT2_texture (A.cu:119-143) */
+CU32_API int cu32_batchMatMulT2(const int64_t* streams, int length, const float* dA, const float* dB,
+                       float* dC, int Batch, int N, int CM, int BM, int K);
+CU32_API int cu32_batchMatMulT2_texture(const int64_t* streams, int length, const float* dA, const float* dB,
+                               float* dC, int Batch, int N, int CM, int BM, int K);
+/* TF32 fast mode (Cuda_batchMatMul.java:166-170, :236-239, :355-359). */
+CU32_API int cu32_batchMatMul_mma(int useTexture, const int64_t* streams, int length, const float* dA,
+                         const float* dB, float* dC, int Batch, int N, int M, int BK, int AK);
+CU32_API int cu32_batchMatMulT1_mma(const int64_t* streams, int length, const float* dA, const float* dB,
+                           float* dC, int Batch, int CN, int AN, int M, int K);
+CU32_API int cu32_batchMatMulT2_mma(int useTexture, const int64_t* streams, int length, const float* dA,
+                           const float* dB, float* dC, int Batch, int N, int CM, int BM, int K);
+
+/* ------------------------------------------------------------------ Cuda_conv3D (GEMM / GEMMR)
+ * Reference: source/engine-cuda-base/Cuda_conv3D/Cuda_conv3D/A.cu.
+ * X[N,IH,IW,IC] (NHWC), W[OC,FH,FW,IC], CW[FH,FW,IC,OC], Y[N,OH,OW,OC];
+ * Y[n,oh,ow,oc] = sum_{fh,fw,ic} X[n, oh*sh-ph+fh, ow*sw-pw+fw, ic] * W[oc,fh,fw,ic],
+ * zero outside the image. */
+
+/* CW[fh,fw,ic,oc] = W[oc,fh,fw,ic].   replaces JNI kernel_remode (A.cu:18-28) */
+CU32_API int cu32_kernel_remode(int64_t stream, const float* dW, float* dCW, int FH, int FW, int OC, int IC);
+
+/* replaces JNI conv3D_GemmR (A.cu:169-191), conv3D_GemmR_texture (A.cu:245-268) and their
+ * _SGM forms (A.cu:194-236, :271-314; GM_slice only bounds the reference's grid size and does
+ * not change the result) */
+CU32_API int cu32_conv3D_GemmR(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                      const float* dW, const float* dCW, int FH, int FW, float* dY, int OH, int OW,
+                      int N, int IC, int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_GemmR_texture(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                              const float* dW, const float* dCW, int FH, int FW, float* dY, int OH,
+                              int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_GemmR_SGM(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                          const float* dW, const float* dCW, int FH, int FW, float* dY, int OH,
+                          int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
+                          int GM_slice);
+CU32_API int cu32_conv3D_GemmR_texture_SGM(const int64_t* streams, int length, const float* dX, int IH,
+                                  int IW, const float* dW, const float* dCW, int FH, int FW,
+                                  float* dY, int OH, int OW, int N, int IC, int OC, int sh, int sw,
+                                  int ph, int pw, int GM_slice);
+/* 1x1, stride 1, no padding.  replaces JNI conv3D_GemmR_W1 (A.cu:323-341) and conv3D_GemmR_W1_SGM (A.cu:344-381) */
+CU32_API int cu32_conv3D_GemmR_W1(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                         const float* dW, const float* dCW, float* dY, int N, int IC, int OC);
+CU32_API int cu32_conv3D_GemmR_W1_SGM(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                             const float* dW, const float* dCW, float* dY, int N, int IC, int OC,
+                             int GM_slice);
+/* Filter not remoded (W only).  replaces JNI conv3D (A.cu:39-60), conv3D_texture (A.cu:63-87),
+ * conv3D_np (A.cu:114-136, no padding) and conv3D_W1 (A.cu:138-155) */
+CU32_API int cu32_conv3D(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
+                int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_texture(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                        const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC,
+                        int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_np(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                   const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
+                   int sh, int sw);
+CU32_API int cu32_conv3D_W1(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                   const float* dW, float* dY, int N, int IC, int OC);
+
+/* ------------------------------------------------------------------ library control
+ * No counterpart in the reference (its only native-side switch is a compile-time macro). */
+
+/* Tuning / diagnostics knobs, process-wide.  Keys:
+ *   "kc"       k-blocks (of 32) accumulated inside the tensor core before each FP32
+ *              register add, FP32-accurate mode (default 1)
+ *   "kc_fast"  same for the TF32 fast mode (default 4)
+ *   "tile"     force a tile configuration 0..4 (128x64, 128x128, 128x256, 256x128 pair,
+ *              256x256 pair); -1 = choose from the shape (default)
+ * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
+CU32_API int cu32_tune(const char* key, int value);
+CU32_API int cu32_get_tune(const char* key, int* value);
+
+/* Device-side give-up word of the current device: 0 if no kernel of this library ever ran
+ * out of its bounded waits, else (role<<24 | stage<<16 | iteration) of the first one.
+ * Synchronises the device; resets the word.  For tests and diagnostics only. */
+CU32_API int cu32_read_status(int* status);
+
+/* "dragon_cu32 <version> sm_100a" */
+CU32_API const char* cu32_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DRAGON_CU32_H */

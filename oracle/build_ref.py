@@ -1,0 +1,81 @@
+"""Compile the reference's own sources for this path into oracle/_ref/ (test infrastructure).
+
+What is built, from the read-only reference tree given by --reference (sources are compiled
+where they lie; nothing is copied into this repository):
+
+  libref_matmul.so   Cuda_matMul:      CPU check loops (test.cuh) + SIMT kernels/dispatchers
+  libref_bmm.so      Cuda_batchMatMul: same
+  libref_conv.so     Cuda_conv3D:      same (about 25 minutes; only with --conv)
+
+The CPU loops pin oracle/cu32_oracle.c (tests/test_oracle.py compares them bit for bit) and
+serve as the timed CPU baseline of the benchmark; the GPU dispatchers give the reference's
+own FP32 output on the same inputs as a second witness.  The reference's Visual-Studio
+build system is not used: each project is a single translation unit, compiled by one nvcc
+command on a thin wrapper (ref_wrap_*.cu) that #includes the project's headers.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+PROJECTS = {
+    "matmul": ("ref_wrap_matmul.cu", "Cuda_matMul/Cuda_matMul", "libref_matmul.so"),
+    "bmm": ("ref_wrap_bmm.cu", "Cuda_batchMatMul/Cuda_batchMatMul", "libref_bmm.so"),
+    "conv": ("ref_wrap_conv.cu", "Cuda_conv3D/Cuda_conv3D", "libref_conv.so"),
+}
+
+# The conv project was written on a case-insensitive file system: these includes differ in
+# case from the files on disk (conv3D.cuh:9, conv3D_tensor_remode.cuh:6-8).
+CASE_FIX = {
+    "conv3D_im2col_Winograd.cuh": "conv3D_Im2col_Winograd.cuh",
+    "conv3D_kernel_remode_v1.cuh": "conv3D_kernel_remode_V1.cuh",
+    "conv3D_kernel_remode_v2.cuh": "conv3D_kernel_remode_V2.cuh",
+    "conv3D_kernel_remode_v3.cuh": "conv3D_kernel_remode_V3.cuh",
+}
+
+
+def build(reference: Path, names: list[str], force: bool = False) -> list[Path]:
+    base = reference / "source" / "engine-cuda-base"
+    if not base.is_dir():
+        raise FileNotFoundError(f"{base} not found: the reference tree is needed to build oracle/_ref")
+    OUT.mkdir(exist_ok=True)
+    built = []
+    for name in names:
+        wrap, proj, lib = PROJECTS[name]
+        out = OUT / lib
+        if out.exists() and not force and out.stat().st_mtime > (HERE / wrap).stat().st_mtime:
+            built.append(out)
+            continue
+        inc = ["-I", str(HERE / "jni_shim"), "-I", str(base / proj)]
+        if name == "conv":
+            fix = OUT / "casefix"
+            fix.mkdir(exist_ok=True)
+            for alias, real in CASE_FIX.items():
+                link = fix / alias
+                if not link.exists():
+                    link.symlink_to(base / proj / real)
+            inc += ["-I", str(fix)]
+        cmd = [NVCC, "-std=c++14", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-shared",
+               "-Xcompiler", "-fPIC", "-w", *inc, "-o", str(out), str(HERE / wrap)]
+        print(" ".join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+        built.append(out)
+    return built
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--conv", action="store_true", help="also build Cuda_conv3D (about 25 minutes)")
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    names = ["matmul", "bmm"] + (["conv"] if a.conv else [])
+    for p in build(Path(a.reference), names, a.force):
+        print(p)

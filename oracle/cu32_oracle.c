@@ -1,0 +1,227 @@
+/* CPU oracle for the Cu32 dense-contraction path.  TEST INFRASTRUCTURE ONLY: nothing in
+ * the product library links, imports or calls this file; it exists so that tests, the smoke
+ * check and the benchmark's CPU-baseline leg can check and time the reference's algorithm.
+ *
+ * Part 1 restates, loop for loop, the CPU check routines the reference uses to validate
+ * its GPU kernels (they are the only CPU implementation of this path in the reference):
+ *   multiply / multiplyT1 / multiplyT2   engine-cuda-base/Cuda_matMul/Cuda_matMul/test.cuh:60-82
+ *   bmm / bmmT1 / bmmT2                  engine-cuda-base/Cuda_batchMatMul/Cuda_batchMatMul/test.cuh:97-140
+ *   CONV_3D_NAIVE (float accumulator)    engine-cuda-base/Cuda_conv3D/Cuda_conv3D/test.cuh:171-200
+ *   CONV_3D_img2col (double accumulator) engine-cuda-base/Cuda_conv3D/Cuda_conv3D/test.cuh:203-243
+ *   samePercent (relative, thresholded)  Cuda_matMul/test.cuh:48-58, Cuda_conv3D/test.cuh:38-57,
+ *                                        Cuda_batchMatMul/test.cuh:69-89
+ *   buf_summary (Kahan)                  Cuda_matMul/Cuda_matMul/SKbufsum.cuh:29-68
+ *   filter remode W[OC,FH,FW,IC] -> CW[FH,FW,IC,OC]   Cuda_conv3D/conv3D_kernel_remode_V1.cuh:50-196
+ * Loop order and accumulation type follow the reference exactly (k outermost, FP32 "+=" into
+ * C), so that on the same inputs the results are bit-identical to the reference routines
+ * compiled with the same compiler flags; oracle/build_ref.py builds those routines from the
+ * reference tree and tests/test_oracle.py checks the identity.
+ *
+ * Part 2 holds FP64-accumulating versions of the same contractions; they are the accuracy
+ * oracle the GPU results are measured against.
+ *
+ * Pinning status: pinned against the reference's own routines compiled here (see above) and
+ * against hand-computed known answers in tests/golden/; the reference ships no golden vectors.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+
+/* ------------------------------------------------------------------ part 1: reference loops */
+
+/* C[N,M] += A[N,K] * B[K,M]   (caller zeroes C first, as the reference's newPtr does) */
+void oracle_multiply(const float* A, const float* B, float* C, int N, int M, int K) {
+  for (int k = 0; k < K; k++)
+    for (int i = 0; i < N; i++)
+      for (int j = 0; j < M; j++)
+        C[(size_t)i * M + j] += A[(size_t)i * K + k] * B[(size_t)k * M + j];
+}
+
+/* C[N,M] += A[K,N]^T * B[K,M] */
+void oracle_multiplyT1(const float* A, const float* B, float* C, int N, int M, int K) {
+  for (int k = 0; k < K; k++)
+    for (int i = 0; i < N; i++)
+      for (int j = 0; j < M; j++)
+        C[(size_t)i * M + j] += A[(size_t)k * N + i] * B[(size_t)k * M + j];
+}
+
+/* C[N,M] += A[N,K] * B[M,K]^T */
+void oracle_multiplyT2(const float* A, const float* B, float* C, int N, int M, int K) {
+  for (int k = 0; k < K; k++)
+    for (int i = 0; i < N; i++)
+      for (int j = 0; j < M; j++)
+        C[(size_t)i * M + j] += A[(size_t)i * K + k] * B[(size_t)j * K + k];
+}
+
+/* C[b][N,CM] += A[b][N,AK] * B[b][BK,CM], reduction over BK */
+void oracle_bmm(const float* A, const float* B, float* C, int Batch, int N, int CM, int BK, int AK) {
+  for (int b = 0; b < Batch; b++)
+    for (int k = 0; k < BK; k++)
+      for (int i = 0; i < N; i++)
+        for (int j = 0; j < CM; j++)
+          C[((size_t)b * N + i) * CM + j] +=
+              A[((size_t)b * N + i) * AK + k] * B[((size_t)b * BK + k) * CM + j];
+}
+
+/* C[b][CN,CM] += A[b][K,AN]^T * B[b][K,CM] */
+void oracle_bmmT1(const float* A, const float* B, float* C, int Batch, int CN, int AN, int CM, int K) {
+  for (int b = 0; b < Batch; b++)
+    for (int k = 0; k < K; k++)
+      for (int i = 0; i < CN; i++)
+        for (int j = 0; j < CM; j++)
+          C[((size_t)b * CN + i) * CM + j] +=
+              A[((size_t)b * K + k) * AN + i] * B[((size_t)b * K + k) * CM + j];
+}
+
+/* C[b][N,CM] (columns < BM) += A[b][N,K] * B[b][BM,K]^T */
+void oracle_bmmT2(const float* A, const float* B, float* C, int Batch, int N, int CM, int BM, int K) {
+  for (int b = 0; b < Batch; b++)
+    for (int k = 0; k < K; k++)
+      for (int i = 0; i < N; i++)
+        for (int j = 0; j < BM; j++)
+          C[((size_t)b * N + i) * CM + j] +=
+              A[((size_t)b * N + i) * K + k] * B[((size_t)b * BM + j) * K + k];
+}
+
+#define X4(n, h, w, c) X[(((size_t)(n) * IH + (h)) * IW + (w)) * IC + (c)]
+#define W4(o, h, w, c) W[(((size_t)(o) * FH + (h)) * FW + (w)) * IC + (c)]
+#define Y4(n, h, w, c) Y[(((size_t)(n) * OH + (h)) * OW + (w)) * OC + (c)]
+
+/* Direct convolution, FP32 accumulator, taps outside the image skipped. */
+void oracle_conv3D_naive(const float* X, int IH, int IW, const float* W, int FH, int FW, float* Y,
+                         int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  for (int oc = 0; oc < OC; oc++)
+    for (int n = 0; n < N; n++) {
+      int ih_s, iw_s, oh, ow;
+      for (ih_s = -ph, oh = 0; ih_s <= (IH + ph - FH); ih_s += sh, oh++)
+        for (iw_s = -pw, ow = 0; iw_s <= (IW + pw - FW); iw_s += sw, ow++) {
+          float v = 0;
+          for (int fh = 0; fh < FH; fh++)
+            for (int fw = 0; fw < FW; fw++)
+              for (int ic = 0; ic < IC; ic++) {
+                int ih = ih_s + fh, iw = iw_s + fw;
+                if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+                v += X4(n, ih, iw, ic) * W4(oc, fh, fw, ic);
+              }
+          Y4(n, oh, ow, oc) = v;
+        }
+    }
+}
+
+/* The same convolution walked as the implicit GEMM (GN = OC, GM = N*OH*OW, GK = FH*FW*IC)
+ * with a double accumulator. */
+void oracle_conv3D_img2col(const float* X, int IH, int IW, const float* W, int FH, int FW, float* Y,
+                           int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  int GN = OC, GM = N * OH * OW, GK = FH * FW * IC;
+  for (int i = 0; i < GN; i++) {
+    int oc = i;
+    for (int j = 0; j < GM; j++) {
+      int n = j / (OH * OW), j_res = j % (OH * OW);
+      int oh = j_res / OW, ow = j_res % OW;
+      double v = 0;
+      for (int k = 0; k < GK; k++) {
+        int fh = k / (FW * IC), k_res = k % (FW * IC);
+        int fw = k_res / IC, ic = k_res % IC;
+        int ih = oh * sh - ph + fh, iw = ow * sw - pw + fw;
+        if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+        v += X4(n, ih, iw, ic) * W4(oc, fh, fw, ic);
+      }
+      Y4(n, oh, ow, oc) = (float)v;
+    }
+  }
+}
+
+/* Fraction of elements with |a-b| / |a+b| < threshold (equal elements count as same). */
+float oracle_samePercent_relative(const float* a, const float* b, int length, float threshold) {
+  int sum = 0;
+  for (int i = 0; i < length; i++) {
+    if (a[i] == b[i]) { sum++; continue; }
+    float dif = fabsf((a[i] - b[i]) / (a[i] + b[i]));
+    if (dif < threshold) sum++;
+  }
+  return 1.0f * sum / length;
+}
+
+/* Fraction of elements with |a-b| < threshold (the batched tests' absolute criterion). */
+float oracle_samePercent_absolute(const float* a, const float* b, int length, float threshold) {
+  int sum = 0;
+  for (int i = 0; i < length; i++) {
+    if (a[i] == b[i]) { sum++; continue; }
+    if (fabsf(a[i] - b[i]) < threshold) sum++;
+  }
+  return 1.0f * sum / length;
+}
+
+float oracle_zeroPercent(const float* a, int length) {
+  int sum = 0;
+  for (int i = 0; i < length; i++)
+    if (a[i] == 0) sum++;
+  return 1.0f * sum / length;
+}
+
+/* C += sum_p Cbuf[p], Kahan-compensated in FP32, element by element. */
+void oracle_buf_summary(const float* Cbuf, float* C, int part, int sizeC) {
+  for (int i = 0; i < sizeC; i++) {
+    volatile float v = C[i], c = 0.0f;
+    for (int p = 0; p < part; p++) {
+      volatile float vbuf = Cbuf[(size_t)p * sizeC + i];
+      vbuf -= c;
+      volatile float t = v + vbuf;
+      volatile float d = t - v;
+      c = d - vbuf;
+      v = t;
+    }
+    C[i] = v;
+  }
+}
+
+/* CW[fh,fw,ic,oc] = W[oc,fh,fw,ic] */
+void oracle_kernel_remode(const float* W, float* CW, int FH, int FW, int OC, int IC) {
+  size_t G = (size_t)FH * FW * IC;
+  for (int oc = 0; oc < OC; oc++)
+    for (size_t g = 0; g < G; g++) CW[g * OC + oc] = W[(size_t)oc * G + g];
+}
+
+/* ------------------------------------------------------------------ part 2: FP64 oracle */
+
+/* Row-range versions so callers can run slices on several host threads. */
+void oracle_multiply_f64(const float* A, const float* B, double* C, int N, int M, int K, int form,
+                         int row_begin, int row_end) {
+  /* form 0: A[N,K] B[K,M]; 1: A[K,N]^T B[K,M]; 2: A[N,K] B[M,K]^T.  C is [N,M] doubles. */
+  for (int i = row_begin; i < row_end; i++) {
+    double* c = C + (size_t)i * M;
+    for (int j = 0; j < M; j++) c[j] = 0.0;
+    for (int k = 0; k < K; k++) {
+      double a = form == 1 ? (double)A[(size_t)k * N + i] : (double)A[(size_t)i * K + k];
+      if (form == 2) {
+        for (int j = 0; j < M; j++) c[j] += a * (double)B[(size_t)j * K + k];
+      } else {
+        const float* b = B + (size_t)k * M;
+        for (int j = 0; j < M; j++) c[j] += a * (double)b[j];
+      }
+    }
+  }
+}
+
+void oracle_conv3D_f64(const float* X, int IH, int IW, const float* W, int FH, int FW, double* Y,
+                       int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
+                       int n_begin, int n_end) {
+  for (int n = n_begin; n < n_end; n++)
+    for (int oh = 0; oh < OH; oh++)
+      for (int ow = 0; ow < OW; ow++)
+        for (int oc = 0; oc < OC; oc++) {
+          double v = 0.0;
+          for (int fh = 0; fh < FH; fh++) {
+            int ih = oh * sh - ph + fh;
+            if (ih < 0 || ih >= IH) continue;
+            for (int fw = 0; fw < FW; fw++) {
+              int iw = ow * sw - pw + fw;
+              if (iw < 0 || iw >= IW) continue;
+              const float* x = &X4(n, ih, iw, 0);
+              const float* w = &W4(oc, fh, fw, 0);
+              for (int ic = 0; ic < IC; ic++) v += (double)x[ic] * (double)w[ic];
+            }
+          }
+          Y[(((size_t)n * OH + oh) * OW + ow) * OC + oc] = v;
+        }
+}

@@ -1,0 +1,255 @@
+"""CPU oracle for the Cu32 dense-contraction path (TEST INFRASTRUCTURE ONLY).
+
+Only tests/, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of
+``bench.py`` import this module, and only as the checker or the timed CPU baseline; the
+product library never does.
+
+Three layers:
+  * ``ref_loops``  the reference's CPU check loops restated in C (oracle/cu32_oracle.c),
+                   FP32 accumulation in the reference's loop order;
+  * ``f64``        FP64 contractions (numpy) — the accuracy oracle;
+  * ``ref_native`` the reference's own routines compiled from the reference tree into
+                   oracle/_ref/ by oracle/build_ref.py, when that build exists.
+Error metrics follow the definitions used throughout the reports:
+  frob  = ||C - C64||_F / ||C64||_F
+  elem  = max_i |C_i - C64_i| / max(|C64_i|, tau),  tau = 1e-3 * rms(C64)
+  same% = share of elements with |a-b|/|a+b| < thr  (the reference's own gate)
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from ctypes import POINTER, c_double, c_float, c_int
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+SRC = HERE / "cu32_oracle.c"
+LIB = HERE / "libcu32_oracle.so"
+REF_DIR = HERE / "_ref"
+
+_lib = None
+_fp = POINTER(c_float)
+_dp = POINTER(c_double)
+
+
+def build(force: bool = False) -> Path:
+    """Compile cu32_oracle.c with gcc -O2 (no vectorisation flags, like the reference's loops)."""
+    if force or not LIB.exists() or LIB.stat().st_mtime < SRC.stat().st_mtime:
+        subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-o", str(LIB), str(SRC), "-lm"], check=True)
+    return LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(str(LIB))
+        _lib.oracle_samePercent_relative.restype = c_float
+        _lib.oracle_samePercent_absolute.restype = c_float
+        _lib.oracle_zeroPercent.restype = c_float
+    return _lib
+
+
+def _f(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_fp)
+
+
+def _d(a: np.ndarray):
+    assert a.dtype == np.float64 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_dp)
+
+
+def _c32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+# ------------------------------------------------------------------ reference loops (FP32)
+class ref_loops:
+    """The reference's CPU check loops (restated).  Letters as in the reference."""
+
+    @staticmethod
+    def multiply(A, B, N, M, K):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((N, M), np.float32)
+        lib().oracle_multiply(_f(A), _f(B), _f(C), N, M, K)
+        return C
+
+    @staticmethod
+    def multiplyT1(A, B, N, M, K):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((N, M), np.float32)
+        lib().oracle_multiplyT1(_f(A), _f(B), _f(C), N, M, K)
+        return C
+
+    @staticmethod
+    def multiplyT2(A, B, N, M, K):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((N, M), np.float32)
+        lib().oracle_multiplyT2(_f(A), _f(B), _f(C), N, M, K)
+        return C
+
+    @staticmethod
+    def bmm(A, B, Batch, N, CM, BK, AK):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((Batch, N, CM), np.float32)
+        lib().oracle_bmm(_f(A), _f(B), _f(C), Batch, N, CM, BK, AK)
+        return C
+
+    @staticmethod
+    def bmmT1(A, B, Batch, CN, AN, CM, K):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((Batch, CN, CM), np.float32)
+        lib().oracle_bmmT1(_f(A), _f(B), _f(C), Batch, CN, AN, CM, K)
+        return C
+
+    @staticmethod
+    def bmmT2(A, B, Batch, N, CM, BM, K):
+        A, B = _c32(A), _c32(B)
+        C = np.zeros((Batch, N, CM), np.float32)
+        lib().oracle_bmmT2(_f(A), _f(B), _f(C), Batch, N, CM, BM, K)
+        return C
+
+    @staticmethod
+    def conv3D_naive(X, W, OH, OW, sh, sw, ph, pw):
+        X, W = _c32(X), _c32(W)
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, _ = W.shape
+        Y = np.zeros((N, OH, OW, OC), np.float32)
+        lib().oracle_conv3D_naive(_f(X), IH, IW, _f(W), FH, FW, _f(Y), OH, OW, N, IC, OC, sh, sw, ph, pw)
+        return Y
+
+    @staticmethod
+    def conv3D_img2col(X, W, OH, OW, sh, sw, ph, pw):
+        X, W = _c32(X), _c32(W)
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, _ = W.shape
+        Y = np.zeros((N, OH, OW, OC), np.float32)
+        lib().oracle_conv3D_img2col(_f(X), IH, IW, _f(W), FH, FW, _f(Y), OH, OW, N, IC, OC, sh, sw, ph, pw)
+        return Y
+
+    @staticmethod
+    def buf_summary(Cbuf, C, part, sizeC):
+        Cbuf, C = _c32(Cbuf), _c32(C).copy()
+        lib().oracle_buf_summary(_f(Cbuf), _f(C), part, sizeC)
+        return C
+
+    @staticmethod
+    def kernel_remode(W):
+        W = _c32(W)
+        OC, FH, FW, IC = W.shape
+        CW = np.zeros((FH, FW, IC, OC), np.float32)
+        lib().oracle_kernel_remode(_f(W), _f(CW), FH, FW, OC, IC)
+        return CW
+
+
+def same_percent(a, b, threshold=1e-5, absolute=False) -> float:
+    a, b = _c32(a).ravel(), _c32(b).ravel()
+    fn = lib().oracle_samePercent_absolute if absolute else lib().oracle_samePercent_relative
+    return float(fn(_f(a), _f(b), a.size, c_float(threshold)))
+
+
+def zero_percent(a) -> float:
+    a = _c32(a).ravel()
+    return float(lib().oracle_zeroPercent(_f(a), a.size))
+
+
+# ------------------------------------------------------------------ FP64 oracle
+class f64:
+    """FP64 contractions of FP32 inputs; results are float64 arrays."""
+
+    @staticmethod
+    def matMul(A, B):
+        return np.asarray(A, np.float64) @ np.asarray(B, np.float64)
+
+    @staticmethod
+    def matMulT1(A, B):
+        return np.asarray(A, np.float64).T @ np.asarray(B, np.float64)
+
+    @staticmethod
+    def matMulT2(A, B):
+        return np.asarray(A, np.float64) @ np.asarray(B, np.float64).T
+
+    @staticmethod
+    def batchMatMul(A, B, BK=None):
+        A, B = np.asarray(A, np.float64), np.asarray(B, np.float64)
+        if BK is not None:
+            A = A[:, :, :BK]
+        return np.matmul(A, B)
+
+    @staticmethod
+    def batchMatMulT1(A, B, CN=None):
+        A, B = np.asarray(A, np.float64), np.asarray(B, np.float64)
+        if CN is not None:
+            A = A[:, :, :CN]
+        return np.matmul(A.transpose(0, 2, 1), B)
+
+    @staticmethod
+    def batchMatMulT2(A, B, CM=None):
+        A, B = np.asarray(A, np.float64), np.asarray(B, np.float64)
+        C = np.matmul(A, B.transpose(0, 2, 1))
+        if CM is not None and CM > C.shape[2]:
+            C = np.concatenate([C, np.zeros(C.shape[:2] + (CM - C.shape[2],))], axis=2)
+        return C
+
+    @staticmethod
+    def conv3D(X, W, OH, OW, sh, sw, ph, pw, n_begin=0, n_end=None):
+        """Forward convolution, NHWC / OCxFHxFWxIC, zero padding, via im2col in FP64."""
+        X, W = np.asarray(X, np.float64), np.asarray(W, np.float64)
+        N, IH, IW, IC = X.shape
+        OC, FH, FW, _ = W.shape
+        n_end = N if n_end is None else n_end
+        Xs = X[n_begin:n_end]
+        # pad so that every tap of every output position exists
+        need_h = (OH - 1) * sh + FH
+        need_w = (OW - 1) * sw + FW
+        Xp = np.zeros((Xs.shape[0], max(need_h, IH + 2 * ph), max(need_w, IW + 2 * pw), IC))
+        Xp[:, ph:ph + IH, pw:pw + IW, :] = Xs
+        Y = np.zeros((Xs.shape[0], OH, OW, OC))
+        for fh in range(FH):
+            for fw in range(FW):
+                patch = Xp[:, fh:fh + (OH - 1) * sh + 1:sh, fw:fw + (OW - 1) * sw + 1:sw, :]
+                Y += patch @ W[:, fh, fw, :].T
+        return Y
+
+
+# ------------------------------------------------------------------ metrics
+def frob_rel(C, C64) -> float:
+    C64 = np.asarray(C64, np.float64)
+    d = np.asarray(C, np.float64) - C64
+    return float(np.linalg.norm(d.ravel()) / max(np.linalg.norm(C64.ravel()), 1e-300))
+
+
+def elem_rel(C, C64, tau_factor: float = 1e-3) -> float:
+    C64 = np.asarray(C64, np.float64)
+    d = np.abs(np.asarray(C, np.float64) - C64)
+    rms = float(np.sqrt(np.mean(C64 * C64)))
+    tau = tau_factor * rms if rms > 0 else 1.0
+    return float(np.max(d / np.maximum(np.abs(C64), tau)))
+
+
+def report(C, C64) -> dict:
+    C64 = np.asarray(C64, np.float64)
+    d = np.abs(np.asarray(C, np.float64) - C64)
+    nz = np.abs(C64) > 0
+    rel = d[nz] / np.abs(C64[nz]) if nz.any() else np.zeros(1)
+    return {"frob": frob_rel(C, C64), "elem": elem_rel(C, C64),
+            "rel_p999": float(np.quantile(rel, 0.999)) if rel.size else 0.0}
+
+
+# ------------------------------------------------------------------ reference's own routines
+def ref_native(name: str):
+    """ctypes handle on oracle/_ref/libref_<name>.so ('matmul', 'bmm', 'conv'), or None if
+    that build is absent (it needs the reference tree; see oracle/build_ref.py)."""
+    p = REF_DIR / f"libref_{name}.so"
+    if not p.exists():
+        return None
+    try:
+        l = ctypes.CDLL(str(p))
+    except OSError:
+        return None
+    if hasattr(l, "ref_cpu_samePercent"):
+        l.ref_cpu_samePercent.restype = c_float
+    return l

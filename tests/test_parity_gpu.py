@@ -1,0 +1,350 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle.
+
+Tolerances (FP32-accurate entry points), against the FP64 oracle:
+    relative Frobenius error   <= 1e-6
+    elementwise relative error <= 1e-4   (denominator floored at 1e-3 * rms of the oracle)
+and the reference's own acceptance gate against its FP32 CPU loops:
+    >= 99.9 % of elements within |a-b|/|a+b| < 1e-5          (Cuda_matMul/test.cuh:48-58, :328)
+The TF32 fast mode (`_mma` entry points) has its own looser tolerance: frob <= 1e-3, elem <= 5e-3.
+Bandwidth kernels (filter remode, split-K buffer summation) are bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+FROB_TOL, ELEM_TOL = 1e-6, 1e-4
+FAST_FROB_TOL, FAST_ELEM_TOL = 1e-3, 5e-3
+
+
+def assert_accurate(O, C, C64, what=""):
+    assert np.isfinite(C).all(), f"{what}: non-finite output (unwritten element?)"
+    rep = O.report(C, C64)
+    assert rep["frob"] <= FROB_TOL and rep["elem"] <= ELEM_TOL, f"{what}: {rep}"
+    return rep
+
+
+# ------------------------------------------------------------------ golden fixtures
+def test_golden_matmul(pkg, O, cuda, golden):
+    data = np.load(golden.HERE / "golden_matmul_bmm.npz")
+    for name, (kind, N, M, K) in golden.MATMUL_CASES.items():
+        A, B = golden.golden_inputs(name, golden.matmul_shapes(kind, N, M, K))
+        C = G.matmul(pkg, kind, A, B, N, M, K)
+        assert O.same_percent(C, data[name], 1e-5) >= 0.999, name
+        assert_accurate(O, C, G.f64_matmul(O, kind, A, B), name)
+
+
+def test_golden_bmm(pkg, O, cuda, golden):
+    data = np.load(golden.HERE / "golden_matmul_bmm.npz")
+    bm = pkg.cu32.Cuda_batchMatMul
+    for name, (kind, Batch, d0, d1, d2, d3) in golden.BMM_CASES.items():
+        shapes, cshape = golden.bmm_shapes(kind, Batch, d0, d1, d2, d3)
+        A, B = golden.golden_inputs(name, shapes)
+        dA, dB = G.dev(A), G.dev(B)
+        out = G.Out(int(np.prod(cshape)))
+        fn = {"AB": bm.batchMatMul, "T1": bm.batchMatMulT1, "T2": bm.batchMatMulT2}[kind]
+        fn([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, d0, d1, d2, d3)
+        C = out.host(cshape)
+        G.check_status(pkg)
+        assert np.isfinite(C).all(), name
+        assert O.same_percent(C, data[name], 1e-5) >= 0.999, name
+        # the batched tests of the reference use an absolute 1e-2 criterion (Cuda_batchMatMul/test.cuh:69-89)
+        assert O.same_percent(C, data[name], 1e-2, absolute=True) == 1.0, name
+        if kind == "T2":  # pad columns BM..CM-1 come out zero
+            assert np.all(C[:, :, d2:] == 0), name
+
+
+def test_golden_conv(pkg, O, cuda, golden):
+    path = golden.HERE / "golden_conv.npz"
+    if not path.exists():
+        pytest.skip("conv fixtures not generated")
+    data = np.load(path)
+    for name, (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw) in golden.CONV_CASES.items():
+        X, W = golden.golden_inputs(name, [(N, IH, IW, IC), (OC, FH, FW, IC)])
+        Y = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
+        # the reference's conv gate: relative 1e-3 on >= 99 % and identical zero share (Cuda_conv3D/test.cuh:38-57, :913)
+        assert O.same_percent(Y, data[name + "/img2col"], 1e-3) >= 0.99, name
+        assert O.same_percent(Y, data[name + "/naive"], 1e-3) >= 0.99, name
+        assert O.zero_percent(Y) == O.zero_percent(data[name + "/img2col"]), name
+
+
+# ------------------------------------------------------------------ matMul family
+SHAPES = [
+    (4, 4, 4), (4, 8, 36), (8, 4, 32), (128, 128, 32), (128, 128, 64), (132, 124, 100), (256, 256, 256),
+    (60, 516, 132), (516, 60, 128), (300, 260, 516), (1024, 64, 96), (64, 1024, 40), (388, 392, 1028),
+]
+
+
+@pytest.mark.parametrize("form", ["AB", "T1", "T2"])
+def test_matmul_shapes(pkg, O, cuda, form):
+    for i, (N, M, K) in enumerate(SHAPES):
+        sa, sb = G.mm_shapes(form, N, M, K)
+        A, B = G.rand_pm1(sa, 100 + i), G.rand_pm1(sb, 200 + i)
+        C = G.matmul(pkg, form, A, B, N, M, K)
+        assert_accurate(O, C, G.f64_matmul(O, form, A, B), f"{form} {N}x{M}x{K}")
+        if N * M * K <= 40e6:
+            assert O.same_percent(C, G.ref_matmul(O, form, A, B, N, M, K), 1e-5) >= 0.999
+
+
+def test_matmul_remainder_sweep(pkg, O, cuda):
+    """A slice of the reference's exhaustive sweep (n, m in 1..255 padded to 4, k around 128 and
+    512: Cuda_matMul_test.java:135-141), subsampled to keep the run short."""
+    rng = np.random.default_rng(1)
+    for _ in range(24):
+        N = int(rng.integers(1, 64)) * 4
+        M = int(rng.integers(1, 64)) * 4
+        K = int(rng.choice([128, 132, 512, 516]))
+        form = ["AB", "T1", "T2"][int(rng.integers(0, 3))]
+        sa, sb = G.mm_shapes(form, N, M, K)
+        A, B = rng.random(sa, dtype=np.float32), rng.random(sb, dtype=np.float32)  # [0,1) like the reference tests
+        C = G.matmul(pkg, form, A, B, N, M, K)
+        assert_accurate(O, C, G.f64_matmul(O, form, A, B), f"{form} {N}x{M}x{K}")
+        assert O.same_percent(C, G.ref_matmul(O, form, A, B, N, M, K), 1e-5) >= 0.999
+
+
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4])
+def test_every_tile_configuration(pkg, O, cuda, tile):
+    pkg.cu32.tune("tile", tile)
+    for form in ("AB", "T1", "T2"):
+        for (N, M, K) in [(256, 256, 128), (520, 772, 200), (132, 68, 64)]:
+            sa, sb = G.mm_shapes(form, N, M, K)
+            A, B = G.rand_pm1(sa, 7), G.rand_pm1(sb, 8)
+            C = G.matmul(pkg, form, A, B, N, M, K)
+            assert_accurate(O, C, G.f64_matmul(O, form, A, B), f"tile {tile} {form} {N}x{M}x{K}")
+
+
+@pytest.mark.parametrize("kc", [1, 2, 3, 8, 1000])
+def test_chunk_lengths(pkg, O, cuda, kc):
+    """Any chunk length gives the same product (accuracy bound checked at moderate K)."""
+    pkg.cu32.tune("kc", kc)
+    N, M, K = 256, 384, 1000
+    A, B = G.rand_pm1((N, K), 1), G.rand_pm1((K, M), 2)
+    C = G.matmul(pkg, "AB", A, B, N, M, K)
+    rep = O.report(C, O.f64.matMul(A, B))
+    assert rep["frob"] <= 1e-5 and np.isfinite(C).all(), rep
+
+
+def test_config1_full_size(pkg, O, cuda):
+    w = pkg.workloads.config1()
+    A, B = w.A.numpy(), w.B.numpy()
+    C = G.matmul(pkg, "AB", A, B, w.N, w.M, w.K)
+    assert_accurate(O, C, O.f64.matMul(A, B), "config 1")
+    assert O.same_percent(C, O.ref_loops.multiply(A, B, w.N, w.M, w.K), 1e-5) >= 0.999
+
+
+@pytest.mark.parametrize("form", ["AB", "T1", "T2"])
+@pytest.mark.parametrize("GZ", [2, 4, 16])
+def test_splitk_protocol(pkg, O, cuda, form, GZ):
+    """slice 0 -> C, slice z -> Cbuf[z-1]; every partial is written (no NaN left), their
+    FP64 sum is the product, and SKbuf_summary leaves the product in C."""
+    N, M, K = 132, 260, 2052
+    sa, sb = G.mm_shapes(form, N, M, K)
+    A, B = G.rand_pm1(sa, 31), G.rand_pm1(sb, 32)
+    C, C0, Cbuf = G.matmul_sk(pkg, form, A, B, N, M, K, GZ)
+    assert np.isfinite(C0).all() and np.isfinite(Cbuf).all()
+    C64 = G.f64_matmul(O, form, A, B)
+    assert O.frob_rel(C0.astype(np.float64) + Cbuf.astype(np.float64).sum(0), C64) <= FROB_TOL
+    assert_accurate(O, C, C64, f"split-K {form} GZ={GZ}")
+    assert np.array_equal(C, O.ref_loops.buf_summary(Cbuf.reshape(GZ - 1, -1), C0.ravel(), GZ - 1, N * M).reshape(N, M))
+
+
+def test_splitk_more_slices_than_kblocks(pkg, O, cuda):
+    N, M, K = 64, 64, 96   # 3 k-blocks, 16 slices: empty slices must write zeros
+    A, B = G.rand_pm1((N, K), 1), G.rand_pm1((K, M), 2)
+    C, C0, Cbuf = G.matmul_sk(pkg, "AB", A, B, N, M, K, 16)
+    assert np.isfinite(Cbuf).all()
+    assert_accurate(O, C, O.f64.matMul(A, B), "split-K with empty slices")
+
+
+def test_engine_split_decision_end_to_end(pkg, O, cuda):
+    """Drive the natives the way CudaFloat32EngineBase.matMulT1 does for a weight-gradient shape."""
+    keep = []
+
+    def malloc(n):
+        t = torch.empty(n, device="cuda")
+        keep.append(t)
+        return t.data_ptr(), t
+    eng = pkg.engine.Cu32Engine(148, malloc, [G.stream()])
+    N, M, K = 256, 128, 16384
+    g = torch.Generator().manual_seed(5)
+    A = torch.randn((K, N), generator=g) * 0.01
+    B = torch.randn((K, M), generator=g) * 0.01
+    dA, dB = A.cuda(), B.cuda()
+    out = G.Out(N * M)
+    gz = eng.matMulT1(out.ptr, dA.data_ptr(), dB.data_ptr(), N, M, K)
+    assert gz > 1
+    C = out.host((N, M))
+    G.check_status(pkg)
+    assert_accurate(O, C, O.f64.matMulT1(A.numpy(), B.numpy()), f"engine matMulT1 gz={gz}")
+
+
+def test_skbuf_summary_bit_exact(pkg, O, cuda):
+    rng = np.random.default_rng(3)
+    for part, size in [(1, 4), (3, 252), (15, 4096), (35, 1028)]:
+        C = rng.standard_normal(size).astype(np.float32)
+        Cbuf = (rng.standard_normal((part, size)) * 10.0 ** rng.integers(-6, 3, (part, 1))).astype(np.float32)
+        dC, dB = G.dev(C), G.dev(Cbuf)
+        pkg.cu32.Cuda_matMul.SKbuf_summary(G.stream(), dB.data_ptr(), dC.data_ptr(), part, size)
+        torch.cuda.synchronize()
+        assert np.array_equal(dC.cpu().numpy(), O.ref_loops.buf_summary(Cbuf, C, part, size))
+
+
+@pytest.mark.parametrize("form", ["AB", "T1", "T2"])
+def test_tf32_fast_mode(pkg, O, cuda, form):
+    N, M, K = 256, 260, 512
+    sa, sb = G.mm_shapes(form, N, M, K)
+    A, B = G.rand_pm1(sa, 41), G.rand_pm1(sb, 42)
+    C = G.matmul(pkg, form, A, B, N, M, K, mma=True)
+    rep = O.report(C, G.f64_matmul(O, form, A, B))
+    assert rep["frob"] <= FAST_FROB_TOL and rep["elem"] <= FAST_ELEM_TOL, rep
+    assert rep["frob"] > 1e-6   # it really is the single-pass mode
+
+
+# ------------------------------------------------------------------ batched family
+def test_batched_forms(pkg, O, cuda):
+    bm = pkg.cu32.Cuda_batchMatMul
+    rng = np.random.default_rng(9)
+    s = [G.stream()]
+    # batchMatMul: N not a multiple of 4, AK > BK (A rows padded)
+    for (Batch, N, M, BK, AK) in [(3, 37, 64, 30, 32), (8, 128, 132, 64, 64), (2, 250, 260, 100, 100), (5, 512, 64, 512, 512)]:
+        A = rng.standard_normal((Batch, N, AK)).astype(np.float32)
+        B = rng.standard_normal((Batch, BK, M)).astype(np.float32)
+        out = G.Out(Batch * N * M)
+        dA, dB = G.dev(A), G.dev(B)
+        for fn in (bm.batchMatMul, bm.batchMatMul_texture):
+            fn(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, M, BK, AK)
+            C = out.host((Batch, N, M))
+            assert_accurate(O, C, O.f64.batchMatMul(A, B, BK), f"bmm {Batch}x{N}x{M}x{BK}")
+    # batchMatMulT1: AN > CN
+    for (Batch, CN, AN, M, K) in [(2, 50, 52, 24, 40), (4, 128, 128, 128, 96), (3, 130, 132, 68, 260)]:
+        A = rng.standard_normal((Batch, K, AN)).astype(np.float32)
+        B = rng.standard_normal((Batch, K, M)).astype(np.float32)
+        out = G.Out(Batch * CN * M)
+        dA, dB = G.dev(A), G.dev(B)
+        bm.batchMatMulT1(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, CN, AN, M, K)
+        C = out.host((Batch, CN, M))
+        assert_accurate(O, C, O.f64.batchMatMulT1(A, B, CN), f"bmmT1 {Batch}x{CN}x{M}x{K}")
+    # batchMatMulT2: CM > BM (pad columns written as zero)
+    for (Batch, N, CM, BM, K) in [(4, 33, 68, 66, 16), (2, 512, 512, 512, 64), (3, 100, 132, 130, 36)]:
+        A = rng.standard_normal((Batch, N, K)).astype(np.float32)
+        B = rng.standard_normal((Batch, BM, K)).astype(np.float32)
+        out = G.Out(Batch * N * CM)
+        dA, dB = G.dev(A), G.dev(B)
+        for fn in (bm.batchMatMulT2, bm.batchMatMulT2_texture):
+            fn(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, CM, BM, K)
+            C = out.host((Batch, N, CM))
+            assert_accurate(O, C, O.f64.batchMatMulT2(A, B, CM), f"bmmT2 {Batch}x{N}x{BM}x{K}")
+            assert np.all(C[:, :, BM:] == 0)
+    G.check_status(pkg)
+
+
+def test_attention_shaped_pair_reduced(pkg, O, cuda):
+    """Config 3 at batch 16: S = Q K^T, P = softmax rows (FP32, as an input), O = P V."""
+    w = pkg.workloads.config3(Batch=16)
+    bm = pkg.cu32.Cuda_batchMatMul
+    s = [G.stream()]
+    dQ, dK, dV = w.Q.cuda(), w.K.cuda(), w.V.cuda()
+    S = G.Out(w.Batch * w.L * w.L)
+    bm.batchMatMulT2(s, 1, dQ.data_ptr(), dK.data_ptr(), S.ptr, w.Batch, w.L, w.L, w.L, w.D)
+    Sh = S.host((w.Batch, w.L, w.L))
+    assert_accurate(O, Sh, O.f64.batchMatMulT2(w.Q.numpy(), w.K.numpy()), "Q K^T")
+    P = pkg.workloads.softmax_rows(torch.from_numpy(Sh), w.D)
+    dP = P.cuda()
+    Oo = G.Out(w.Batch * w.L * w.D)
+    bm.batchMatMul(s, 1, dP.data_ptr(), dV.data_ptr(), Oo.ptr, w.Batch, w.L, w.D, w.L, w.L)
+    assert_accurate(O, Oo.host((w.Batch, w.L, w.D)), O.f64.batchMatMul(P.numpy(), w.V.numpy()), "P V")
+    G.check_status(pkg)
+
+
+# ------------------------------------------------------------------ convolution
+CONV_CASES = [
+    # N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw
+    (4, 9, 9, 8, 12, 3, 3, 1, 1, 1, 1),
+    (4, 28, 28, 64, 64, 3, 3, 1, 1, 1, 1),
+    (8, 14, 14, 32, 256, 3, 3, 1, 1, 1, 1),
+    (4, 16, 16, 36, 40, 3, 3, 2, 2, 1, 1),
+    (4, 11, 10, 4, 8, 5, 3, 2, 2, 2, 1),
+    (4, 32, 32, 16, 32, 7, 7, 2, 2, 3, 3),
+    (4, 12, 12, 128, 132, 1, 1, 1, 1, 0, 0),
+    (4, 10, 10, 8, 16, 3, 3, 1, 1, 0, 0),
+    (4, 8, 8, 256, 64, 2, 2, 2, 2, 0, 0),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_gemmr(pkg, O, cuda, case):
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+    rng = np.random.default_rng(17)
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * np.sqrt(2.0 / (FH * FW * IC))).astype(np.float32)
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    Y64 = O.f64.conv3D(X, W, OH, OW, sh, sw, ph, pw)
+    Y = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
+    assert_accurate(O, Y, Y64, f"conv {case}")
+    if N * OH * OW * OC * FH * FW * IC <= 60e6:
+        assert O.same_percent(Y, O.ref_loops.conv3D_img2col(X, W, OH, OW, sh, sw, ph, pw), 1e-3) >= 0.99
+
+
+def test_conv_entry_point_aliases(pkg, O, cuda):
+    rng = np.random.default_rng(18)
+    X = rng.standard_normal((4, 12, 12, 16)).astype(np.float32)
+    W = rng.standard_normal((24, 3, 3, 16)).astype(np.float32) * 0.1
+    Y64 = O.f64.conv3D(X, W, 12, 12, 1, 1, 1, 1)
+    base = G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, 1, 1)
+    assert_accurate(O, base, Y64, "GemmR")
+    for entry in ("conv3D_GemmR_texture", "conv3D_GemmR_SGM", "conv3D_GemmR_texture_SGM", "conv3D", "conv3D_texture"):
+        assert np.array_equal(G.conv(pkg, entry, X, W, 1, 1, 1, 1), base), entry
+    Ynp = G.conv(pkg, "conv3D_np", X, W, 1, 1, 0, 0)
+    assert_accurate(O, Ynp, O.f64.conv3D(X, W, 10, 10, 1, 1, 0, 0), "conv3D_np")
+    W1 = rng.standard_normal((20, 1, 1, 16)).astype(np.float32)
+    Y1 = O.f64.conv3D(X, W1, 12, 12, 1, 1, 0, 0)
+    for entry in ("conv3D_W1", "conv3D_GemmR_W1", "conv3D_GemmR_W1_SGM"):
+        assert_accurate(O, G.conv(pkg, entry, X, W1, 1, 1, 0, 0), Y1, entry)
+
+
+def test_kernel_remode_bit_exact(pkg, O, cuda):
+    rng = np.random.default_rng(19)
+    for (OC, FH, FW, IC) in [(4, 1, 1, 4), (12, 3, 3, 8), (256, 3, 3, 64), (36, 5, 3, 20), (33, 2, 2, 7)]:
+        W = rng.standard_normal((OC, FH, FW, IC)).astype(np.float32)
+        dW = G.dev(W)
+        out = G.Out(W.size)
+        pkg.cu32.Cuda_conv3D.kernel_remode(G.stream(), dW.data_ptr(), out.ptr, FH, FW, OC, IC)
+        assert np.array_equal(out.host((FH, FW, IC, OC)), O.ref_loops.kernel_remode(W))
+
+
+def test_config4_reduced(pkg, O, cuda):
+    """Config 4 geometry (28x28, 256 -> 256, 3x3 s1 p1) on 8 images."""
+    w = pkg.workloads.config4(N=8)
+    X, W = w.X.numpy(), w.W.numpy()
+    Y = G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, 1, 1)
+    assert_accurate(O, Y, O.f64.conv3D(X, W, 28, 28, 1, 1, 1, 1), "config 4 (8 images)")
+
+
+# ------------------------------------------------------------------ full-size properties
+def test_config2_full_size_sampled_rows_and_checksum(pkg, O, cuda):
+    """8192^3 is too large for a full CPU oracle run inside a test; check (1) 48 sampled rows of
+    C against the FP64 oracle, and (2) the checksum identity C*1 = A*(B*1) over the whole output."""
+    size = 8192
+    for form in ("AB", "T1", "T2"):
+        w = pkg.workloads.config2(form, size)
+        dA, dB = w.A.cuda(), w.B.cuda()
+        dC = torch.empty((size, size), device="cuda")
+        fn = {"AB": pkg.cu32.Cuda_matMul.matMul, "T1": pkg.cu32.Cuda_matMul.matMulT1,
+              "T2": pkg.cu32.Cuda_matMul.matMulT2}[form]
+        fn([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), size, size, size)
+        G.check_status(pkg)
+        rows = np.linspace(0, size - 1, 48).astype(int)
+        A, B = w.A.numpy(), w.B.numpy()
+        Arows = A[:, rows].T if form == "T1" else A[rows]
+        Bm = B.T if form == "T2" else B
+        C64 = Arows.astype(np.float64) @ Bm.astype(np.float64)
+        C = dC[torch.as_tensor(rows, device="cuda")].cpu().numpy()
+        assert_accurate(O, C, C64, f"config 2 {form} sampled rows")
+        rowsum = dC.double().sum(1).cpu().numpy()
+        A64 = (A.T if form == "T1" else A).astype(np.float64)
+        want = A64 @ Bm.astype(np.float64).sum(1)
+        assert np.linalg.norm(rowsum - want) / np.linalg.norm(want) <= 1e-6, form
+        del dA, dB, dC
