@@ -79,17 +79,21 @@ static bool load_driver_entry_points() {
   return g_encode_tiled != nullptr;
 }
 
-// 3-D FP32 map (inner, outer, batch), 128-byte swizzle, zero fill outside the extents.
+// 3-D FP32 map (inner, outer, batch), zero fill outside the extents.  K-major operands
+// (reduction axis innermost) use the plain 128-byte swizzle; MN-major operands use the
+// 128-byte swizzle with 32-byte units, the only one the tensor core reads for 32-bit
+// MN-major tiles.
 static int make_map3(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2,
-                     uint64_t pitch1_floats, uint64_t pitch2_floats, uint32_t b0, uint32_t b1) {
+                     uint64_t pitch1_floats, uint64_t pitch2_floats, uint32_t b0, uint32_t b1,
+                     bool mn_major) {
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {pitch1_floats * 4, pitch2_floats * 4};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? CU32_OK : CU32_E_TENSORMAP;
 }
 
@@ -133,12 +137,12 @@ static int run_gemm(const GemmCall& c) {
   int rc;
   const uint64_t nb = static_cast<uint64_t>(c.batch);
   // A
-  if (c.a_mn) rc = make_map3(&p.tmA, c.A, c.M, c.K, nb, c.lda, c.sA ? c.sA : c.lda * c.K, 32, 32);
-  else        rc = make_map3(&p.tmA, c.A, c.K, c.M, nb, c.lda, c.sA ? c.sA : c.lda * c.M, 32, 128);
+  if (c.a_mn) rc = make_map3(&p.tmA, c.A, c.M, c.K, nb, c.lda, c.sA ? c.sA : c.lda * c.K, 32, 32, true);
+  else        rc = make_map3(&p.tmA, c.A, c.K, c.M, nb, c.lda, c.sA ? c.sA : c.lda * c.M, 32, 128, false);
   if (rc) return rc;
   // B
-  if (c.b_mn) rc = make_map3(&p.tmB, c.B, c.N, c.K, nb, c.ldb, c.sB ? c.sB : c.ldb * c.K, 32, 32);
-  else        rc = make_map3(&p.tmB, c.B, c.K, c.N, nb, c.ldb, c.sB ? c.sB : c.ldb * c.N, 32, bn / ctas);
+  if (c.b_mn) rc = make_map3(&p.tmB, c.B, c.N, c.K, nb, c.ldb, c.sB ? c.sB : c.ldb * c.K, 32, 32, true);
+  else        rc = make_map3(&p.tmB, c.B, c.K, c.N, nb, c.ldb, c.sB ? c.sB : c.ldb * c.N, 32, bn / ctas, false);
   if (rc) return rc;
 
   p.C = c.C;
@@ -165,11 +169,11 @@ static int run_gemm(const GemmCall& c) {
     if (z0 > 0) {  // only reachable for batch > 65535: re-encode the maps at the batch offset
       const float* A2 = c.A + static_cast<long long>(z0) * c.sA;
       const float* B2 = c.B + static_cast<long long>(z0) * c.sB;
-      if (c.a_mn) rc = make_map3(&q.tmA, A2, c.M, c.K, nz, c.lda, c.sA, 32, 32);
-      else        rc = make_map3(&q.tmA, A2, c.K, c.M, nz, c.lda, c.sA, 32, 128);
+      if (c.a_mn) rc = make_map3(&q.tmA, A2, c.M, c.K, nz, c.lda, c.sA, 32, 32, true);
+      else        rc = make_map3(&q.tmA, A2, c.K, c.M, nz, c.lda, c.sA, 32, 128, false);
       if (rc) return rc;
-      if (c.b_mn) rc = make_map3(&q.tmB, B2, c.N, c.K, nz, c.ldb, c.sB, 32, 32);
-      else        rc = make_map3(&q.tmB, B2, c.K, c.N, nz, c.ldb, c.sB, 32, bn / ctas);
+      if (c.b_mn) rc = make_map3(&q.tmB, B2, c.N, c.K, nz, c.ldb, c.sB, 32, 32, true);
+      else        rc = make_map3(&q.tmB, B2, c.K, c.N, nz, c.ldb, c.sB, 32, bn / ctas, false);
       if (rc) return rc;
       q.C = c.C + static_cast<long long>(z0) * c.sC;
     }
@@ -331,7 +335,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
       reinterpret_cast<uint64_t*>(&p.tmA)[1] &= ~(1ULL << 21);
   }
   // Filters W[OC][FH*FW*IC]: reduction axis contiguous.
-  if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas)) return rc;
+  if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas, false)) return rc;
 
   p.C = dY; p.Cbuf = nullptr; p.ldc = OC; p.c_stride = 0;
   p.M = static_cast<int>(GM); p.N = OC;

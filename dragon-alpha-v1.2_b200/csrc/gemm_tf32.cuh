@@ -12,9 +12,11 @@
 //     hi = tf32_round(x)          lo = tf32_round(x - hi)
 // and the product is formed as  lo*hi + hi*lo + hi*hi  on tcgen05.mma kind::tf32
 // (the lo*lo term, below 2^-22 relative, is dropped).  The tensor core
-// accumulates in FP32 inside TMEM for `kc` k-blocks (one "chunk"); drain warps
-// then add the chunk to FP32 register accumulators with round-to-nearest adds,
-// so the length of any in-TMEM accumulation chain is bounded regardless of K.
+// accumulates in FP32 inside TMEM, but truncates the accumulator after every
+// instruction; it is therefore only trusted for `kc` k-blocks (one "chunk"):
+// drain warps then add the chunk to FP32 register accumulators with
+// round-to-nearest adds, so the length of any truncating accumulation chain is
+// bounded regardless of K.
 //
 // Roles inside a CTA of 16 warps:
 //   warp 0        TMA producer      global -> shared (raw FP32 tiles, 128B swizzle)
@@ -254,6 +256,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN, Cfg::B_MN);
       constexpr uint32_t A_LBO = Cfg::A_MN ? 4096u : 16u;
       constexpr uint32_t B_LBO = Cfg::B_MN ? 4096u : 16u;
+      constexpr uint32_t A_SBO = Cfg::A_MN ? 512u : 1024u;
+      constexpr uint32_t B_SBO = Cfg::B_MN ? 512u : 1024u;
+      constexpr uint32_t A_LT = Cfg::A_MN ? SMEM_LAYOUT_SW128_32B : SMEM_LAYOUT_SW128;
+      constexpr uint32_t B_LT = Cfg::B_MN ? SMEM_LAYOUT_SW128_32B : SMEM_LAYOUT_SW128;
       constexpr uint32_t A_KSTEP = Cfg::A_MN ? 1024u : 32u;  // bytes per 8 elements of K
       constexpr uint32_t B_KSTEP = Cfg::B_MN ? 1024u : 32u;
       int buf = 0;
@@ -278,20 +284,27 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
         const uint32_t b_hi = a_hi + Cfg::A_BYTES;
         const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
+        // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
+        // instruction, an error of up to one ulp of the *accumulator*.  Issuing all the
+        // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
+        // fresh chunk is still small, keeps those truncations negligible; only the four
+        // hi*hi instructions then round at full magnitude.
+        if (X3) {
+#pragma unroll
+          for (int j = 0; j < Cfg::BK / 8; ++j) {
+            const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+            const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+            const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+            const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+            umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+            umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+          }
+        }
 #pragma unroll
         for (int j = 0; j < Cfg::BK / 8; ++j) {
-          const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, 1024u);
-          const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, 1024u);
-          const uint32_t first = (chunk_start && j == 0) ? 0u : 1u;
-          if (X3) {
-            const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, 1024u);
-            const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, 1024u);
-            umma_tf32<CTAS>(d, da_lo, db_hi, idesc, first);  // small terms first
-            umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
-            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, 1u);
-          } else {
-            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, first);
-          }
+          const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+          const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+          umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
         }
         // The stage may be refilled once these MMAs have read it.
         umma_commit<CTAS>(smem_u32(&bar_empty[s]));

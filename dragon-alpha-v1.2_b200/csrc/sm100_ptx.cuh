@@ -221,21 +221,27 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
 }
 
 // ---------------------------------------------------------------- descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
+// Shared-memory matrix descriptor for 128-byte-swizzled operand tiles.
 //   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1 (Blackwell)
-//   bits [61,64) layout type = 2 (SWIZZLE_128B)
-// K-major operand  (rows of 32 floats = 128 B): SBO = 1024 (8 rows), LBO unused.
-// MN-major operand (slabs of 32 floats along MN, 128 B per k-row): LBO = byte
-//   distance between consecutive 32-wide MN slabs, SBO = 1024 (8 k-rows).
+//   bits [61,64) layout type: 2 = 128B swizzle of 16-byte units (tile base 1024-byte
+//                aligned), 1 = 128B swizzle of 32-byte units (pattern period 512 bytes)
+// K-major operand (rows of 32 floats = 128 B along K), layout type 2:
+//   SBO = 1024 (8 rows), LBO unused.
+// MN-major 32-bit operand (slabs of 32 floats along MN, one 128 B line per k-row):
+//   the tensor core only accepts the 32-byte-unit swizzle for this case (layout type 1,
+//   TMA swizzle 128B_ATOM_32B); its atom is 32 MN elements x 4 k-rows, so SBO = 512
+//   (next 4 k-rows) and LBO = byte distance between consecutive 32-wide MN slabs.
+constexpr uint32_t SMEM_LAYOUT_SW128 = 2;
+constexpr uint32_t SMEM_LAYOUT_SW128_32B = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(layout_type & 7) << 61;
   return d;
 }
 // Instruction descriptor for kind::tf32: FP32 accumulate, TF32 A and B.

@@ -1,0 +1,139 @@
+"""The Java_* exports, driven through a fake JNIEnv built with ctypes.
+
+A JNIEnv is a pointer to a pointer to a table of function pointers.  The shim uses five
+entries (FindClass 6, Throw 13, NewObjectA 30, GetMethodID 33, GetLongArrayRegion 204 - the
+indices of the JNI specification's function table); the fake fills exactly those, so a call
+through any other slot would crash the test rather than pass silently."""
+import ctypes
+from ctypes import CFUNCTYPE, POINTER, c_char_p, c_int32, c_int64, c_void_p
+
+import numpy as np
+import pytest
+
+
+class FakeJNI:
+    def __init__(self, streams):
+        self.streams = list(streams)
+        self.log = []
+        self.thrown = None
+        table = (c_void_p * 230)()
+        self._keep = []
+
+        def put(idx, proto, fn):
+            cb = proto(fn)
+            self._keep.append(cb)
+            table[idx] = ctypes.cast(cb, c_void_p).value
+
+        def find_class(env, name):
+            self.log.append(("FindClass", name.decode()))
+            return 0x1111
+
+        def get_method_id(env, cls, name, sig):
+            self.log.append(("GetMethodID", cls, name.decode(), sig.decode()))
+            return 0x2222
+
+        def new_object_a(env, cls, mid, args):
+            code = ctypes.cast(args, POINTER(c_int32))[0]   # jvalue.i of the first argument
+            self.log.append(("NewObjectA", cls, mid, code))
+            return 0x3333
+
+        def throw(env, obj):
+            self.thrown = obj
+            self.log.append(("Throw", obj))
+            return 0
+
+        def get_long_array_region(env, arr, start, length, buf):
+            self.log.append(("GetLongArrayRegion", arr, start, length))
+            for i in range(length):
+                buf[i] = self.streams[start + i]
+
+        put(6, CFUNCTYPE(c_void_p, c_void_p, c_char_p), find_class)
+        put(13, CFUNCTYPE(c_int32, c_void_p, c_void_p), throw)
+        put(30, CFUNCTYPE(c_void_p, c_void_p, c_void_p, c_void_p, c_void_p), new_object_a)
+        put(33, CFUNCTYPE(c_void_p, c_void_p, c_void_p, c_char_p, c_char_p), get_method_id)
+        put(204, CFUNCTYPE(None, c_void_p, c_void_p, c_int32, c_int32, POINTER(c_int64)), get_long_array_region)
+        self.table = table
+        self.table_ptr = c_void_p(ctypes.addressof(table))
+        self.env = ctypes.pointer(self.table_ptr)      # JNIEnv* : pointer to pointer to table
+
+
+ARRAY_HANDLE = 0xABCD
+
+
+def _fn(lib, name, argtypes):
+    f = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1" + name)
+    f.argtypes = [c_void_p, c_void_p] + argtypes
+    f.restype = None
+    return f
+
+
+MATMUL_ARGS = [c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32]
+
+
+def test_error_becomes_cuda_exception(pkg):
+    """Argument errors are detected before any CUDA call, so this runs without a GPU: the shim
+    must construct z.dragon.engine.cuda.impl.CudaException(int) and Throw it
+    (reference: Cuda_matMul/JNITool.cuh:9-26)."""
+    lib = pkg.cu32.load()
+    jni = FakeJNI([0])
+    f = _fn(lib, "matMul_matMul", MATMUL_ARGS)
+    f(jni.env, None, ARRAY_HANDLE, 1, 0x10000, 0x10000, 0x10000, 0, 4, 4)   # N = 0
+    assert ("GetLongArrayRegion", ARRAY_HANDLE, 0, 1) in jni.log
+    assert ("FindClass", "z/dragon/engine/cuda/impl/CudaException") in jni.log
+    assert ("GetMethodID", 0x1111, "<init>", "(I)V") in jni.log
+    assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log
+    assert jni.thrown == 0x3333
+    # a stream-array length outside 1..10 is rejected without touching the array
+    jni = FakeJNI([0])
+    f(jni.env, None, ARRAY_HANDLE, 11, 0x10000, 0x10000, 0x10000, 4, 4, 4)
+    assert not any(e[0] == "GetLongArrayRegion" for e in jni.log)
+    assert ("NewObjectA", 0x1111, 0x2222, -3) in jni.log
+    # SKbuf_summary takes a single stream handle, no array
+    g = _fn(lib, "matMul_SKbuf_1summary", [c_int64, c_int64, c_int64, c_int32, c_int32])
+    jni = FakeJNI([0])
+    g(jni.env, None, 0, 0x10000, 0, 3, 8)
+    assert ("NewObjectA", 0x1111, 0x2222, -1) in jni.log
+
+
+@pytest.mark.gpu
+def test_jni_matmul_and_conv_on_gpu(pkg, O, cuda):
+    import gpu_util as G
+    torch = cuda
+    lib = pkg.cu32.load()
+    jni = FakeJNI([G.stream()])
+    N, M, K = 132, 260, 96
+    A, B = G.rand_pm1((N, K), 1), G.rand_pm1((K, M), 2)
+    dA, dB = G.dev(A), G.dev(B)
+    out = G.Out(N * M)
+    _fn(lib, "matMul_matMul", MATMUL_ARGS)(jni.env, None, ARRAY_HANDLE, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, N, M, K)
+    C = out.host((N, M))
+    assert jni.thrown is None
+    rep = O.report(C, O.f64.matMul(A, B))
+    assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, rep
+    # batched, through the JNI symbol
+    Batch, L, D = 3, 64, 32
+    Q = np.random.default_rng(1).standard_normal((Batch, L, D)).astype(np.float32)
+    Kt = np.random.default_rng(2).standard_normal((Batch, L, D)).astype(np.float32)
+    dQ, dK = G.dev(Q), G.dev(Kt)
+    out = G.Out(Batch * L * L)
+    _fn(lib, "batchMatMul_batchMatMulT2", [c_void_p, c_int32, c_int64, c_int64, c_int64] + [c_int32] * 5)(
+        jni.env, None, ARRAY_HANDLE, 1, dQ.data_ptr(), dK.data_ptr(), out.ptr, Batch, L, L, L, D)
+    rep = O.report(out.host((Batch, L, L)), O.f64.batchMatMulT2(Q, Kt))
+    assert rep["frob"] <= 1e-6, rep
+    # convolution: kernel_remode + conv3D_GemmR
+    X = np.random.default_rng(3).standard_normal((4, 8, 8, 16)).astype(np.float32)
+    W = np.random.default_rng(4).standard_normal((8, 3, 3, 16)).astype(np.float32) * 0.1
+    dX, dW = G.dev(X), G.dev(W)
+    dCW = torch.empty(W.size, device="cuda")
+    _fn(lib, "conv3D_kernel_1remode", [c_int64, c_int64, c_int64] + [c_int32] * 4)(
+        jni.env, None, G.stream(), dW.data_ptr(), dCW.data_ptr(), 3, 3, 8, 16)
+    out = G.Out(4 * 8 * 8 * 8)
+    _fn(lib, "conv3D_conv3D_1GemmR", [c_void_p, c_int32, c_int64, c_int32, c_int32, c_int64, c_int64, c_int32, c_int32,
+                                     c_int64] + [c_int32] * 9)(
+        jni.env, None, ARRAY_HANDLE, 1, dX.data_ptr(), 8, 8, dW.data_ptr(), dCW.data_ptr(), 3, 3, out.ptr, 8, 8, 4, 16, 8,
+        1, 1, 1, 1)
+    rep = O.report(out.host((4, 8, 8, 8)), O.f64.conv3D(X, W, 8, 8, 1, 1, 1, 1))
+    assert jni.thrown is None and rep["frob"] <= 1e-6, rep
+    torch.cuda.synchronize()
+    assert np.array_equal(dCW.cpu().numpy().reshape(3, 3, 16, 8), O.ref_loops.kernel_remode(W))
+    G.check_status(pkg)

@@ -136,7 +136,9 @@ def test_metrics(O):
     C64 = np.array([1.0, -2.0, 0.0, 4.0])
     C = C64 + np.array([1e-6, 0, 1e-9, 0])
     assert abs(O.frob_rel(C, C64) - np.sqrt(1e-12 + 1e-18) / np.sqrt(21)) < 1e-12
-    assert O.elem_rel(C, C64) == pytest.approx(1e-6, rel=1e-3)
+    assert O.elem_rel(C, C64, 1e-3) == pytest.approx(1e-6, rel=1e-3)
+    rms = np.sqrt(21 / 4)
+    assert O.elem_rel(C, C64) == pytest.approx(1e-6 / rms, rel=1e-3)   # error on the element 1.0 < rms
     a = np.array([1.0, 2.0, 3.0, 0.0], np.float32)
     b = np.array([1.0, 2.00001, 3.1, 0.0], np.float32)
     assert O.same_percent(a, b, 1e-5) == pytest.approx(0.75)
