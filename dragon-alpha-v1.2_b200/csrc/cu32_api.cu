@@ -112,12 +112,24 @@ struct GemmCall {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static int pick_tile(int M, int N) {
+// Tile choice: estimated time = waves over the 148 SMs x work per CTA / measured per-CTA
+// rate.  The rates are FP32-accurate TFLOP/s measured at 8192^3 on a B200 with every SM
+// busy (the 128x64 figure is scaled from the 128x128 one); padded rows and columns count
+// as work, so narrow outputs pick narrow tiles and small problems pick small tiles.
+static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;
-  (void)M;
-  if (N <= 64) return TILE_1x64;
-  return TILE_1x128;
+  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0};
+  int best = TILE_1x128;
+  double best_t = 1e300;
+  for (int t = 0; t < TILE_COUNT; ++t) {
+    const int ctas = tile_ctas(t), bn = tile_bn(t);
+    const double n_cta = static_cast<double>((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn) * ctas * z;
+    const double waves = static_cast<double>(static_cast<long long>((n_cta + 147.0) / 148.0));
+    const double time = waves * (128.0 * bn) / rate[t];
+    if (time < best_t) { best_t = time; best = t; }
+  }
+  return best;
 }
 
 static int run_gemm(const GemmCall& c) {
@@ -129,7 +141,7 @@ static int run_gemm(const GemmCall& c) {
     return CU32_E_ALIGN;
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
-  const int tile = pick_tile(c.M, c.n_store);
+  const int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -308,7 +320,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
       upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8)
     return CU32_E_GEOMETRY;
 
-  const int tile = pick_tile(static_cast<int>(GM), OC);
+  const int tile = pick_tile(GM, OC, 1);
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
