@@ -557,6 +557,45 @@ int cu32_conv3D_W1(const int64_t* s, int n, const float* X, int IH, int IW, cons
   return conv_any(true, s, n, X, IH, IW, W, 1, 1, Y, IH, IW, N, IC, OC, 1, 1, 0, 0);
 }
 
+// ---- split-K without any allocation
+// Partial products of cu32_matMulT1SK_noalloc live here instead of in a caller buffer.
+// One instance per device that loads the library, held until the process exits.
+static __device__ __align__(256) float g_splitk_scratch[CU32_NOALLOC_SCRATCH_FLOATS];
+
+// In host code the array's name only stands for the symbol; the device address has to be
+// asked for, once per device, while that device is current.
+static float* splitk_scratch_ptr(cudaError_t* err) {
+  static std::atomic<float*> cache[64];
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  float* p = cache[dev & 63].load(std::memory_order_acquire);
+  if (p) return p;
+  float* sym = nullptr;
+  *err = cudaGetSymbolAddress(reinterpret_cast<void**>(&sym), g_splitk_scratch);
+  if (*err != cudaSuccess) return nullptr;
+  cache[dev & 63].store(sym, std::memory_order_release);
+  return sym;
+}
+
+int cu32_matMulT1SK_noalloc(const int64_t* s, int n, int GZ, const float* A, const float* B, float* C,
+                            int N, int M, int K) {
+  cudaStream_t st;
+  if (int rc = check_streams(s, n, &st)) return rc;
+  if (N <= 0 || M <= 0 || K <= 0) return CU32_E_DIM;
+  if (GZ < 1) return CU32_E_ARG;
+  const long long need = static_cast<long long>(GZ - 1) * N * M;
+  if (need > CU32_NOALLOC_SCRATCH_FLOATS) return CU32_E_SCRATCH;
+  cudaError_t e;
+  float* scratch = splitk_scratch_ptr(&e);
+  if (!scratch) return static_cast<int>(e);
+  // Every slice overwrites its whole partial buffer (slices without k-blocks write zeros),
+  // so nothing of an earlier call's contents is ever read.
+  if (int rc = matmul_any(FORM_T1, true, s, n, GZ, A, B, C, GZ > 1 ? scratch : nullptr, N, M, K)) return rc;
+  if (GZ == 1) return CU32_OK;
+  return cu32_SKbuf_summary(s[0], scratch, C, GZ - 1, N * M);
+}
+
 // ---- library control
 int cu32_tune(const char* key, int value) {
   load_env_once();

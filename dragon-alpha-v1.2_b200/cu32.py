@@ -22,6 +22,7 @@ LIB_PATH = _HERE / "libdragon_cu32.so"
 ERROR_NAMES = {
     -1: "CU32_E_NULL", -2: "CU32_E_DIM", -3: "CU32_E_STREAMS", -4: "CU32_E_ALIGN",
     -5: "CU32_E_GEOMETRY", -6: "CU32_E_DRIVER", -7: "CU32_E_TENSORMAP", -8: "CU32_E_ARG",
+    -9: "CU32_E_SCRATCH",
 }
 
 TILE_NAMES = {0: "128x64", 1: "128x128", 2: "128x256", 3: "256x128 pair", 4: "256x256 pair"}
@@ -58,6 +59,7 @@ SIGNATURES = {
     "cu32_matMulT1SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMulT2SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
     "cu32_SKbuf_summary": [c_int64, _fp, _fp, _I, _I],
+    "cu32_matMulT1SK_noalloc": [_sp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMul_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMulT1_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMulT2_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],

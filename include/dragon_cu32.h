@@ -52,6 +52,7 @@ extern "C" {
 #define CU32_E_DRIVER (-6)      /* tensor-map encoder entry point not available in the driver */
 #define CU32_E_TENSORMAP (-7)   /* the driver rejected a tensor map */
 #define CU32_E_ARG (-8)         /* other invalid argument (e.g. GridZ < 1, unknown tuning key) */
+#define CU32_E_SCRATCH (-9)     /* cu32_matMulT1SK_noalloc: (GridZ-1)*N*M exceeds the built-in scratch */
 
 /* ------------------------------------------------------------------ Cuda_matMul
  * Reference: source/engine-cuda-base/Cuda_matMul/Cuda_matMul/A.cu,
@@ -91,6 +92,31 @@ CU32_API int cu32_matMulT1_mma(const int64_t* streams, int length, const float* 
                       float* dC, int N, int M, int K);
 CU32_API int cu32_matMulT2_mma(const int64_t* streams, int length, const float* dA, const float* dB,
                       float* dC, int N, int M, int K);
+
+/* Split-K A^T*B that allocates nothing and needs no partial buffer from the caller.
+ * No counterpart in the reference (its split-K natives always take a caller-allocated Cbuf).
+ *
+ * C[N,M] = A[K,N]^T * B[K,M], K cut into GridZ slices, partials summed (Kahan) into C, all on
+ * streams[0]; the result is the same as cu32_matMulT1SK followed by cu32_SKbuf_summary.
+ *
+ * Who needs it: hosts that cannot obtain device memory at the moment of the call - an engine
+ * whose memory pool has already handed out everything it reserved (the Java engine takes the
+ * partial buffer from such a pool, CudaFloat32EngineBase.java:1565-1568), or a thread that
+ * must not trigger the device-wide synchronisation an allocation or a free implies.  For them
+ * the partial products go to a scratch array compiled into the library:
+ *  - capacity CU32_NOALLOC_SCRATCH_FLOATS floats (16 MiB), i.e. (GridZ-1)*N*M must not exceed
+ *    it (e.g. 512x512 with GridZ <= 17); larger requests return CU32_E_SCRATCH and do nothing;
+ *  - every GPU that loads the library carries the array for the life of the process;
+ *  - the array is shared by all calls on a device: two calls whose GPU work can overlap
+ *    (different streams, no ordering between them) race on it - serialise them.  Its contents
+ *    after a call are the last call's partials; every call overwrites all the floats it reads
+ *    back, so nothing has to be cleared beforehand;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *    make that first call outside any stream capture.
+ * The function calls no allocation or free routine of the CUDA runtime or of any library. */
+#define CU32_NOALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+CU32_API int cu32_matMulT1SK_noalloc(const int64_t* streams, int length, int GridZ, const float* dA,
+                                     const float* dB, float* dC, int N, int M, int K);
 
 /* ------------------------------------------------------------------ Cuda_batchMatMul
  * Reference: source/engine-cuda-base/Cuda_batchMatMul/Cuda_batchMatMul/A.cu. */
