@@ -141,7 +141,7 @@ class Workload:
     """Builds device operands and returns `launch()` (enqueue one step on the current stream),
     flops and algorithmic bytes per launch, plus host buffers for the end-to-end leg."""
 
-    def __init__(self, name, pkg, torch, rank):
+    def __init__(self, name, pkg, torch, rank, size=8192):
         self.name, self.pkg, self.torch = name, pkg, torch
         W = pkg.workloads
         mm, bm, cv = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_batchMatMul, pkg.cu32.Cuda_conv3D
@@ -156,7 +156,7 @@ class Workload:
             elif name == "c5":
                 w = W.config5(K=1048576 // 8)   # one GPU's K shard of the 8-GPU configuration
             else:
-                w = W.config2({"c2_ab": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name])
+                w = W.config2({"c2_ab": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name], size)
             self.hosts = [w.A.pin_memory(), w.B.pin_memory()]
             self.dev_in = [torch.empty_like(h, device="cuda") for h in self.hosts]
             for d, h in zip(self.dev_in, self.hosts):
@@ -267,6 +267,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_ab")
+    ap.add_argument("--size", type=int, default=8192, help="edge of the c2_* cubes (profiling on a smaller case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
@@ -311,7 +312,7 @@ def main():
     pkg.cu32.load()
     pk = peaks()
 
-    wl = Workload(a.workload, pkg, torch, rank)
+    wl = Workload(a.workload, pkg, torch, rank, a.size)
     for _ in range(a.warmup):
         wl.launch()
     st = pkg.cu32.read_status()
