@@ -173,28 +173,13 @@ static int run_gemm(const GemmCall& c) {
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
 
-  // blockIdx.z carries the batch index or the split-K slice; at most 65535 per launch.
+  // Batches (or split-K slices) are folded into the kernel's tile index.
   const int zs = c.gz > 1 ? c.gz : c.batch;
-  for (int z0 = 0; z0 < zs; z0 += 65535) {
-    const int nz = zs - z0 < 65535 ? zs - z0 : 65535;
-    GemmParams q = p;
-    if (z0 > 0) {  // only reachable for batch > 65535: re-encode the maps at the batch offset
-      const float* A2 = c.A + static_cast<long long>(z0) * c.sA;
-      const float* B2 = c.B + static_cast<long long>(z0) * c.sB;
-      if (c.a_mn) rc = make_map3(&q.tmA, A2, c.M, c.K, nz, c.lda, c.sA, 32, 32, true);
-      else        rc = make_map3(&q.tmA, A2, c.K, c.M, nz, c.lda, c.sA, 32, 128, false);
-      if (rc) return rc;
-      if (c.b_mn) rc = make_map3(&q.tmB, B2, c.N, c.K, nz, c.ldb, c.sB, 32, 32, true);
-      else        rc = make_map3(&q.tmB, B2, c.K, c.N, nz, c.ldb, c.sB, 32, bn / ctas, false);
-      if (rc) return rc;
-      q.C = c.C + static_cast<long long>(z0) * c.sC;
-    }
-    if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, q, nz, c.stream);
-    else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, q, nz, c.stream);
-    else if (!c.a_mn)           e = launch_gemm_kk(tile, c.x3, false, q, nz, c.stream);
-    else return CU32_E_ARG;
-    if (e != cudaSuccess) return static_cast<int>(e);
-  }
+  if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
+  else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, p, zs, c.stream);
+  else if (!c.a_mn)           e = launch_gemm_kk(tile, c.x3, false, p, zs, c.stream);
+  else return CU32_E_ARG;
+  if (e != cudaSuccess) return static_cast<int>(e);
   e = cudaPeekAtLastError();
   return static_cast<int>(e);
 }

@@ -43,19 +43,48 @@ int gemm_stages(int tile_cfg, bool x3);
 template <class Cfg>
 cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   auto kernel = gemm_tf32_kernel<Cfg>;
-  // Opt in to the large dynamic shared-memory carve-out once per device.
-  static unsigned long long configured_devices = 0ULL;  // bit per device ordinal
+  // Once per device: opt in to the large dynamic shared-memory carve-out and ask how many
+  // CTAs (or CTA pairs) of this kernel can be resident at the same time - the persistent
+  // grid must not exceed that, or the surplus CTAs would run after the others have finished.
+  static int resident_units[64];  // per device ordinal; 0 = not configured yet
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  const unsigned long long bit = 1ULL << (dev & 63);
-  if (!(__atomic_load_n(&configured_devices, __ATOMIC_ACQUIRE) & bit)) {
+  int units = __atomic_load_n(&resident_units[dev & 63], __ATOMIC_ACQUIRE);
+  if (units == 0) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM);
     if (e != cudaSuccess) return e;
-    __atomic_fetch_or(&configured_devices, bit, __ATOMIC_RELEASE);
+    if (Cfg::CTAS == 2) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * 148, 1, 1);
+      q.blockDim = dim3(Cfg::THREADS, 1, 1);
+      q.dynamicSmemBytes = Cfg::DYN_SMEM;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      e = cudaOccupancyMaxActiveClusters(&units, kernel, &q);
+      if (e != cudaSuccess) return e;
+    } else {
+      int sms = 0, per_sm = 0;
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return e;
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Cfg::THREADS, Cfg::DYN_SMEM);
+      if (e != cudaSuccess) return e;
+      units = sms * per_sm;
+    }
+    if (units < 1) return cudaErrorLaunchOutOfResources;
+    __atomic_store_n(&resident_units[dev & 63], units, __ATOMIC_RELEASE);
   }
+  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * grid_z;
+  const long long grid_units = total_tiles < units ? total_tiles : units;
+  GemmParams q = p;
+  q.zcount = grid_z;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(p.tiles_m) * p.tiles_n * Cfg::CTAS, 1, grid_z);
+  cfg.gridDim = dim3(static_cast<unsigned>(grid_units) * Cfg::CTAS, 1, 1);
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
   cfg.stream = stream;
@@ -69,7 +98,7 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  return cudaLaunchKernelEx(&cfg, kernel, p);
+  return cudaLaunchKernelEx(&cfg, kernel, q);
 }
 
 // Expands to the switch over tile configurations for one layout pair.

@@ -18,6 +18,11 @@
 // round-to-nearest adds, so the length of any truncating accumulation chain is
 // bounded regardless of K.
 //
+// The kernel is persistent: the grid is one CTA (or CTA pair) per SM and each walks
+// the tile list with a fixed stride, so the drain and store of one tile overlap
+// the loads and MMAs of the next; pipeline-stage and TMEM-buffer phases simply
+// keep counting across tiles.
+//
 // Roles inside a CTA of 16 warps:
 //   warp 0        TMA producer      global -> shared (raw FP32 tiles, 128B swizzle)
 //   warp 1        MMA issuer        one thread issues tcgen05.mma, commits to mbarriers
@@ -48,7 +53,8 @@ struct GemmParams {
   int M, N;             // rows / columns of C to store
   int nkb_total;        // k-blocks of 32 in the whole reduction (before split-K)
   int tiles_m, tiles_n; // tile grid; a tile is (128*CTAS) x BN
-  int gz;               // > 1: blockIdx.z is a split-K slice; else a batch index
+  int gz;               // > 1: tiles run over gz split-K slices; else over zcount batches
+  int zcount;           // batches (gz == 1) or slices (= gz) folded into the tile index
   int kc;               // k-blocks accumulated in TMEM before a drain (>= 1)
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
   int* status;          // device word, 0 = ok; first give-up code otherwise
@@ -99,6 +105,17 @@ __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
                : "memory");
 }
 
+// Work of one CTA for one output tile.
+struct TileWork {
+  int row0;    // first row of A / C handled by this CTA
+  int col0;    // first column of C of the tile
+  int bcol0;   // first column of B staged by this CTA
+  int batch;   // batch coordinate of the tensor maps
+  int kb0;     // first k-block
+  int nkb;     // number of k-blocks (0 for a split-K slice that got none)
+  float* out;  // output base for this batch / slice
+};
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
   using namespace ptx;
@@ -121,31 +138,41 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
 
   const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
 
-  // ---- tile and k-range of this CTA (pair)
-  const int tile = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
-  constexpr int GROUP = 8;  // m-tiles swept together so concurrently resident tiles share operands in L2
-  const int per_group = GROUP * p.tiles_n;
-  const int g_first = (tile / per_group) * GROUP;
-  const int g_size = min(p.tiles_m - g_first, GROUP);
-  const int tm = g_first + (tile % per_group) % g_size;
-  const int tn = (tile % per_group) / g_size;
-
-  const int z = blockIdx.z;
-  const int nkb_total = p.nkb_total;
-  int kb0 = 0, nkb = nkb_total, batch = z;
-  float* out = p.C;
-  if (p.gz > 1) {
-    kb0 = static_cast<int>((static_cast<long long>(z) * nkb_total) / p.gz);
-    nkb = static_cast<int>((static_cast<long long>(z + 1) * nkb_total) / p.gz) - kb0;
-    batch = 0;
-    if (z > 0) out = p.Cbuf + static_cast<long long>(z - 1) * p.c_stride;
-  } else {
-    out = p.C + static_cast<long long>(z) * p.c_stride;
-  }
+  // ---- persistent tile loop: this CTA (pair) takes tiles first, first + step, ...
+  // Tile ids run over (z, m-group, n, m-in-group); concurrently resident tiles are
+  // consecutive ids, i.e. a GROUP x n patch of the output that shares operands in L2.
+  const int tiles_mn = p.tiles_m * p.tiles_n;
+  const long long total_tiles = static_cast<long long>(tiles_mn) * p.zcount;
+  const long long tile_first = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int kc = p.kc;
-  const int row0 = (tm * CTAS + static_cast<int>(rank)) * Cfg::BM;  // first A row of this CTA
-  const int col0 = tn * BN;                                         // first C column of the tile
-  const int bcol0 = col0 + static_cast<int>(rank) * Cfg::BN_CTA;    // first B column staged here
+
+  auto decode = [&](long long t) -> TileWork {
+    constexpr int GROUP = 8;
+    const int z = static_cast<int>(t / tiles_mn);
+    const int r = static_cast<int>(t - static_cast<long long>(z) * tiles_mn);
+    const int per_group = GROUP * p.tiles_n;
+    const int g_first = (r / per_group) * GROUP;
+    const int g_size = min(p.tiles_m - g_first, GROUP);
+    const int tm = g_first + (r % per_group) % g_size;
+    const int tn = (r % per_group) / g_size;
+    TileWork w;
+    w.row0 = (tm * CTAS + static_cast<int>(rank)) * Cfg::BM;
+    w.col0 = tn * BN;
+    w.bcol0 = w.col0 + static_cast<int>(rank) * Cfg::BN_CTA;
+    if (p.gz > 1) {
+      w.kb0 = static_cast<int>((static_cast<long long>(z) * p.nkb_total) / p.gz);
+      w.nkb = static_cast<int>((static_cast<long long>(z + 1) * p.nkb_total) / p.gz) - w.kb0;
+      w.batch = 0;
+      w.out = (z == 0) ? p.C : p.Cbuf + static_cast<long long>(z - 1) * p.c_stride;
+    } else {
+      w.kb0 = 0;
+      w.nkb = p.nkb_total;
+      w.batch = z;
+      w.out = p.C + static_cast<long long>(z) * p.c_stride;
+    }
+    return w;
+  };
 
   auto give_up = [&](int role, int a, int b) {
     abort_flag = 1;
@@ -192,56 +219,61 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
-          give_up(ROLE_TMA, s, i);
-          break;
-        }
-        const uint32_t full = smem_u32(&bar_full_tma[s]);
-        mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
-        int k0 = (kb0 + i) * Cfg::BK;
-        const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
-        const uint32_t b_dst = a_dst + Cfg::A_BYTES;
-        if (Cfg::IM2COL) {
-          // k-block -> (filter tap, block of 32 channels inside the tap)
-          const int tap = (kb0 + i) / p.conv_icb;
-          const int ic0 = ((kb0 + i) - tap * p.conv_icb) * Cfg::BK;
-          const int fh = tap / p.conv_FW;
-          const int fw = tap - fh * p.conv_FW;
-          k0 = tap * p.conv_IC + ic0;  // position in the filter's (fh, fw, ic) axis
-          // row0 addresses output pixel (n, oh, ow); the run of 128 pixels wraps
-          // over rows and images inside the tensor map's traversal box.
-          const int ohw = p.conv_OH * p.conv_OW;
-          const int n = row0 / ohw;
-          const int r = row0 - n * ohw;
-          const int oh = r / p.conv_OW;
-          const int ow = r - oh * p.conv_OW;
-          tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
-                             oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
-                             static_cast<uint16_t>(fh));
-        } else if (Cfg::A_MN) {
+      uint32_t it = 0;  // k-blocks issued so far, over all tiles: stage = it % STAGES
+      bool alive = true;
+      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+        const TileWork w = decode(t);
+        for (int i = 0; i < w.nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
+            give_up(ROLE_TMA, s, i);
+            alive = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full_tma[s]);
+          mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
+          int k0 = (w.kb0 + i) * Cfg::BK;
+          const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          if (Cfg::IM2COL) {
+            // k-block -> (filter tap, block of 32 channels inside the tap)
+            const int tap = (w.kb0 + i) / p.conv_icb;
+            const int ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
+            const int fh = tap / p.conv_FW;
+            const int fw = tap - fh * p.conv_FW;
+            k0 = tap * p.conv_IC + ic0;  // position in the filter's (fh, fw, ic) axis
+            // row0 addresses output pixel (n, oh, ow); the run of 128 pixels wraps
+            // over rows and images inside the tensor map's traversal box.
+            const int ohw = p.conv_OH * p.conv_OW;
+            const int n = w.row0 / ohw;
+            const int r = w.row0 - n * ohw;
+            const int oh = r / p.conv_OW;
+            const int ow = r - oh * p.conv_OW;
+            tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
+                               oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
+                               static_cast<uint16_t>(fh));
+          } else if (Cfg::A_MN) {
 #pragma unroll
-          for (int j = 0; j < Cfg::BM / 32; ++j)
-            tma_load_3d(a_dst + j * 4096, &p.tmA, full, row0 + 32 * j, k0, batch);
-        } else {
-          tma_load_3d(a_dst, &p.tmA, full, k0, row0, batch);
-        }
-        if (Cfg::B_MN) {
+            for (int j = 0; j < Cfg::BM / 32; ++j)
+              tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch);
+          } else {
+            tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch);
+          }
+          if (Cfg::B_MN) {
 #pragma unroll
-          for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-            tma_load_3d(b_dst + j * 4096, &p.tmB, full, bcol0 + 32 * j, k0, batch);
-        } else {
-          tma_load_3d(b_dst, &p.tmB, full, k0, bcol0, batch);
+            for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
+              tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch);
+          } else {
+            tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch);
+          }
         }
-        issued = i + 1;
       }
       if (abort_flag) {
         // Let copies already in flight land before shared memory is released:
         // wait (bounded) for the barrier of every stage still outstanding.
-        for (int i = max(0, issued - STAGES); i < issued; ++i) {
+        const uint32_t lo = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
+        for (uint32_t i = lo; i < it; ++i) {
           const int s = i % STAGES;
           const uint32_t ph = (i / STAGES) & 1;
           const long long t0 = clock64();
@@ -262,57 +294,64 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       constexpr uint32_t B_LT = Cfg::B_MN ? SMEM_LAYOUT_SW128_32B : SMEM_LAYOUT_SW128;
       constexpr uint32_t A_KSTEP = Cfg::A_MN ? 1024u : 32u;  // bytes per 8 elements of K
       constexpr uint32_t B_KSTEP = Cfg::B_MN ? 1024u : 32u;
-      int buf = 0;
-      uint32_t empty_parity[2] = {1u, 1u};
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
-        if (!mbar_wait<CTAS == 2>(ready, ph, &abort_flag)) {
-          give_up(ROLE_MMA, s, i);
-          break;
-        }
-        const bool chunk_start = (i % kc) == 0;
-        if (chunk_start) {
-          if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[buf]), empty_parity[buf], &abort_flag)) {
-            give_up(ROLE_MMA_TMEM, buf, i);
+      uint32_t it = 0;  // k-blocks consumed so far, over all tiles
+      uint32_t ch = 0;  // chunks started so far: TMEM buffer = ch & 1
+      bool alive = true;
+      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+        const TileWork w = decode(t);
+        for (int i = 0; i < w.nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
+          if (!mbar_wait<CTAS == 2>(ready, ph, &abort_flag)) {
+            give_up(ROLE_MMA, s, i);
+            alive = false;
             break;
           }
-          empty_parity[buf] ^= 1u;
-        }
-        tc_fence_after();
-        const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
-        const uint32_t b_hi = a_hi + Cfg::A_BYTES;
-        const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
-        // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
-        // instruction, an error of up to one ulp of the *accumulator*.  Issuing all the
-        // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
-        // fresh chunk is still small, keeps those truncations negligible; only the four
-        // hi*hi instructions then round at full magnitude.
-        if (X3) {
+          const bool chunk_start = (i % kc) == 0;
+          const int buf = ch & 1;
+          if (chunk_start) {
+            // the n-th use of a buffer waits for the (n-1)-th drain; the first use passes
+            if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[buf]), ((ch >> 1) & 1u) ^ 1u, &abort_flag)) {
+              give_up(ROLE_MMA_TMEM, buf, i);
+              alive = false;
+              break;
+            }
+          }
+          tc_fence_after();
+          const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
+          const uint32_t b_hi = a_hi + Cfg::A_BYTES;
+          const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
+          // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
+          // instruction, an error of up to one ulp of the *accumulator*.  Issuing all the
+          // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
+          // fresh chunk is still small, keeps those truncations negligible; only the four
+          // hi*hi instructions then round at full magnitude.
+          if (X3) {
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j) {
+              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+              umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+            }
+          }
 #pragma unroll
           for (int j = 0; j < Cfg::BK / 8; ++j) {
             const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
             const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-            const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-            const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-            umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-            umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
           }
-        }
-#pragma unroll
-        for (int j = 0; j < Cfg::BK / 8; ++j) {
-          const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-          const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-          umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
-        }
-        // The stage may be refilled once these MMAs have read it.
-        umma_commit<CTAS>(smem_u32(&bar_empty[s]));
-        if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_empty[s]), 1u));
-        if (((i + 1) % kc) == 0 || i + 1 == nkb) {
-          umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
-          if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_tmem_full[buf]), 1u));
-          buf ^= 1;
+          // The stage may be refilled once these MMAs have read it.
+          umma_commit<CTAS>(smem_u32(&bar_empty[s]));
+          if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_empty[s]), 1u));
+          if (((i + 1) % kc) == 0 || i + 1 == w.nkb) {
+            umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
+            if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_tmem_full[buf]), 1u));
+            ++ch;
+          }
         }
       }
     }
@@ -322,34 +361,40 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;
       constexpr int NST = Cfg::SPLIT_WARPS * 32;
       constexpr int NVEC = Cfg::HI_BYTES / 16;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
-          if (lane == 0) give_up(ROLE_SPLIT, s, i);
-          break;
-        }
-        if (X3) {
-          const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
-#pragma unroll 4
-          for (int v = st; v < NVEC; v += NST) {
-            const uint32_t addr = hi_base + v * 16;
-            const float4 x = lds128(addr);
-            float4 h, l;
-            h.x = rn_tf32(x.x); h.y = rn_tf32(x.y); h.z = rn_tf32(x.z); h.w = rn_tf32(x.w);
-            l.x = rn_tf32(x.x - h.x); l.y = rn_tf32(x.y - h.y);
-            l.z = rn_tf32(x.z - h.z); l.w = rn_tf32(x.w - h.w);
-            sts128(addr, h);
-            sts128(addr + Cfg::HI_BYTES, l);
+      uint32_t it = 0;
+      bool alive = true;
+      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+        const TileWork w = decode(t);
+        for (int i = 0; i < w.nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
+            if (lane == 0) give_up(ROLE_SPLIT, s, i);
+            alive = false;
+            break;
           }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) {
-          if (CTAS == 2 && rank != 0)
-            mbar_arrive_cluster(leader_addr(&bar_full_split[s]));
-          else
-            mbar_arrive(smem_u32(&bar_full_split[s]));
+          if (X3) {
+            const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
+#pragma unroll 4
+            for (int v = st; v < NVEC; v += NST) {
+              const uint32_t addr = hi_base + v * 16;
+              const float4 x = lds128(addr);
+              float4 h, l;
+              h.x = rn_tf32(x.x); h.y = rn_tf32(x.y); h.z = rn_tf32(x.z); h.w = rn_tf32(x.w);
+              l.x = rn_tf32(x.x - h.x); l.y = rn_tf32(x.y - h.y);
+              l.z = rn_tf32(x.z - h.z); l.w = rn_tf32(x.w - h.w);
+              sts128(addr, h);
+              sts128(addr + Cfg::HI_BYTES, l);
+            }
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) {
+            if (CTAS == 2 && rank != 0)
+              mbar_arrive_cluster(leader_addr(&bar_full_split[s]));
+            else
+              mbar_arrive(smem_u32(&bar_full_split[s]));
+          }
         }
       }
     }
@@ -359,59 +404,65 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     if (Cfg::REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     const int q = warp & 3;                              // TMEM lane quarter this warp may read
     const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
-    float acc[CW];
+    uint32_t ch = 0;                                     // chunks drained so far, over all tiles
+    bool alive = true;
+    for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+      const TileWork w = decode(t);
+      float acc[CW];
 #pragma unroll
-    for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
-    const int nchunks = (nkb + kc - 1) / kc;
-    bool ok = true;
-    for (int c = 0; c < nchunks; ++c) {
-      const int buf = c & 1;
-      const uint32_t par = (c >> 1) & 1;
-      if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
-        if (lane == 0) give_up(ROLE_DRAIN, buf, c);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                          static_cast<uint32_t>(buf * BN + h * CW);
-#pragma unroll
-      for (int g = 0; g < CW / 32; ++g) {
-        float t[32];
-        tmem_ld_32x32(t0 + g * 32, t);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[g * 32 + j] += t[j];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (CTAS == 2 && rank != 0)
-          mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
-        else
-          mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-      }
-    }
-    // ---- store this thread's row segment
-    const int row = row0 + q * 32 + lane;
-    if (ok && row < p.M) {
-      float* dst = out + static_cast<long long>(row) * p.ldc + col0 + h * CW;
-      const int ncols = p.N - (col0 + h * CW);  // columns left in this row segment
-      if (p.vec4_ok) {
-#pragma unroll
-        for (int j = 0; j < CW; j += 4) {
-          if (j + 3 < ncols) {
-            *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (j + e < ncols) dst[j + e] = acc[j + e];
-          }
+      for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
+      const int nchunks = (w.nkb + kc - 1) / kc;
+      for (int c = 0; c < nchunks; ++c, ++ch) {
+        const int buf = ch & 1;
+        const uint32_t par = (ch >> 1) & 1;
+        if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
+          if (lane == 0) give_up(ROLE_DRAIN, buf, c);
+          alive = false;
+          break;
         }
-      } else {
+        tc_fence_after();
+        const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                            static_cast<uint32_t>(buf * BN + h * CW);
 #pragma unroll
-        for (int j = 0; j < CW; ++j)
-          if (j < ncols) dst[j] = acc[j];
+        for (int g = 0; g < CW / 32; ++g) {
+          float v[32];
+          tmem_ld_32x32(t0 + g * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[g * 32 + j] += v[j];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2 && rank != 0)
+            mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
+          else
+            mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+        }
+      }
+      if (!alive) break;
+      // ---- store this thread's row segment; the MMA warp is already filling the
+      // TMEM buffers with the next tile's chunks meanwhile
+      const int row = w.row0 + q * 32 + lane;
+      if (row < p.M) {
+        float* dst = w.out + static_cast<long long>(row) * p.ldc + w.col0 + h * CW;
+        const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
+        if (p.vec4_ok) {
+#pragma unroll
+          for (int j = 0; j < CW; j += 4) {
+            if (j + 3 < ncols) {
+              *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (j + e < ncols) dst[j + e] = acc[j + e];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (j < ncols) dst[j] = acc[j];
+        }
       }
     }
   }
