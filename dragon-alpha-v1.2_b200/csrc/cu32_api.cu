@@ -169,6 +169,15 @@ static int run_gemm(const GemmCall& c) {
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
+  if (p.vec4_ok) {
+    // Output maps for the TMA-store epilogue: (columns, rows, batch) with the caller's pitch.
+    const uint64_t zs_c = c.gz > 1 ? 1 : nb;
+    const uint64_t sc = c.sC ? c.sC : static_cast<uint64_t>(c.ldc) * c.M;
+    rc = make_map3(&p.tmC, c.C, c.n_store, c.M, zs_c, c.ldc, sc, 32, 32, false);
+    if (!rc && c.gz > 1) rc = make_map3(&p.tmCbuf, c.Cbuf, c.n_store, c.M, c.gz - 1, c.ldc, sc, 32, 32, false);
+    if (rc) return rc;
+    p.tma_store = 1;
+  }
   cudaError_t e;
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
@@ -343,6 +352,10 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   p.gz = 1;
   p.kc = x3 ? g_kc.load() : g_kc_fast.load();
   p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
+  if (p.vec4_ok) {
+    if (int rc = make_map3(&p.tmC, dY, OC, static_cast<uint64_t>(GM), 1, OC, static_cast<uint64_t>(GM) * OC, 32, 32, false)) return rc;
+    p.tma_store = 1;
+  }
   p.conv_OW = OW; p.conv_OH = OH; p.conv_FW = FW; p.conv_IC = IC;
   p.conv_sw = sw; p.conv_sh = sh; p.conv_pw = pw; p.conv_ph = ph;
   cudaError_t e;

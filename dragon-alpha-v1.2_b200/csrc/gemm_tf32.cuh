@@ -46,6 +46,8 @@ struct GemmParams {
                         // im2col A: NHWC dims (C, W, H, N), 32 channels x 128 pixels
   CUtensorMap tmB;      // K-major B: dims (K, N, batch), box (32, BN/CTAS, 1)
                         // MN-major B: dims (N, K, batch), box (32, 32, 1)
+  CUtensorMap tmC;      // output C: dims (N, M, batches), box (32, 32, 1), 128B swizzle
+  CUtensorMap tmCbuf;   // split-K partial buffers: dims (N, M, gz-1), same box
   float* C;             // output of batch 0 / split-K slice 0
   float* Cbuf;          // split-K: outputs of slices 1..gz-1, c_stride floats apart
   long long ldc;        // row pitch of C in floats
@@ -57,6 +59,7 @@ struct GemmParams {
   int zcount;           // batches (gz == 1) or slices (= gz) folded into the tile index
   int kc;               // k-blocks accumulated in TMEM before a drain (>= 1)
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
+  int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
   int* status;          // device word, 0 = ok; first give-up code otherwise
   // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
@@ -77,10 +80,11 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN_CTA * BK * 4;
   static constexpr int HI_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGE_BYTES = HI_BYTES * (X3 ? 2 : 1);
-  static constexpr int SMEM_BUDGET = 220 * 1024;
+  static constexpr int SMEM_BUDGET = 192 * 1024;   // pipeline stages
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int STORE_STAGING = 8 * 4096;  // one 32x32 FP32 staging tile per drain warp
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + STORE_STAGING + 1024;  // +1024: manual alignment
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two chunk buffers
   static constexpr int THREADS = 512;
   static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;
@@ -114,6 +118,8 @@ struct TileWork {
   int kb0;     // first k-block
   int nkb;     // number of k-blocks (0 for a split-K slice that got none)
   float* out;  // output base for this batch / slice
+  int zc;      // batch / slice coordinate in the output tensor map
+  bool to_cbuf;  // this tile's output goes to the split-K partial buffers
 };
 
 template <class Cfg>
@@ -165,11 +171,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       w.nkb = static_cast<int>((static_cast<long long>(z + 1) * p.nkb_total) / p.gz) - w.kb0;
       w.batch = 0;
       w.out = (z == 0) ? p.C : p.Cbuf + static_cast<long long>(z - 1) * p.c_stride;
+      w.to_cbuf = z > 0;
+      w.zc = z > 0 ? z - 1 : 0;
     } else {
       w.kb0 = 0;
       w.nkb = p.nkb_total;
       w.batch = z;
       w.out = p.C + static_cast<long long>(z) * p.c_stride;
+      w.to_cbuf = false;
+      w.zc = z;
     }
     return w;
   };
@@ -441,30 +451,61 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         }
       }
       if (!alive) break;
-      // ---- store this thread's row segment; the MMA warp is already filling the
-      // TMEM buffers with the next tile's chunks meanwhile
-      const int row = w.row0 + q * 32 + lane;
-      if (row < p.M) {
-        float* dst = w.out + static_cast<long long>(row) * p.ldc + w.col0 + h * CW;
-        const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
-        if (p.vec4_ok) {
+      // ---- store; the MMA warp is already filling the TMEM buffers with the next
+      // tile's chunks meanwhile
+      if (p.tma_store) {
+        // Each drain warp owns a 32-row x CW-column block.  32x32 pieces go through a
+        // swizzled 4 KB staging tile (row r, 16-byte chunk c at r*128 + ((c ^ (r & 7)) * 16):
+        // conflict-free for the row-per-lane writes) and leave as one TMA store each, which
+        // writes whole 128-byte row segments and clips rows >= M and columns >= N.
+        const uint32_t stg = tiles_base + STAGES * Cfg::STAGE_BYTES + (warp - Cfg::DRAIN_WARP0) * 4096;
+        const CUtensorMap* cmap = w.to_cbuf ? &p.tmCbuf : &p.tmC;
 #pragma unroll
-          for (int j = 0; j < CW; j += 4) {
-            if (j + 3 < ncols) {
-              *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-            } else {
+        for (int g = 0; g < CW / 32; ++g) {
+          const int c0 = w.col0 + h * CW + g * 32;
+          const int r0 = w.row0 + q * 32;
+          if (c0 < p.N && r0 < p.M) {   // warp-uniform
+            if (lane == 0) tma_store_wait_read();   // the previous piece has left the staging tile
+            __syncwarp();
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (j + e < ncols) dst[j + e] = acc[j + e];
+            for (int c = 0; c < 8; ++c)
+              sts128(stg + lane * 128 + ((c ^ (lane & 7)) * 16),
+                     make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1], acc[g * 32 + c * 4 + 2],
+                                 acc[g * 32 + c * 4 + 3]));
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(cmap, stg, c0, r0, w.zc);
+              tma_store_commit();
             }
           }
-        } else {
+        }
+      } else {
+        const int row = w.row0 + q * 32 + lane;
+        if (row < p.M) {
+          float* dst = w.out + static_cast<long long>(row) * p.ldc + w.col0 + h * CW;
+          const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
+          if (p.vec4_ok) {
 #pragma unroll
-          for (int j = 0; j < CW; ++j)
-            if (j < ncols) dst[j] = acc[j];
+            for (int j = 0; j < CW; j += 4) {
+              if (j + 3 < ncols) {
+                *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (j + e < ncols) dst[j + e] = acc[j + e];
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (j < ncols) dst[j] = acc[j];
+          }
         }
       }
     }
+    // stores still in flight read this CTA's shared memory: let them finish before exit
+    if (lane == 0) tma_store_wait_all();
   }
 
   // ---- common exit: everyone arrives here, also after a give-up
