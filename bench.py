@@ -367,7 +367,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3",
         "data": "synthetic",
-        "config": {"workload": wl.desc + (f"; {world} ranks, one row block each" if world > 1 else ""),
+        "config": {"workload": wl.desc + (f"; {world} ranks, each its own shard of a {world}x larger problem" if world > 1 else ""),
                    "l2": "operands larger than L2 (no flush needed)" if wl.bytes > 126e6 else "L2 not flushed: operands fit in L2",
                    "kc": pkg.cu32.get_tune("kc"), "tile": pkg.cu32.get_tune("tile")},
         "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": a.steps * wl.kernels_per_step,
