@@ -141,7 +141,7 @@ class Workload:
     """Builds device operands and returns `launch()` (enqueue one step on the current stream),
     flops and algorithmic bytes per launch, plus host buffers for the end-to-end leg."""
 
-    def __init__(self, name, pkg, torch, rank, size=8192):
+    def __init__(self, name, pkg, torch, rank, size=8192, batch=1024, images=256):
         self.name, self.pkg, self.torch = name, pkg, torch
         W = pkg.workloads
         mm, bm, cv = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_batchMatMul, pkg.cu32.Cuda_conv3D
@@ -183,7 +183,7 @@ class Workload:
             self.cpu_case = (w.form, w.N, w.M, w.K, w.A, w.B)
             self.units = None
         elif name in ("c3_qk", "c3_pv"):
-            w = W.config3()
+            w = W.config3(Batch=batch)
             if name == "c3_qk":
                 self.hosts = [w.Q.pin_memory(), w.K.pin_memory()]
                 self.dev_in = [h.cuda() for h in self.hosts]
@@ -203,7 +203,7 @@ class Workload:
             self.flops = w.flops_each
             self.bytes = w.algorithmic_bytes_each
         elif name == "c4":
-            w = W.config4()
+            w = W.config4(N=images)
             d = w.dims
             self.hosts = [w.X.pin_memory(), w.W.pin_memory()]
             self.dev_in = [h.cuda() for h in self.hosts]
@@ -268,6 +268,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_ab")
     ap.add_argument("--size", type=int, default=8192, help="edge of the c2_* cubes (profiling on a smaller case)")
+    ap.add_argument("--batch", type=int, default=1024, help="batch of the c3_* workloads (smaller for profiling)")
+    ap.add_argument("--images", type=int, default=256, help="images of the c4 workload (smaller for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
@@ -312,7 +314,7 @@ def main():
     pkg.cu32.load()
     pk = peaks()
 
-    wl = Workload(a.workload, pkg, torch, rank, a.size)
+    wl = Workload(a.workload, pkg, torch, rank, a.size, a.batch, a.images)
     for _ in range(a.warmup):
         wl.launch()
     st = pkg.cu32.read_status()
@@ -337,6 +339,28 @@ def main():
         ms_e = time_steps(torch, dist, wl.e2e_step, e2e_steps, world) / e2e_steps
         e2e = {"value": wl.flops * world / (ms_e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e,
                "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
+
+    reassemble = None
+    if world > 1:
+        # The only collective of the path: putting the shards' outputs back together (all-gather
+        # over NVLink), or for the K-sharded long-K shape summing the partial products.
+        if a.workload == "c5":
+            def step_collective():
+                wl.launch()
+                dist.all_reduce(wl.out)
+            kind = "all-reduce of the [N,M] partial products"
+        else:
+            gathered = torch.empty((world,) + tuple(wl.out.shape), device="cuda")
+
+            def step_collective():
+                wl.launch()
+                dist.all_gather_into_tensor(gathered, wl.out)
+            kind = "all-gather of the output shards"
+        for _ in range(2):
+            step_collective()
+        rs = max(3, min(a.steps, 10))
+        ms_r = time_steps(torch, dist, step_collective, rs, world) / rs
+        reassemble = {"value": wl.flops * world / (ms_r * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_r, "collective": kind}
 
     if rank != 0:
         if world > 1:
@@ -373,6 +397,8 @@ def main():
         "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": a.steps * wl.kernels_per_step,
         "clocks": clocks,
     }
+    if reassemble:
+        line["with_collective"] = reassemble
     if hasattr(wl, "images"):
         line["images_per_s"] = wl.images * world / (ms_step * 1e-3)
     print(json.dumps(line))
