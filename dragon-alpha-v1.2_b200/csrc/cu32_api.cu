@@ -19,7 +19,7 @@
 namespace dragon {
 
 // ------------------------------------------------------------------ tuning knobs
-static std::atomic<int> g_kc{1};
+static std::atomic<int> g_kc{2};
 static std::atomic<int> g_kc_fast{4};
 static std::atomic<int> g_tile{-1};
 
@@ -97,6 +97,18 @@ static int make_map3(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1
   return r == CUDA_SUCCESS ? CU32_OK : CU32_E_TENSORMAP;
 }
 
+#ifdef DRAGON_TRACE
+static long long* g_trace_buf = nullptr;
+extern "C" __attribute__((visibility("default"))) int cu32_trace_enable(void) {
+  if (!g_trace_buf && cudaMalloc(&g_trace_buf, sizeof(long long) * 8 * 256) != cudaSuccess) return -1;
+  return static_cast<int>(cudaMemset(g_trace_buf, 0, sizeof(long long) * 8 * 256));
+}
+extern "C" __attribute__((visibility("default"))) int cu32_trace_read(long long* out) {
+  cudaDeviceSynchronize();
+  return static_cast<int>(cudaMemcpy(out, g_trace_buf, sizeof(long long) * 8 * 256, cudaMemcpyDeviceToHost));
+}
+#endif
+
 // One contraction, BLAS letters: C[M,N] = A * B over K.
 struct GemmCall {
   const float* A; const float* B; float* C; float* Cbuf;
@@ -119,10 +131,12 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;
-  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0};
+  // the TMEM-operand tiles (last three) are not chosen automatically yet
+  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0, 0.0, 0.0, 0.0};
   int best = TILE_1x128;
   double best_t = 1e300;
   for (int t = 0; t < TILE_COUNT; ++t) {
+    if (rate[t] <= 0.0) continue;
     const int ctas = tile_ctas(t), bn = tile_bn(t);
     const double n_cta = static_cast<double>((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn) * ctas * z;
     const double waves = static_cast<double>(static_cast<long long>((n_cta + 147.0) / 148.0));
@@ -141,7 +155,8 @@ static int run_gemm(const GemmCall& c) {
     return CU32_E_ALIGN;
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
-  const int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
+  int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
+  if (!c.x3 && tile_is_ts(tile)) tile = TILE_1x256;   // the TMEM-operand tiles are FP32-accurate only
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -182,6 +197,9 @@ static int run_gemm(const GemmCall& c) {
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
 
+#ifdef DRAGON_TRACE
+  p.trace = g_trace_buf;
+#endif
   // Batches (or split-K slices) are folded into the kernel's tile index.
   const int zs = c.gz > 1 ? c.gz : c.batch;
   if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
@@ -314,7 +332,8 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
       upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8)
     return CU32_E_GEOMETRY;
 
-  const int tile = pick_tile(GM, OC, 1);
+  int tile = pick_tile(GM, OC, 1);
+  if (!x3 && tile_is_ts(tile)) tile = TILE_1x256;
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;

@@ -14,14 +14,20 @@ enum TileCfg : int {
   TILE_1x256 = 2,  // 128 x 256, one CTA
   TILE_2x128 = 3,  // 256 x 128, CTA pair
   TILE_2x256 = 4,  // 256 x 256, CTA pair
-  TILE_COUNT = 5
+  // "T" tiles feed the A operand to the tensor core through TMEM (FP32-accurate mode only)
+  TILE_2x192T = 5, // 256 x 192, CTA pair
+  TILE_1x64T = 6,  // 128 x 64, one CTA
+  TILE_1x128T = 7, // 128 x 128, one CTA
+  TILE_COUNT = 8
 };
 
-inline int tile_ctas(int cfg) { return cfg >= TILE_2x128 ? 2 : 1; }
+inline int tile_ctas(int cfg) { return (cfg == TILE_2x128 || cfg == TILE_2x256 || cfg == TILE_2x192T) ? 2 : 1; }
+inline bool tile_is_ts(int cfg) { return cfg >= TILE_2x192T; }
 inline int tile_bn(int cfg) {
   switch (cfg) {
-    case TILE_1x64: return 64;
-    case TILE_1x128: case TILE_2x128: return 128;
+    case TILE_1x64: case TILE_1x64T: return 64;
+    case TILE_1x128: case TILE_2x128: case TILE_1x128T: return 128;
+    case TILE_2x192T: return 192;
     default: return 256;
   }
 }
@@ -109,6 +115,9 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
     case TILE_1x256: return launch_one<GemmCfg<256, 1, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
     case TILE_2x128: return launch_one<GemmCfg<128, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
     case TILE_2x256: return launch_one<GemmCfg<256, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
+    case TILE_2x192T: return launch_one<GemmCfg<192, 2, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
+    case TILE_1x64T:  return launch_one<GemmCfg<64, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream);  \
+    case TILE_1x128T: return launch_one<GemmCfg<128, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
     default: return cudaErrorInvalidValue;                                                     \
   }
 

@@ -61,39 +61,67 @@ struct GemmParams {
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
   int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
   int* status;          // device word, 0 = ok; first give-up code otherwise
+#ifdef DRAGON_TRACE
+  long long* trace;     // 8 x 256 timestamps (tracing builds only)
+#endif
   // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
   // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
   int conv_OW, conv_OH, conv_FW, conv_IC, conv_icb, conv_sw, conv_sh, conv_pw, conv_ph;
 };
 
+#ifdef DRAGON_TRACE
+// Timeline instrumentation for pipeline studies: CTA 0 records clock64() at the hand-over
+// points of its first 256 k-blocks into GemmParams::trace.  Not compiled into the product.
+#define TRACE(ev, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 256u) p.trace[(ev) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(ev, idx) do { } while (0)
+#endif
+
 enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5 };
 
-template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false>
+template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false, bool TS_ = false>
 struct GemmCfg {
   static constexpr int BN = BN_, CTAS = CTAS_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, X3 = X3_, IM2COL = IM2COL_;
+  // TS: the A operand reaches the tensor core through TMEM instead of shared memory.
+  // The raw A tile is split by four warps straight into TMEM (hi and lo, 32 columns
+  // each per k-block, two slots), which removes A's hi/lo tiles and all of A's
+  // operand fetches from shared memory - the bandwidth that otherwise bounds the kernel.
+  static constexpr bool TS = TS_;
   static constexpr int BM = 128;            // rows of A (and TMEM lanes) per CTA
   static constexpr int BK = 32;             // one 128-byte swizzle row of FP32
   static constexpr int BN_CTA = BN / CTAS;  // B columns staged per CTA
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN_CTA * BK * 4;
-  static constexpr int HI_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGE_BYTES = HI_BYTES * (X3 ? 2 : 1);
+  static constexpr int HI_BYTES = A_BYTES + B_BYTES;   // bytes one k-block brings in by TMA
+  // stage layout   !TS: [A_hi][B_hi][A_lo][B_lo]      TS: [A_raw][B_hi][B_lo]
+  static constexpr int STAGE_BYTES = TS ? (A_BYTES + B_BYTES * (X3 ? 2 : 1)) : HI_BYTES * (X3 ? 2 : 1);
+  static constexpr int B_LO_OFFSET = TS ? B_BYTES : HI_BYTES;  // from B_hi to B_lo
   static constexpr int SMEM_BUDGET = 192 * 1024;   // pipeline stages
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int STORE_STAGING = 8 * 4096;  // one 32x32 FP32 staging tile per drain warp
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + STORE_STAGING + 1024;  // +1024: manual alignment
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two chunk buffers
+  static constexpr int A_TMEM_COL0 = 2 * BN;                    // TS: A slots follow the two chunk buffers
+  static constexpr int A_SLOT_COLS = 2 * BK;                    // hi (32 columns) + lo (32 columns)
+  static constexpr int TMEM_NEED = 2 * BN + (TS ? 2 * A_SLOT_COLS : 0);
+  static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
+                                   : TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int THREADS = 512;
-  static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;
+  static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;      // TS: warps 2,3 split B, warps 4..7 split A
   static constexpr int DRAIN_WARP0 = 8, DRAIN_WARPS = 8;
   static constexpr int CW = BN / 2;          // columns per drain warp
   static constexpr bool REALLOC = CW > 64;   // drainers need > 128 registers
-  static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
+  // register budgets after reallocation (256 threads each side, 64 K registers per SM):
+  // the TMEM-writing splitters hold 64 split values, so they keep more than the plain ones
+  static constexpr int REGS_MOVERS = TS ? 96 : 64;
+  static constexpr int REGS_DRAINERS = TS ? 160 : 192;
+  static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN");
+  static_assert(TMEM_NEED <= 512, "TMEM");
   static_assert(STAGES >= 2, "stages");
   static_assert(!(IM2COL && A_MN), "im2col A is K-major");
+  static_assert(!TS || X3, "TS is only built for the FP32-accurate mode");
 };
 
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
@@ -135,6 +163,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   __shared__ __align__(8) uint64_t bar_empty[8];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ __align__(8) uint64_t bar_a_empty[2];   // TS: the MMAs have read A slot i
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
 
@@ -200,6 +229,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[b]), Cfg::DRAIN_WARPS * CTAS);
+      mbar_init(smem_u32(&bar_a_empty[b]), 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&p.tmA);
@@ -225,7 +255,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   // accumulators alone need 128 registers per thread, so registers are moved
   // from the first two warpgroups to the last two.
   if (warp < Cfg::DRAIN_WARP0) {
-  if (Cfg::REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (Cfg::REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_MOVERS));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -241,6 +271,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             alive = false;
             break;
           }
+          TRACE(0, it);
           const uint32_t full = smem_u32(&bar_full_tma[s]);
           mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
           int k0 = (w.kb0 + i) * Cfg::BK;
@@ -294,8 +325,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // Measured cost to this thread: ~70 cycles per MMA, ~125 per commit, a few hundred per
+    // barrier wait, against at most 1536 cycles of execution per k-block - so commits are
+    // kept to the minimum (one paired commit instead of two for a CTA pair).
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN, Cfg::B_MN);
+      constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN && !Cfg::TS, Cfg::B_MN);
       constexpr uint32_t A_LBO = Cfg::A_MN ? 4096u : 16u;
       constexpr uint32_t B_LBO = Cfg::B_MN ? 4096u : 16u;
       constexpr uint32_t A_SBO = Cfg::A_MN ? 512u : 1024u;
@@ -310,6 +344,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it) {
+          const bool chunk_end = ((i + 1) % kc) == 0 || i + 1 == w.nkb;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
@@ -318,6 +353,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             alive = false;
             break;
           }
+          TRACE(3, it);
           const bool chunk_start = (i % kc) == 0;
           const int buf = ch & 1;
           if (chunk_start) {
@@ -337,29 +373,50 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
           // fresh chunk is still small, keeps those truncations negligible; only the four
           // hi*hi instructions then round at full magnitude.
-          if (X3) {
+          if (Cfg::TS) {
+            const uint32_t slot = it & 1u;
+            const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + slot * Cfg::A_SLOT_COLS;
+            const uint32_t ta_lo = ta_hi + Cfg::BK;
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j) {
+              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::B_LO_OFFSET + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+              umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo, idesc, 1u);
+            }
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j) {
+              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi, idesc, 1u);
+            }
+            if (CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
+            else umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
+          } else {
+            if (X3) {
+#pragma unroll
+              for (int j = 0; j < Cfg::BK / 8; ++j) {
+                const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+                const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+                const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+                const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+                umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+                umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+              }
+            }
 #pragma unroll
             for (int j = 0; j < Cfg::BK / 8; ++j) {
               const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
               const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-              umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+              umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
             }
           }
-#pragma unroll
-          for (int j = 0; j < Cfg::BK / 8; ++j) {
-            const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-            const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-            umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
-          }
+          TRACE(4, it);
           // The stage may be refilled once these MMAs have read it.
-          umma_commit<CTAS>(smem_u32(&bar_empty[s]));
-          if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_empty[s]), 1u));
-          if (((i + 1) % kc) == 0 || i + 1 == w.nkb) {
-            umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
-            if (CTAS == 2) umma_commit<CTAS>(mapa(smem_u32(&bar_tmem_full[buf]), 1u));
+          if (CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[s]));
+          else umma_commit<CTAS>(smem_u32(&bar_empty[s]));
+          if (chunk_end) {
+            if (CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[buf]));
+            else umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
             ++ch;
           }
         }
@@ -368,9 +425,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   } else {
     // ------------------------------------------------------------ splitters
     if (RELAY) {
-      const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;
-      constexpr int NST = Cfg::SPLIT_WARPS * 32;
+      const bool a_splitter = Cfg::TS && warp >= 4;   // TS: warps 4..7 own TMEM lane quarters 0..3
+      // shared-memory split: which 16-byte vectors of the stage this thread handles
+      const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;   // TS: only warps 2,3 (0..63) use it
+      constexpr int NST = Cfg::TS ? 64 : Cfg::SPLIT_WARPS * 32;
+      constexpr int VEC0 = Cfg::TS ? Cfg::A_BYTES / 16 : 0;           // TS: only the B tile
       constexpr int NVEC = Cfg::HI_BYTES / 16;
+      constexpr int LO_OFF = Cfg::TS ? Cfg::B_LO_OFFSET : Cfg::HI_BYTES;
       uint32_t it = 0;
       bool alive = true;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
@@ -383,10 +444,56 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             alive = false;
             break;
           }
-          if (X3) {
-            const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
+          if (!Cfg::TS && warp == 2 && lane == 0) TRACE(1, it);
+          if (Cfg::TS && warp == 4 && lane == 0) TRACE(6, it);
+          const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
+          if (a_splitter) {
+            // This thread owns row (quarter*32 + lane) of the A tile = its TMEM lane.
+            const uint32_t slot = it & 1u;
+            if (!mbar_wait(smem_u32(&bar_a_empty[slot]), ((it >> 1) & 1u) ^ 1u, &abort_flag)) {
+              if (lane == 0) give_up(ROLE_SPLIT, 100 + static_cast<int>(slot), i);
+              alive = false;
+              break;
+            }
+            tc_fence_after();
+            const int qd = warp & 3;
+            float hi[32], lo[32];
+            if (Cfg::A_MN) {
+              // A tile = 4 slabs of [32 k][32 m] floats, 32-byte-unit swizzle; this lane reads
+              // its column m = lane of slab qd, one element per k-row.
+              const uint32_t slab = hi_base + qd * 4096;
+#pragma unroll
+              for (int k = 0; k < 32; ++k) {
+                float x;
+                const uint32_t addr = slab + k * 128 + ((((lane >> 3) ^ (k & 3)) << 5) | ((lane & 7) << 2));
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(addr));
+                hi[k] = rn_tf32(x);
+                lo[k] = rn_tf32(x - hi[k]);
+              }
+            } else {
+              // A tile = [128 rows][32 k] floats, 16-byte-unit swizzle: chunk c of row r sits
+              // at r*128 + ((c ^ (r & 7)) * 16).
+              const int r = qd * 32 + lane;
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const float4 x = lds128(hi_base + r * 128 + ((c ^ (r & 7)) * 16));
+                hi[c * 4 + 0] = rn_tf32(x.x); lo[c * 4 + 0] = rn_tf32(x.x - hi[c * 4 + 0]);
+                hi[c * 4 + 1] = rn_tf32(x.y); lo[c * 4 + 1] = rn_tf32(x.y - hi[c * 4 + 1]);
+                hi[c * 4 + 2] = rn_tf32(x.z); lo[c * 4 + 2] = rn_tf32(x.z - hi[c * 4 + 2]);
+                hi[c * 4 + 3] = rn_tf32(x.w); lo[c * 4 + 3] = rn_tf32(x.w - hi[c * 4 + 3]);
+              }
+            }
+            const uint32_t ta = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + Cfg::A_TMEM_COL0 +
+                                slot * Cfg::A_SLOT_COLS;
+            if (warp == 4 && lane == 0) TRACE(1, it);
+            tmem_st_32x32(ta, hi);
+            tmem_st_32x32(ta + Cfg::BK, lo);
+            tmem_wait_st();
+            if (warp == 4 && lane == 0) TRACE(2, it);
+            tc_fence_before();
+          } else if (X3) {
 #pragma unroll 4
-            for (int v = st; v < NVEC; v += NST) {
+            for (int v = VEC0 + st; v < NVEC; v += NST) {
               const uint32_t addr = hi_base + v * 16;
               const float4 x = lds128(addr);
               float4 h, l;
@@ -394,11 +501,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               l.x = rn_tf32(x.x - h.x); l.y = rn_tf32(x.y - h.y);
               l.z = rn_tf32(x.z - h.z); l.w = rn_tf32(x.w - h.w);
               sts128(addr, h);
-              sts128(addr + Cfg::HI_BYTES, l);
+              sts128(addr + LO_OFF, l);
             }
+            if (warp == 2 && lane == 0 && !Cfg::TS) TRACE(6, it);
             fence_proxy_async_smem();
           }
           __syncwarp();
+          if (!Cfg::TS && warp == 2 && lane == 0) TRACE(2, it);
+          if (Cfg::TS && warp == 4 && lane == 0) TRACE(7, it);
           if (lane == 0) {
             if (CTAS == 2 && rank != 0)
               mbar_arrive_cluster(leader_addr(&bar_full_split[s]));
@@ -411,7 +521,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   }
   } else {
     // ------------------------------------------------------------ drainers
-    if (Cfg::REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    if (Cfg::REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_DRAINERS));
     const int q = warp & 3;                              // TMEM lane quarter this warp may read
     const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
     uint32_t ch = 0;                                     // chunks drained so far, over all tiles
@@ -431,23 +541,33 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           break;
         }
         tc_fence_after();
+        if (warp == 8 && lane == 0) TRACE(5, ch);
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                             static_cast<uint32_t>(buf * BN + h * CW);
+        // 16-column pieces, the load of piece g+1 in flight while piece g is added; the
+        // buffer goes back to the MMA issuer as soon as the last piece has left TMEM.
+        constexpr int PIECES = CW / 16;
+        float va[16], vb[16];
+        tmem_ld_32x16(t0, va);
 #pragma unroll
-        for (int g = 0; g < CW / 32; ++g) {
-          float v[32];
-          tmem_ld_32x32(t0 + g * 32, v);
+        for (int g = 0; g < PIECES; ++g) {
           tmem_wait_ld();
+          float (&cur)[16] = (g & 1) ? vb : va;
+          float (&nxt)[16] = (g & 1) ? va : vb;
+          if (g + 1 < PIECES) {
+            tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (CTAS == 2 && rank != 0)
+                mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
+              else
+                mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+            }
+          }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[g * 32 + j] += v[j];
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (CTAS == 2 && rank != 0)
-            mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
-          else
-            mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+          for (int j = 0; j < 16; ++j) acc[g * 16 + j] += cur[j];
         }
       }
       if (!alive) break;

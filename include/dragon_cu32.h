@@ -196,10 +196,11 @@ CU32_API int cu32_conv3D_W1(const int64_t* streams, int length, const float* dX,
 
 /* Tuning / diagnostics knobs, process-wide.  Keys:
  *   "kc"       k-blocks (of 32) accumulated inside the tensor core before each FP32
- *              register add, FP32-accurate mode (default 1)
+ *              register add, FP32-accurate mode (default 2)
  *   "kc_fast"  same for the TF32 fast mode (default 4)
- *   "tile"     force a tile configuration 0..4 (128x64, 128x128, 128x256, 256x128 pair,
- *              256x256 pair); -1 = choose from the shape (default)
+ *   "tile"     force a tile configuration: 0..4 = 128x64, 128x128, 128x256, 256x128 pair,
+ *              256x256 pair (operands from shared memory); 5..7 = 256x192 pair, 128x64,
+ *              128x128 with the A operand fed through TMEM; -1 = choose from the shape (default)
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
 CU32_API int cu32_tune(const char* key, int value);
 CU32_API int cu32_get_tune(const char* key, int* value);

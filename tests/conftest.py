@@ -57,4 +57,4 @@ def _default_tuning(request):
         p.cu32.tune("kc_fast", DEFAULT_KC["kc_fast"])
 
 
-DEFAULT_KC = {"kc": 1, "kc_fast": 4}
+DEFAULT_KC = {"kc": 2, "kc_fast": 4}

@@ -106,7 +106,7 @@ def test_matmul_remainder_sweep(pkg, O, cuda):
         assert O.same_percent(C, G.ref_matmul(O, form, A, B, N, M, K), 1e-5) >= 0.999
 
 
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6, 7])
 def test_every_tile_configuration(pkg, O, cuda, tile):
     pkg.cu32.tune("tile", tile)
     for form in ("AB", "T1", "T2"):
@@ -115,6 +115,21 @@ def test_every_tile_configuration(pkg, O, cuda, tile):
             A, B = G.rand_pm1(sa, 7), G.rand_pm1(sb, 8)
             C = G.matmul(pkg, form, A, B, N, M, K)
             assert_accurate(O, C, G.f64_matmul(O, form, A, B), f"tile {tile} {form} {N}x{M}x{K}")
+    # the same tile through the batched, split-K and convolution paths
+    rng = np.random.default_rng(tile)
+    Batch, N, M, K = 3, 200, 196, 100
+    A = rng.standard_normal((Batch, N, K)).astype(np.float32)
+    B = rng.standard_normal((Batch, K, M)).astype(np.float32)
+    out = G.Out(Batch * N * M)
+    dA, dB = G.dev(A), G.dev(B)
+    pkg.cu32.Cuda_batchMatMul.batchMatMul([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, M, K, K)
+    assert_accurate(O, out.host((Batch, N, M)), O.f64.batchMatMul(A, B), f"tile {tile} bmm")
+    A, B = G.rand_pm1((1028, 132), 3), G.rand_pm1((1028, 260), 4)
+    C, _, _ = G.matmul_sk(pkg, "T1", A, B, 132, 260, 1028, 4)
+    assert_accurate(O, C, O.f64.matMulT1(A, B), f"tile {tile} split-K T1")
+    X = rng.standard_normal((4, 12, 12, 36)).astype(np.float32)
+    W = rng.standard_normal((40, 3, 3, 36)).astype(np.float32) * 0.1
+    assert_accurate(O, G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, 1, 1), O.f64.conv3D(X, W, 12, 12, 1, 1, 1, 1), f"tile {tile} conv")
 
 
 @pytest.mark.parametrize("kc", [1, 2, 3, 8, 1000])
