@@ -42,6 +42,12 @@ sys.path.insert(0, str(ROOT))
 METRIC = "FP32-accurate matMul TFLOPS"
 UNIT = "TFLOP/s"
 
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
+# one ncu capture of the same workload; the captures are summarised in profiles/).
+NCU_TRAFFIC_BYTES = {
+    "c2_ab": 2.54e9,     # profiles/gemm_tf32_matMul_AB_8192_traffic.md
+}
+
 
 def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
@@ -374,7 +380,7 @@ def main():
     bound = "hbm" if a.workload.startswith("c3") else "tensor"
     if bound == "tensor":
         roof = {"bound": "tensor", "achieved": per_gpu, "peak": ceiling, "unit": "TFLOP/s", "frac": per_gpu / ceiling,
-                "traffic": None,
+                "traffic": NCU_TRAFFIC_BYTES.get(a.workload) if a.size == 8192 else None,
                 "peak_basis": f"{pk['basis']} bf16 {'sustained' if sustained else 'burst'} {bf16} TFLOP/s / 2 (TF32 rate) / 3 (hi*hi + hi*lo + lo*hi)"}
     else:
         gbs = wl.bytes / (ms_step * 1e-3) / 1e9
