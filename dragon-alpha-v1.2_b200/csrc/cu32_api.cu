@@ -22,12 +22,14 @@ namespace dragon {
 static std::atomic<int> g_kc{2};
 static std::atomic<int> g_kc_fast{4};
 static std::atomic<int> g_tile{-1};
+static std::atomic<int> g_l2hint{1};
 
 static void load_env_once() {
   static std::once_flag once;
   std::call_once(once, [] {
     if (const char* s = std::getenv("DRAGON_CU32_KC")) { int v = std::atoi(s); if (v >= 1) g_kc = v; }
     if (const char* s = std::getenv("DRAGON_CU32_KC_FAST")) { int v = std::atoi(s); if (v >= 1) g_kc_fast = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_L2HINT")) { int v = std::atoi(s); if (v == 0 || v == 1) g_l2hint = v; }
     if (const char* s = std::getenv("DRAGON_CU32_TILE")) { int v = std::atoi(s); if (v >= -1 && v < TILE_COUNT) g_tile = v; }
   });
 }
@@ -183,6 +185,7 @@ static int run_gemm(const GemmCall& c) {
   p.tiles_n = (c.n_store + bn - 1) / bn;
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
+  p.l2_hints = (g_l2hint.load() && p.tiles_n > 1 && p.tiles_m > 1) ? 1 : 0;
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.vec4_ok) {
     // Output maps for the TMA-store epilogue: (columns, rows, batch) with the caller's pitch.
@@ -370,6 +373,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   p.tiles_n = (OC + bn - 1) / bn;
   p.gz = 1;
   p.kc = x3 ? g_kc.load() : g_kc_fast.load();
+  p.l2_hints = (g_l2hint.load() && p.tiles_n > 1 && p.tiles_m > 1) ? 1 : 0;
   p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
   if (p.vec4_ok) {
     if (int rc = make_map3(&p.tmC, dY, OC, static_cast<uint64_t>(GM), 1, OC, static_cast<uint64_t>(GM) * OC, 32, 32, false)) return rc;
@@ -620,6 +624,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "kc")) { if (value < 1) return CU32_E_ARG; g_kc = value; return CU32_OK; }
   if (!std::strcmp(key, "kc_fast")) { if (value < 1) return CU32_E_ARG; g_kc_fast = value; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { if (value < -1 || value >= TILE_COUNT) return CU32_E_ARG; g_tile = value; return CU32_OK; }
+  if (!std::strcmp(key, "l2hint")) { if (value < 0 || value > 1) return CU32_E_ARG; g_l2hint = value; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {
@@ -628,6 +633,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "kc")) { *value = g_kc; return CU32_OK; }
   if (!std::strcmp(key, "kc_fast")) { *value = g_kc_fast; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { *value = g_tile; return CU32_OK; }
+  if (!std::strcmp(key, "l2hint")) { *value = g_l2hint; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_read_status(int* status) {

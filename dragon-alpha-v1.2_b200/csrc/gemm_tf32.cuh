@@ -60,6 +60,7 @@ struct GemmParams {
   int kc;               // k-blocks accumulated in TMEM before a drain (>= 1)
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
   int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
+  int l2_hints;         // load A with evict-last and B with evict-first L2 priority
   int* status;          // device word, 0 = ok; first give-up code otherwise
 #ifdef DRAGON_TRACE
   long long* trace;     // 8 x 256 timestamps (tracing builds only)
@@ -261,6 +262,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     if (lane == 0) {
       uint32_t it = 0;  // k-blocks issued so far, over all tiles: stage = it % STAGES
       bool alive = true;
+      // Tiles are walked in groups of 8 row-tiles across all column-tiles, so an A panel is
+      // re-used by every column-tile of the sweep while B streams through once per group:
+      // keep A in L2, let B go first (without this the two panels, together larger than
+      // L2, evict each other in exactly the order they are needed again).
+      const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : 0ull;
+      const uint64_t pol_b = p.l2_hints ? l2_policy_evict_first() : 0ull;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it) {
@@ -293,20 +300,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             const int ow = r - oh * p.conv_OW;
             tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
                                oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
-                               static_cast<uint16_t>(fh));
+                               static_cast<uint16_t>(fh), pol_a);
           } else if (Cfg::A_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BM / 32; ++j)
-              tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch);
+              tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch, pol_a);
           } else {
-            tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch);
+            tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
           }
           if (Cfg::B_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-              tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch);
+              tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);
           } else {
-            tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch);
+            tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch, pol_b);
           }
         }
       }

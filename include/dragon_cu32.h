@@ -201,6 +201,8 @@ CU32_API int cu32_conv3D_W1(const int64_t* streams, int length, const float* dX,
  *   "tile"     force a tile configuration: 0..4 = 128x64, 128x128, 128x256, 256x128 pair,
  *              256x256 pair (operands from shared memory); 5..7 = 256x192 pair, 128x64,
  *              128x128 with the A operand fed through TMEM; -1 = choose from the shape (default)
+ *   "l2hint"   1 = load A with evict-last and B with evict-first L2 priority when the tile
+ *              grid re-uses an A panel across column tiles (default), 0 = no hints
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
 CU32_API int cu32_tune(const char* key, int value);
 CU32_API int cu32_get_tune(const char* key, int* value);
