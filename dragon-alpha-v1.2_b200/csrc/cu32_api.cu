@@ -22,14 +22,14 @@ namespace dragon {
 static std::atomic<int> g_kc{2};
 static std::atomic<int> g_kc_fast{4};
 static std::atomic<int> g_tile{-1};
-static std::atomic<int> g_l2hint{1};
+static std::atomic<int> g_l2hint{0};
 
 static void load_env_once() {
   static std::once_flag once;
   std::call_once(once, [] {
     if (const char* s = std::getenv("DRAGON_CU32_KC")) { int v = std::atoi(s); if (v >= 1) g_kc = v; }
     if (const char* s = std::getenv("DRAGON_CU32_KC_FAST")) { int v = std::atoi(s); if (v >= 1) g_kc_fast = v; }
-    if (const char* s = std::getenv("DRAGON_CU32_L2HINT")) { int v = std::atoi(s); if (v == 0 || v == 1) g_l2hint = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_L2HINT")) { int v = std::atoi(s); if (v >= 0 && v <= 2) g_l2hint = v; }
     if (const char* s = std::getenv("DRAGON_CU32_TILE")) { int v = std::atoi(s); if (v >= -1 && v < TILE_COUNT) g_tile = v; }
   });
 }
@@ -134,7 +134,7 @@ static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;
   // the TMEM-operand tiles (last three) are not chosen automatically yet
-  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0, 0.0, 0.0, 0.0};
+  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0, 0.0, 0.0, 0.0, 0.0};
   int best = TILE_1x128;
   double best_t = 1e300;
   for (int t = 0; t < TILE_COUNT; ++t) {
@@ -185,7 +185,7 @@ static int run_gemm(const GemmCall& c) {
   p.tiles_n = (c.n_store + bn - 1) / bn;
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
-  p.l2_hints = (g_l2hint.load() && p.tiles_n > 1 && p.tiles_m > 1) ? 1 : 0;
+  p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.vec4_ok) {
     // Output maps for the TMA-store epilogue: (columns, rows, batch) with the caller's pitch.
@@ -373,7 +373,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   p.tiles_n = (OC + bn - 1) / bn;
   p.gz = 1;
   p.kc = x3 ? g_kc.load() : g_kc_fast.load();
-  p.l2_hints = (g_l2hint.load() && p.tiles_n > 1 && p.tiles_m > 1) ? 1 : 0;
+  p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
   if (p.vec4_ok) {
     if (int rc = make_map3(&p.tmC, dY, OC, static_cast<uint64_t>(GM), 1, OC, static_cast<uint64_t>(GM) * OC, 32, 32, false)) return rc;
@@ -624,7 +624,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "kc")) { if (value < 1) return CU32_E_ARG; g_kc = value; return CU32_OK; }
   if (!std::strcmp(key, "kc_fast")) { if (value < 1) return CU32_E_ARG; g_kc_fast = value; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { if (value < -1 || value >= TILE_COUNT) return CU32_E_ARG; g_tile = value; return CU32_OK; }
-  if (!std::strcmp(key, "l2hint")) { if (value < 0 || value > 1) return CU32_E_ARG; g_l2hint = value; return CU32_OK; }
+  if (!std::strcmp(key, "l2hint")) { if (value < 0 || value > 2) return CU32_E_ARG; g_l2hint = value; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {

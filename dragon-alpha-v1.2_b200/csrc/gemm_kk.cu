@@ -31,6 +31,7 @@ int gemm_stage_bytes(int tile_cfg, bool x3) {
     case TILE_1x256: return stage_bytes_of<256, 1>(x3);
     case TILE_2x128: return stage_bytes_of<128, 2>(x3);
     case TILE_2x256: return stage_bytes_of<256, 2>(x3);
+    case TILE_2x64: return stage_bytes_of<64, 2>(x3);
     case TILE_2x192T: return GemmCfg<192, 2, false, false, true, false, true>::STAGE_BYTES;
     case TILE_1x64T: return GemmCfg<64, 1, false, false, true, false, true>::STAGE_BYTES;
     case TILE_1x128T: return GemmCfg<128, 1, false, false, true, false, true>::STAGE_BYTES;
@@ -44,6 +45,7 @@ int gemm_stages(int tile_cfg, bool x3) {
     case TILE_1x256: return stages_of<256, 1>(x3);
     case TILE_2x128: return stages_of<128, 2>(x3);
     case TILE_2x256: return stages_of<256, 2>(x3);
+    case TILE_2x64: return stages_of<64, 2>(x3);
     case TILE_2x192T: return GemmCfg<192, 2, false, false, true, false, true>::STAGES;
     case TILE_1x64T: return GemmCfg<64, 1, false, false, true, false, true>::STAGES;
     case TILE_1x128T: return GemmCfg<128, 1, false, false, true, false, true>::STAGES;

@@ -18,14 +18,15 @@ enum TileCfg : int {
   TILE_2x192T = 5, // 256 x 192, CTA pair
   TILE_1x64T = 6,  // 128 x 64, one CTA
   TILE_1x128T = 7, // 128 x 128, one CTA
-  TILE_COUNT = 8
+  TILE_2x64 = 8,   // 256 x 64, CTA pair (narrow outputs: halves the MMA instructions per row)
+  TILE_COUNT = 9
 };
 
-inline int tile_ctas(int cfg) { return (cfg == TILE_2x128 || cfg == TILE_2x256 || cfg == TILE_2x192T) ? 2 : 1; }
-inline bool tile_is_ts(int cfg) { return cfg >= TILE_2x192T; }
+inline int tile_ctas(int cfg) { return (cfg == TILE_2x128 || cfg == TILE_2x256 || cfg == TILE_2x192T || cfg == TILE_2x64) ? 2 : 1; }
+inline bool tile_is_ts(int cfg) { return cfg >= TILE_2x192T && cfg <= TILE_1x128T; }
 inline int tile_bn(int cfg) {
   switch (cfg) {
-    case TILE_1x64: case TILE_1x64T: return 64;
+    case TILE_1x64: case TILE_1x64T: case TILE_2x64: return 64;
     case TILE_1x128: case TILE_2x128: case TILE_1x128T: return 128;
     case TILE_2x192T: return 192;
     default: return 256;
@@ -118,6 +119,7 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
     case TILE_2x192T: return launch_one<GemmCfg<192, 2, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
     case TILE_1x64T:  return launch_one<GemmCfg<64, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream);  \
     case TILE_1x128T: return launch_one<GemmCfg<128, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
+    case TILE_2x64:  return launch_one<GemmCfg<64, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream);  \
     default: return cudaErrorInvalidValue;                                                     \
   }
 

@@ -259,7 +259,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   if (Cfg::REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_MOVERS));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop so that addresses, coordinates and descriptors are
+    // computed once per warp in the uniform datapath (TMA and MMA instructions take their
+    // operands from uniform registers); only the instructions themselves are single-lane.
+    {
+      const bool leader = lane == 0;
       uint32_t it = 0;  // k-blocks issued so far, over all tiles: stage = it % STAGES
       bool alive = true;
       // Tiles are walked in groups of 8 row-tiles across all column-tiles, so an A panel is
@@ -267,20 +271,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       // keep A in L2, let B go first (without this the two panels, together larger than
       // L2, evict each other in exactly the order they are needed again).
       const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : 0ull;
-      const uint64_t pol_b = p.l2_hints ? l2_policy_evict_first() : 0ull;
+      const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
-            give_up(ROLE_TMA, s, i);
+            if (leader) give_up(ROLE_TMA, s, i);
             alive = false;
             break;
           }
-          TRACE(0, it);
+          if (leader) TRACE(0, it);
           const uint32_t full = smem_u32(&bar_full_tma[s]);
-          mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
+          if (leader) mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
           int k0 = (w.kb0 + i) * Cfg::BK;
           const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
@@ -298,26 +302,27 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             const int r = w.row0 - n * ohw;
             const int oh = r / p.conv_OW;
             const int ow = r - oh * p.conv_OW;
-            tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
-                               oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
-                               static_cast<uint16_t>(fh), pol_a);
+            if (leader)
+              tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
+                                 oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
+                                 static_cast<uint16_t>(fh), pol_a);
           } else if (Cfg::A_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BM / 32; ++j)
-              tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch, pol_a);
+              if (leader) tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch, pol_a);
           } else {
-            tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
+            if (leader) tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
           }
           if (Cfg::B_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-              tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);
+              if (leader) tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);
           } else {
-            tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch, pol_b);
+            if (leader) tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch, pol_b);
           }
         }
       }
-      if (abort_flag) {
+      if (leader && abort_flag) {
         // Let copies already in flight land before shared memory is released:
         // wait (bounded) for the barrier of every stage still outstanding.
         const uint32_t lo = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
@@ -335,7 +340,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     // Measured cost to this thread: ~70 cycles per MMA, ~125 per commit, a few hundred per
     // barrier wait, against at most 1536 cycles of execution per k-block - so commits are
     // kept to the minimum (one paired commit instead of two for a CTA pair).
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
+      const bool leader = lane == 0;   // the one thread that issues (and whose commits track) the MMAs
       constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN && !Cfg::TS, Cfg::B_MN);
       constexpr uint32_t A_LBO = Cfg::A_MN ? 4096u : 16u;
       constexpr uint32_t B_LBO = Cfg::B_MN ? 4096u : 16u;
@@ -356,17 +362,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           const uint32_t ph = (it / STAGES) & 1;
           const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
           if (!mbar_wait<CTAS == 2>(ready, ph, &abort_flag)) {
-            give_up(ROLE_MMA, s, i);
+            if (leader) give_up(ROLE_MMA, s, i);
             alive = false;
             break;
           }
-          TRACE(3, it);
+          if (leader) TRACE(3, it);
           const bool chunk_start = (i % kc) == 0;
           const int buf = ch & 1;
           if (chunk_start) {
             // the n-th use of a buffer waits for the (n-1)-th drain; the first use passes
             if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[buf]), ((ch >> 1) & 1u) ^ 1u, &abort_flag)) {
-              give_up(ROLE_MMA_TMEM, buf, i);
+              if (leader) give_up(ROLE_MMA_TMEM, buf, i);
               alive = false;
               break;
             }
@@ -388,16 +394,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             for (int j = 0; j < Cfg::BK / 8; ++j) {
               const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
               const uint64_t db_lo = make_smem_desc(b_hi + Cfg::B_LO_OFFSET + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-              umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo, idesc, 1u);
+              if (leader) umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+              if (leader) umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo, idesc, 1u);
             }
 #pragma unroll
             for (int j = 0; j < Cfg::BK / 8; ++j) {
               const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi, idesc, 1u);
+              if (leader) umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi, idesc, 1u);
             }
-            if (CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
-            else umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
+            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
+            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
           } else {
             if (X3) {
 #pragma unroll
@@ -406,26 +412,26 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
                 const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
                 const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
                 const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-                umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-                umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+                if (leader) umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+                if (leader) umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
               }
             }
 #pragma unroll
             for (int j = 0; j < Cfg::BK / 8; ++j) {
               const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
               const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
+              if (leader) umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
             }
           }
-          TRACE(4, it);
+          if (leader) TRACE(4, it);
           // The stage may be refilled once these MMAs have read it.
-          if (CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[s]));
-          else umma_commit<CTAS>(smem_u32(&bar_empty[s]));
+          if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[s]));
+          if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_empty[s]));
           if (chunk_end) {
-            if (CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[buf]));
-            else umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
-            ++ch;
+            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[buf]));
+            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
           }
+          if (chunk_end) ++ch;
         }
       }
     }

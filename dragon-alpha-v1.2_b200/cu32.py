@@ -26,7 +26,8 @@ ERROR_NAMES = {
 }
 
 TILE_NAMES = {0: "128x64", 1: "128x128", 2: "128x256", 3: "256x128 pair", 4: "256x256 pair",
-              5: "256x192 pair, A via TMEM", 6: "128x64, A via TMEM", 7: "128x128, A via TMEM"}
+              5: "256x192 pair, A via TMEM", 6: "128x64, A via TMEM", 7: "128x128, A via TMEM",
+              8: "256x64 pair"}
 
 
 class CudaException(RuntimeError):

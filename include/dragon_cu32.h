@@ -200,9 +200,10 @@ CU32_API int cu32_conv3D_W1(const int64_t* streams, int length, const float* dX,
  *   "kc_fast"  same for the TF32 fast mode (default 4)
  *   "tile"     force a tile configuration: 0..4 = 128x64, 128x128, 128x256, 256x128 pair,
  *              256x256 pair (operands from shared memory); 5..7 = 256x192 pair, 128x64,
- *              128x128 with the A operand fed through TMEM; -1 = choose from the shape (default)
- *   "l2hint"   1 = load A with evict-last and B with evict-first L2 priority when the tile
- *              grid re-uses an A panel across column tiles (default), 0 = no hints
+ *              128x128 with the A operand fed through TMEM; 8 = 256x64 pair; -1 = choose from the
+ *              shape (default)
+ *   "l2hint"   L2 eviction priority of the operand loads: 0 = none (default; measured best),
+ *              1 = A evict-last and B evict-first, 2 = A evict-last only
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
 CU32_API int cu32_tune(const char* key, int value);
 CU32_API int cu32_get_tune(const char* key, int* value);

@@ -106,7 +106,7 @@ def test_matmul_remainder_sweep(pkg, O, cuda):
         assert O.same_percent(C, G.ref_matmul(O, form, A, B, N, M, K), 1e-5) >= 0.999
 
 
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6, 7, 8])
 def test_every_tile_configuration(pkg, O, cuda, tile):
     pkg.cu32.tune("tile", tile)
     for form in ("AB", "T1", "T2"):
