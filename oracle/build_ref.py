@@ -72,7 +72,7 @@ def build(reference: Path, names: list[str], force: bool = False) -> list[Path]:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("DRAGON_REFERENCE_TREE", "/root/reference"))
     ap.add_argument("--conv", action="store_true", help="also build Cuda_conv3D (about 25 minutes)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()

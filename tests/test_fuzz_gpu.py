@@ -1,0 +1,95 @@
+"""Seeded random shapes through every operator family: small enough for a full FP64 check of
+each case, chosen to hit the corners of the persistent tile loop (fewer tiles than CTAs, one
+tile per CTA pair, ragged last tiles in both directions, K shorter than one k-block, split-K
+slices without work, batches of one, odd strides and paddings)."""
+import numpy as np
+import pytest
+import torch
+
+import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+
+def _acc(O, C, C64, what):
+    assert np.isfinite(C).all(), what
+    rep = O.report(C, C64)
+    assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (what, rep)
+
+
+def test_fuzz_matmul(pkg, O, cuda):
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        form = ["AB", "T1", "T2"][case % 3]
+        N = int(rng.integers(1, 200)) * 4
+        M = int(rng.integers(1, 200)) * 4
+        K = int(rng.choice([4, 8, 28, 32, 36, 64, 100, 256, 516, 1000]))
+        if case % 7 == 0:
+            N = int(rng.choice([4, 8, 128, 256, 1024, 2052]))
+        sa, sb = G.mm_shapes(form, N, M, K)
+        A = rng.standard_normal(sa).astype(np.float32)
+        B = rng.standard_normal(sb).astype(np.float32)
+        if case % 4 == 3 and K >= 64:
+            GZ = int(rng.choice([2, 3, 5, 8, 16]))
+            C, _, _ = G.matmul_sk(pkg, form, A, B, N, M, K, GZ)
+            _acc(O, C, G.f64_matmul(O, form, A, B), f"SK {form} {N}x{M}x{K} GZ={GZ}")
+        else:
+            C = G.matmul(pkg, form, A, B, N, M, K)
+            _acc(O, C, G.f64_matmul(O, form, A, B), f"{form} {N}x{M}x{K}")
+
+
+def test_fuzz_batched(pkg, O, cuda):
+    bm = pkg.cu32.Cuda_batchMatMul
+    rng = np.random.default_rng(7)
+    s = [G.stream()]
+    for case in range(24):
+        Batch = int(rng.choice([1, 2, 3, 7, 16, 150, 301]))
+        N = int(rng.integers(1, 140))
+        M = int(rng.integers(1, 70)) * 4
+        K = int(rng.integers(1, 40)) * 4
+        kind = case % 3
+        if kind == 0:
+            AK = K + int(rng.choice([0, 4, 8]))
+            A = np.zeros((Batch, N, AK), np.float32); A[:, :, :K] = rng.standard_normal((Batch, N, K))
+            B = rng.standard_normal((Batch, K, M)).astype(np.float32)
+            out = G.Out(Batch * N * M)
+            dA, dB = G.dev(A), G.dev(B)
+            bm.batchMatMul(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, M, K, AK)
+            _acc(O, out.host((Batch, N, M)), O.f64.batchMatMul(A, B, K), f"bmm {Batch}x{N}x{M}x{K}/{AK}")
+        elif kind == 1:
+            AN = (N + 3) // 4 * 4 + int(rng.choice([0, 4]))
+            A = np.zeros((Batch, K, AN), np.float32); A[:, :, :N] = rng.standard_normal((Batch, K, N))
+            B = rng.standard_normal((Batch, K, M)).astype(np.float32)
+            out = G.Out(Batch * N * M)
+            dA, dB = G.dev(A), G.dev(B)
+            bm.batchMatMulT1(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, AN, M, K)
+            _acc(O, out.host((Batch, N, M)), O.f64.batchMatMulT1(A, B, N), f"bmmT1 {Batch}x{N}x{M}x{K}/{AN}")
+        else:
+            BM = max(1, M - int(rng.choice([0, 1, 2, 3])))
+            A = rng.standard_normal((Batch, N, K)).astype(np.float32)
+            B = rng.standard_normal((Batch, BM, K)).astype(np.float32)
+            out = G.Out(Batch * N * M)
+            dA, dB = G.dev(A), G.dev(B)
+            bm.batchMatMulT2(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, Batch, N, M, BM, K)
+            C = out.host((Batch, N, M))
+            _acc(O, C, O.f64.batchMatMulT2(A, B, M), f"bmmT2 {Batch}x{N}x{BM}/{M}x{K}")
+            assert np.all(C[:, :, BM:] == 0)
+    G.check_status(pkg)
+
+
+def test_fuzz_conv(pkg, O, cuda):
+    rng = np.random.default_rng(99)
+    for case in range(20):
+        N = int(rng.choice([4, 8, 12]))
+        IH, IW = int(rng.integers(5, 20)), int(rng.integers(5, 20))
+        IC = int(rng.choice([4, 8, 12, 32, 36, 64, 68]))
+        OC = int(rng.choice([4, 8, 36, 64, 132, 260]))
+        FH, FW = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        FH, FW = min(FH, IH), min(FW, IW)
+        sh, sw = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        ph, pw = int(rng.integers(0, FH)), int(rng.integers(0, FW))
+        X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+        W = (rng.standard_normal((OC, FH, FW, IC)) / np.sqrt(FH * FW * IC)).astype(np.float32)
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        Y = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
+        _acc(O, Y, O.f64.conv3D(X, W, OH, OW, sh, sw, ph, pw), f"conv N{N} {IH}x{IW}x{IC}->{OC} f{FH}x{FW} s{sh},{sw} p{ph},{pw}")
