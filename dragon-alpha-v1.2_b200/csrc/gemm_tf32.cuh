@@ -157,10 +157,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, STAGES = Cfg::STAGES, CW = Cfg::CW;
   constexpr bool X3 = Cfg::X3;
   constexpr bool RELAY = X3 || CTAS == 2;  // MMA waits on the splitters' barrier
+  // Shared-memory split: the tensor core drops the low 13 mantissa bits of an FP32 operand
+  // by itself, so the tile as TMA wrote it already is the "hi" operand (hi = trunc(x)) and
+  // only lo = tf32(x - trunc(x)) has to be written.
+  constexpr bool TRUNC_HI = X3 && !Cfg::TS;
+  // Issue the hi*hi instructions of a k-block as soon as its tiles have landed, before the
+  // split is done.  Off: adding the small cross terms to an already large accumulator costs
+  // accuracy (the accumulator truncates after every instruction), and the issuing thread
+  // stalls on the split in the middle of the k-block.
+  constexpr bool EARLY_HH = false;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full_tma[8];
   __shared__ __align__(8) uint64_t bar_full_split[8];
+  __shared__ __align__(8) uint64_t bar_full_split_peer[8];   // CTA pairs: the odd CTA's splitters arrive here
+  __shared__ __align__(8) uint64_t bar_landed[8];            // CTA pairs: both CTAs' raw tiles have landed
   __shared__ __align__(8) uint64_t bar_empty[8];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
@@ -224,7 +235,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     abort_flag = 0;
     for (int s = 0; s < 8; ++s) {
       mbar_init(smem_u32(&bar_full_tma[s]), 1);
-      mbar_init(smem_u32(&bar_full_split[s]), Cfg::SPLIT_WARPS * CTAS);
+      mbar_init(smem_u32(&bar_full_split[s]), Cfg::SPLIT_WARPS);
+      mbar_init(smem_u32(&bar_full_split_peer[s]), Cfg::SPLIT_WARPS);
+      mbar_init(smem_u32(&bar_landed[s]), CTAS);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -264,7 +277,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     // operands from uniform registers); only the instructions themselves are single-lane.
     {
       const bool leader = lane == 0;
-      uint32_t it = 0;  // k-blocks issued so far, over all tiles: stage = it % STAGES
+      uint32_t it = 0;  // k-blocks issued so far, over all tiles
+      uint32_t s = 0, ph = 0;  // stage = it % STAGES and its phase parity, carried as counters
       bool alive = true;
       // Tiles are walked in groups of 8 row-tiles across all column-tiles, so an A panel is
       // re-used by every column-tile of the sweep while B streams through once per group:
@@ -274,9 +288,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
-        for (int i = 0; i < w.nkb; ++i, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == STAGES) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
             if (leader) give_up(ROLE_TMA, s, i);
             alive = false;
@@ -351,27 +363,42 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       constexpr uint32_t B_LT = Cfg::B_MN ? SMEM_LAYOUT_SW128_32B : SMEM_LAYOUT_SW128;
       constexpr uint32_t A_KSTEP = Cfg::A_MN ? 1024u : 32u;  // bytes per 8 elements of K
       constexpr uint32_t B_KSTEP = Cfg::B_MN ? 1024u : 32u;
-      uint32_t it = 0;  // k-blocks consumed so far, over all tiles
-      uint32_t ch = 0;  // chunks started so far: TMEM buffer = ch & 1
+      // This loop's scalar bookkeeping is on the critical path (one warp, dependent
+      // instructions, ~8 cycles each): ring positions are carried as counters instead of
+      // being re-derived with divisions every k-block.
+      uint32_t it = 0;    // k-blocks consumed so far, over all tiles
+      uint32_t ch = 0;    // chunks started so far: TMEM buffer = ch & 1
+      uint32_t s = 0, ph = 0;   // pipeline stage and its phase parity
+      uint32_t kk = 0;    // k-blocks already in the current chunk
       bool alive = true;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
+        kk = 0;
         for (int i = 0; i < w.nkb; ++i, ++it) {
-          const bool chunk_end = ((i + 1) % kc) == 0 || i + 1 == w.nkb;
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          const uint32_t ready = RELAY ? smem_u32(&bar_full_split[s]) : smem_u32(&bar_full_tma[s]);
-          if (!mbar_wait<CTAS == 2>(ready, ph, &abort_flag)) {
+          const bool chunk_start = kk == 0;
+          ++kk;
+          const bool chunk_end = kk == static_cast<uint32_t>(kc) || i + 1 == w.nkb;
+          if (chunk_end) kk = 0;
+          // First wait: EARLY_HH - the raw tiles are in place (in both CTAs of a pair);
+          // otherwise - the operands are complete (split, or relayed by the splitters).
+          const uint32_t ready = EARLY_HH ? (CTAS == 2 ? smem_u32(&bar_landed[0]) : smem_u32(&bar_full_tma[0])) + s * 8u
+                               : (RELAY ? smem_u32(&bar_full_split[0]) : smem_u32(&bar_full_tma[0])) + s * 8u;
+          if (!mbar_wait<EARLY_HH && CTAS == 2>(ready, ph, &abort_flag)) {
             if (leader) give_up(ROLE_MMA, s, i);
             alive = false;
             break;
           }
-          if (leader) TRACE(3, it);
-          const bool chunk_start = (i % kc) == 0;
-          const int buf = ch & 1;
+          if (leader) TRACE(6, it);
+          if (!EARLY_HH && CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
+            if (leader) give_up(ROLE_MMA, 50 + s, i);
+            alive = false;
+            break;
+          }
+          if (leader && !EARLY_HH) TRACE(3, it);
+          const uint32_t buf = ch & 1u;
           if (chunk_start) {
             // the n-th use of a buffer waits for the (n-1)-th drain; the first use passes
-            if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[buf]), ((ch >> 1) & 1u) ^ 1u, &abort_flag)) {
+            if (!mbar_wait<CTAS == 2>(smem_u32(&bar_tmem_empty[0]) + buf * 8u, ((ch >> 1) & 1u) ^ 1u, &abort_flag)) {
               if (leader) give_up(ROLE_MMA_TMEM, buf, i);
               alive = false;
               break;
@@ -380,7 +407,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           tc_fence_after();
           const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_hi = a_hi + Cfg::A_BYTES;
-          const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
+          const uint32_t d = tmem_base + buf * BN;
           // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
           // instruction, an error of up to one ulp of the *accumulator*.  Issuing all the
           // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
@@ -404,6 +431,36 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             }
             if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
             if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
+          } else if (EARLY_HH) {
+            // hi*hi straight from the tiles as they landed ...
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j) {
+              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              if (leader) umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
+            }
+            // ... then the two cross terms once the lo tiles are written (both CTAs of a pair)
+            if (!mbar_wait(smem_u32(&bar_full_split[0]) + s * 8u, ph, &abort_flag)) {
+              if (leader) give_up(ROLE_MMA, 100 + s, i);
+              alive = false;
+              break;
+            }
+            if (CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
+              if (leader) give_up(ROLE_MMA, 50 + s, i);
+              alive = false;
+              break;
+            }
+            if (leader) TRACE(3, it);
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j) {
+              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
+              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
+              if (leader) umma_tf32<CTAS>(d, da_lo, db_hi, idesc, 1u);
+              if (leader) umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+            }
           } else {
             if (X3) {
 #pragma unroll
@@ -425,12 +482,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           }
           if (leader) TRACE(4, it);
           // The stage may be refilled once these MMAs have read it.
-          if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[s]));
-          if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_empty[s]));
+          if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[0]) + s * 8u);
+          if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_empty[0]) + s * 8u);
           if (chunk_end) {
-            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[buf]));
-            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_tmem_full[buf]));
+            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[0]) + buf * 8u);
+            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_tmem_full[0]) + buf * 8u);
           }
+          if (++s == static_cast<uint32_t>(STAGES)) { s = 0; ph ^= 1u; }
+          if (leader && !Cfg::TS) TRACE(7, it);
           if (chunk_end) ++ch;
         }
       }
@@ -446,16 +505,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       constexpr int NVEC = Cfg::HI_BYTES / 16;
       constexpr int LO_OFF = Cfg::TS ? Cfg::B_LO_OFFSET : Cfg::HI_BYTES;
       uint32_t it = 0;
+      uint32_t s = 0, ph = 0;  // stage = it % STAGES and its phase parity, carried as counters
       bool alive = true;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
-        for (int i = 0; i < w.nkb; ++i, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == STAGES) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
             if (lane == 0) give_up(ROLE_SPLIT, s, i);
             alive = false;
             break;
+          }
+          if (EARLY_HH && CTAS == 2 && warp == Cfg::SPLIT_WARP0 && lane == 0) {
+            if (rank != 0) mbar_arrive_cluster(leader_addr(&bar_landed[s]));
+            else mbar_arrive(smem_u32(&bar_landed[s]));
           }
           if (!Cfg::TS && warp == 2 && lane == 0) TRACE(1, it);
           if (Cfg::TS && warp == 4 && lane == 0) TRACE(6, it);
@@ -504,6 +566,29 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             tmem_wait_st();
             if (warp == 4 && lane == 0) TRACE(2, it);
             tc_fence_before();
+          } else if (TRUNC_HI) {
+            // lo = tf32(x - trunc(x)); x itself stays where TMA put it.  Loads are issued in
+            // groups of four ahead of the arithmetic so their latencies overlap.
+            constexpr int PER = (NVEC + NST - 1) / NST;
+#pragma unroll
+            for (int b = 0; b < PER; b += 4) {
+              float4 x[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int v = st + (b + u) * NST;
+                if (b + u < PER && v < NVEC) x[u] = lds128(hi_base + v * 16);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int v = st + (b + u) * NST;
+                if (b + u < PER && v < NVEC) {
+                  float4 l;
+                  l.x = rn_tf32(x[u].x - trunc_tf32(x[u].x)); l.y = rn_tf32(x[u].y - trunc_tf32(x[u].y));
+                  l.z = rn_tf32(x[u].z - trunc_tf32(x[u].z)); l.w = rn_tf32(x[u].w - trunc_tf32(x[u].w));
+                  sts128(hi_base + v * 16 + LO_OFF, l);
+                }
+              }
+            }
           } else if (X3) {
 #pragma unroll 4
             for (int v = VEC0 + st; v < NVEC; v += NST) {
@@ -516,7 +601,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               sts128(addr, h);
               sts128(addr + LO_OFF, l);
             }
-            if (warp == 2 && lane == 0 && !Cfg::TS) TRACE(6, it);
             fence_proxy_async_smem();
           }
           __syncwarp();
@@ -524,7 +608,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           if (Cfg::TS && warp == 4 && lane == 0) TRACE(7, it);
           if (lane == 0) {
             if (CTAS == 2 && rank != 0)
-              mbar_arrive_cluster(leader_addr(&bar_full_split[s]));
+              mbar_arrive_cluster(leader_addr(&bar_full_split_peer[s]));
             else
               mbar_arrive(smem_u32(&bar_full_split[s]));
           }

@@ -362,5 +362,11 @@ __device__ __forceinline__ float rn_tf32(float x) {
   return __uint_as_float(r);
 }
 
+// What the tensor core itself makes of an FP32 operand under kind::tf32: the low 13
+// mantissa bits are ignored (truncation toward zero).
+__device__ __forceinline__ float trunc_tf32(float x) {
+  return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
+
 }  // namespace ptx
 }  // namespace dragon

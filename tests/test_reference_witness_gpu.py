@@ -44,7 +44,7 @@ def test_matmul_forms_against_reference_kernels(pkg, O, cuda):
             C64 = G.f64_matmul(O, form, A, B)
             e_ref, e_our = O.frob_rel(R, C64), O.frob_rel(C, C64)
             assert e_ref <= 2e-6, (form, N, M, K, e_ref)          # the witness itself is sane
-            assert e_our <= 1e-6 and e_our <= max(e_ref, 4e-7), (form, N, M, K, e_our, e_ref)
+            assert e_our <= 1e-6 and e_our <= max(e_ref, 5e-7), (form, N, M, K, e_our, e_ref)
             assert O.frob_rel(C, R) <= 2e-6
 
 
