@@ -102,12 +102,12 @@ static int make_map3(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1
 #ifdef DRAGON_TRACE
 static long long* g_trace_buf = nullptr;
 extern "C" __attribute__((visibility("default"))) int cu32_trace_enable(void) {
-  if (!g_trace_buf && cudaMalloc(&g_trace_buf, sizeof(long long) * 8 * 256) != cudaSuccess) return -1;
-  return static_cast<int>(cudaMemset(g_trace_buf, 0, sizeof(long long) * 8 * 256));
+  if (!g_trace_buf && cudaMalloc(&g_trace_buf, sizeof(long long) * 16 * 256) != cudaSuccess) return -1;
+  return static_cast<int>(cudaMemset(g_trace_buf, 0, sizeof(long long) * 16 * 256));
 }
 extern "C" __attribute__((visibility("default"))) int cu32_trace_read(long long* out) {
   cudaDeviceSynchronize();
-  return static_cast<int>(cudaMemcpy(out, g_trace_buf, sizeof(long long) * 8 * 256, cudaMemcpyDeviceToHost));
+  return static_cast<int>(cudaMemcpy(out, g_trace_buf, sizeof(long long) * 16 * 256, cudaMemcpyDeviceToHost));
 }
 #endif
 

@@ -74,7 +74,7 @@ struct GemmParams {
 #ifdef DRAGON_TRACE
 // Timeline instrumentation for pipeline studies: CTA 0 records clock64() at the hand-over
 // points of its first 256 k-blocks into GemmParams::trace.  Not compiled into the product.
-#define TRACE(ev, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 256u) p.trace[(ev) * 256 + (idx)] = clock64(); } while (0)
+#define TRACE(ev, idx) do { if (p.trace && blockIdx.x < 2 && (idx) < 256u) p.trace[(blockIdx.x * 8 + (ev)) * 256 + (idx)] = clock64(); } while (0)
 #else
 #define TRACE(ev, idx) do { } while (0)
 #endif
@@ -161,17 +161,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   // by itself, so the tile as TMA wrote it already is the "hi" operand (hi = trunc(x)) and
   // only lo = tf32(x - trunc(x)) has to be written.
   constexpr bool TRUNC_HI = X3 && !Cfg::TS;
-  // Issue the hi*hi instructions of a k-block as soon as its tiles have landed, before the
-  // split is done.  Off: adding the small cross terms to an already large accumulator costs
-  // accuracy (the accumulator truncates after every instruction), and the issuing thread
-  // stalls on the split in the middle of the k-block.
-  constexpr bool EARLY_HH = false;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full_tma[8];
   __shared__ __align__(8) uint64_t bar_full_split[8];
   __shared__ __align__(8) uint64_t bar_full_split_peer[8];   // CTA pairs: the odd CTA's splitters arrive here
-  __shared__ __align__(8) uint64_t bar_landed[8];            // CTA pairs: both CTAs' raw tiles have landed
   __shared__ __align__(8) uint64_t bar_empty[8];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
@@ -237,7 +231,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       mbar_init(smem_u32(&bar_full_tma[s]), 1);
       mbar_init(smem_u32(&bar_full_split[s]), Cfg::SPLIT_WARPS);
       mbar_init(smem_u32(&bar_full_split_peer[s]), Cfg::SPLIT_WARPS);
-      mbar_init(smem_u32(&bar_landed[s]), CTAS);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -294,44 +287,50 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             alive = false;
             break;
           }
-          if (leader) TRACE(0, it);
           const uint32_t full = smem_u32(&bar_full_tma[s]);
-          if (leader) mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
           int k0 = (w.kb0 + i) * Cfg::BK;
           const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          // im2col coordinates: k-block -> (filter tap, block of 32 channels inside the tap);
+          // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
+          // rows and images inside the tensor map's traversal box.
+          int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0;
           if (Cfg::IM2COL) {
-            // k-block -> (filter tap, block of 32 channels inside the tap)
             const int tap = (w.kb0 + i) / p.conv_icb;
-            const int ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
-            const int fh = tap / p.conv_FW;
-            const int fw = tap - fh * p.conv_FW;
+            ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
+            fh = tap / p.conv_FW;
+            fw = tap - fh * p.conv_FW;
             k0 = tap * p.conv_IC + ic0;  // position in the filter's (fh, fw, ic) axis
-            // row0 addresses output pixel (n, oh, ow); the run of 128 pixels wraps
-            // over rows and images inside the tensor map's traversal box.
             const int ohw = p.conv_OH * p.conv_OW;
-            const int n = w.row0 / ohw;
+            n = w.row0 / ohw;
             const int r = w.row0 - n * ohw;
-            const int oh = r / p.conv_OW;
-            const int ow = r - oh * p.conv_OW;
-            if (leader)
+            oh = r / p.conv_OW;
+            ow = r - oh * p.conv_OW;
+          }
+          // one single-thread region for all copies of the k-block
+          if (elect_one()) {
+            TRACE(0, it);
+            mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
+            if (Cfg::IM2COL) {
               tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
                                  oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
                                  static_cast<uint16_t>(fh), pol_a);
-          } else if (Cfg::A_MN) {
+            } else if (Cfg::A_MN) {
 #pragma unroll
-            for (int j = 0; j < Cfg::BM / 32; ++j)
-              if (leader) tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch, pol_a);
-          } else {
-            if (leader) tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
-          }
-          if (Cfg::B_MN) {
+              for (int j = 0; j < Cfg::BM / 32; ++j)
+                tma_load_3d(a_dst + j * 4096, &p.tmA, full, w.row0 + 32 * j, k0, w.batch, pol_a);
+            } else {
+              tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
+            }
+            if (Cfg::B_MN) {
 #pragma unroll
-            for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-              if (leader) tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);
-          } else {
-            if (leader) tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch, pol_b);
+              for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
+                tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);
+            } else {
+              tma_load_3d(b_dst, &p.tmB, full, k0, w.bcol0, w.batch, pol_b);
+            }
           }
+          __syncwarp();
         }
       }
       if (leader && abort_flag) {
@@ -379,22 +378,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           ++kk;
           const bool chunk_end = kk == static_cast<uint32_t>(kc) || i + 1 == w.nkb;
           if (chunk_end) kk = 0;
-          // First wait: EARLY_HH - the raw tiles are in place (in both CTAs of a pair);
-          // otherwise - the operands are complete (split, or relayed by the splitters).
-          const uint32_t ready = EARLY_HH ? (CTAS == 2 ? smem_u32(&bar_landed[0]) : smem_u32(&bar_full_tma[0])) + s * 8u
-                               : (RELAY ? smem_u32(&bar_full_split[0]) : smem_u32(&bar_full_tma[0])) + s * 8u;
-          if (!mbar_wait<EARLY_HH && CTAS == 2>(ready, ph, &abort_flag)) {
+          const uint32_t ready = (RELAY ? smem_u32(&bar_full_split[0]) : smem_u32(&bar_full_tma[0])) + s * 8u;
+          if (!mbar_wait(ready, ph, &abort_flag)) {
             if (leader) give_up(ROLE_MMA, s, i);
             alive = false;
             break;
           }
           if (leader) TRACE(6, it);
-          if (!EARLY_HH && CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
+          if (CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
             if (leader) give_up(ROLE_MMA, 50 + s, i);
             alive = false;
             break;
           }
-          if (leader && !EARLY_HH) TRACE(3, it);
+          if (leader) TRACE(3, it);
           const uint32_t buf = ch & 1u;
           if (chunk_start) {
             // the n-th use of a buffer waits for the (n-1)-th drain; the first use passes
@@ -413,83 +409,57 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           // small lo*hi / hi*lo products of the k-block first, while the accumulator of a
           // fresh chunk is still small, keeps those truncations negligible; only the four
           // hi*hi instructions then round at full magnitude.
-          if (Cfg::TS) {
-            const uint32_t slot = it & 1u;
-            const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + slot * Cfg::A_SLOT_COLS;
-            const uint32_t ta_lo = ta_hi + Cfg::BK;
-#pragma unroll
-            for (int j = 0; j < Cfg::BK / 8; ++j) {
-              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::B_LO_OFFSET + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              if (leader) umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-              if (leader) umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo, idesc, 1u);
-            }
-#pragma unroll
-            for (int j = 0; j < Cfg::BK / 8; ++j) {
-              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              if (leader) umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi, idesc, 1u);
-            }
-            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
-            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
-          } else if (EARLY_HH) {
-            // hi*hi straight from the tiles as they landed ...
-#pragma unroll
-            for (int j = 0; j < Cfg::BK / 8; ++j) {
-              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              if (leader) umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-            }
-            // ... then the two cross terms once the lo tiles are written (both CTAs of a pair)
-            if (!mbar_wait(smem_u32(&bar_full_split[0]) + s * 8u, ph, &abort_flag)) {
-              if (leader) give_up(ROLE_MMA, 100 + s, i);
-              alive = false;
-              break;
-            }
-            if (CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
-              if (leader) give_up(ROLE_MMA, 50 + s, i);
-              alive = false;
-              break;
-            }
-            if (leader) TRACE(3, it);
-            tc_fence_after();
-#pragma unroll
-            for (int j = 0; j < Cfg::BK / 8; ++j) {
-              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-              const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              if (leader) umma_tf32<CTAS>(d, da_lo, db_hi, idesc, 1u);
-              if (leader) umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
-            }
-          } else {
-            if (X3) {
+          //
+          // All instructions of the k-block sit in ONE elect.sync region: the compiler then
+          // knows a single thread runs it and feeds the MMAs from uniform registers - measured
+          // 24 cycles per issued MMA against 50-60 with a (lane == 0) test on each.  Successive
+          // descriptors differ only in the start-address field (low word, 16-byte units).
+          if (elect_one()) {
+            constexpr uint64_t A_STEP = A_KSTEP >> 4, B_STEP = B_KSTEP >> 4;
+            const uint64_t db_hi0 = make_smem_desc(b_hi, B_LBO, B_SBO, B_LT);
+            const uint32_t first = chunk_start ? 0u : 1u;
+            if (Cfg::TS) {
+              const uint32_t slot = it & 1u;
+              const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + slot * Cfg::A_SLOT_COLS;
+              const uint32_t ta_lo = ta_hi + Cfg::BK;
+              const uint64_t db_lo0 = make_smem_desc(b_hi + Cfg::B_LO_OFFSET, B_LBO, B_SBO, B_LT);
 #pragma unroll
               for (int j = 0; j < Cfg::BK / 8; ++j) {
-                const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-                const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-                const uint64_t da_lo = make_smem_desc(a_hi + Cfg::HI_BYTES + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-                const uint64_t db_lo = make_smem_desc(b_hi + Cfg::HI_BYTES + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-                if (leader) umma_tf32<CTAS>(d, da_lo, db_hi, idesc, (chunk_start && j == 0) ? 0u : 1u);
-                if (leader) umma_tf32<CTAS>(d, da_hi, db_lo, idesc, 1u);
+                umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi0 + j * B_STEP, idesc, j == 0 ? first : 1u);
+                umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo0 + j * B_STEP, idesc, 1u);
               }
-            }
 #pragma unroll
-            for (int j = 0; j < Cfg::BK / 8; ++j) {
-              const uint64_t da_hi = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_LT);
-              const uint64_t db_hi = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_LT);
-              if (leader) umma_tf32<CTAS>(d, da_hi, db_hi, idesc, (!X3 && chunk_start && j == 0) ? 0u : 1u);
+              for (int j = 0; j < Cfg::BK / 8; ++j)
+                umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi0 + j * B_STEP, idesc, 1u);
+              if (CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
+              else umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
+            } else {
+              const uint64_t da_hi0 = make_smem_desc(a_hi, A_LBO, A_SBO, A_LT);
+              if (X3) {
+                const uint64_t da_lo0 = make_smem_desc(a_hi + Cfg::HI_BYTES, A_LBO, A_SBO, A_LT);
+                const uint64_t db_lo0 = make_smem_desc(b_hi + Cfg::HI_BYTES, B_LBO, B_SBO, B_LT);
+#pragma unroll
+                for (int j = 0; j < Cfg::BK / 8; ++j) {
+                  umma_tf32<CTAS>(d, da_lo0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, j == 0 ? first : 1u);
+                  umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_lo0 + j * B_STEP, idesc, 1u);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < Cfg::BK / 8; ++j)
+                umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, (!X3 && j == 0) ? first : 1u);
             }
+            TRACE(4, it);
+            // The stage may be refilled once these MMAs have read it.
+            if (CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[0]) + s * 8u);
+            else umma_commit<CTAS>(smem_u32(&bar_empty[0]) + s * 8u);
+            if (chunk_end) {
+              if (CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[0]) + buf * 8u);
+              else umma_commit<CTAS>(smem_u32(&bar_tmem_full[0]) + buf * 8u);
+            }
+            if (!Cfg::TS) TRACE(7, it);
           }
-          if (leader) TRACE(4, it);
-          // The stage may be refilled once these MMAs have read it.
-          if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[0]) + s * 8u);
-          if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_empty[0]) + s * 8u);
-          if (chunk_end) {
-            if (leader && CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[0]) + buf * 8u);
-            if (leader && CTAS != 2) umma_commit<CTAS>(smem_u32(&bar_tmem_full[0]) + buf * 8u);
-          }
+          __syncwarp();
           if (++s == static_cast<uint32_t>(STAGES)) { s = 0; ph ^= 1u; }
-          if (leader && !Cfg::TS) TRACE(7, it);
           if (chunk_end) ++ch;
         }
       }
@@ -514,10 +484,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             if (lane == 0) give_up(ROLE_SPLIT, s, i);
             alive = false;
             break;
-          }
-          if (EARLY_HH && CTAS == 2 && warp == Cfg::SPLIT_WARP0 && lane == 0) {
-            if (rank != 0) mbar_arrive_cluster(leader_addr(&bar_landed[s]));
-            else mbar_arrive(smem_u32(&bar_landed[s]));
           }
           if (!Cfg::TS && warp == 2 && lane == 0) TRACE(1, it);
           if (Cfg::TS && warp == 4 && lane == 0) TRACE(6, it);

@@ -30,9 +30,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Arrive on a barrier that lives in another CTA of the cluster (address from mapa).
+// Default semantics (release at CTA scope), on purpose: a cluster-scope release was measured
+// to hold the arriving warp for 1300-1800 cycles per call, which made the odd CTA of a pair
+// the pace-setter of the whole pipeline.  What the arrival publishes here is always data in
+// the arriving CTA's OWN shared or tensor memory, complete (fence.proxy.async /
+// tcgen05.wait) before the arrive is sent, and read there by hardware that the waiting
+// thread starts only afterwards.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
@@ -360,6 +365,14 @@ __device__ __forceinline__ float rn_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
+}
+
+// True in exactly one lane of a converged warp.  Code under it is a single-thread region the
+// compiler can recognise as such (unlike a test of the lane number).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 
 // What the tensor core itself makes of an FP32 operand under kind::tf32: the low 13
