@@ -134,7 +134,8 @@ static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;
   // the TMEM-operand tiles (last three) are not chosen automatically yet
-  static const double rate[TILE_COUNT] = {75.0, 133.0, 164.0, 122.0, 230.0, 0.0, 0.0, 0.0, 0.0};
+  // measured matMul 8192^3 rates per tile shape, TFLOP/s (order of the TileCfg enum)
+  static const double rate[TILE_COUNT] = {123.0, 180.0, 200.0, 228.0, 278.0, 0.0, 0.0, 0.0, 140.0};
   int best = TILE_1x128;
   double best_t = 1e300;
   for (int t = 0; t < TILE_COUNT; ++t) {

@@ -533,24 +533,32 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             if (warp == 4 && lane == 0) TRACE(2, it);
             tc_fence_before();
           } else if (TRUNC_HI) {
-            // lo = tf32(x - trunc(x)); x itself stays where TMA put it.  Loads are issued in
-            // groups of four ahead of the arithmetic so their latencies overlap.
+            // lo = tf32(x - trunc(x)); x itself stays where TMA put it.  The loads of the
+            // next group of four vectors are in flight while this group is converted and stored.
             constexpr int PER = (NVEC + NST - 1) / NST;
+            constexpr int G = 3;
+            float4 x[2][G];
 #pragma unroll
-            for (int b = 0; b < PER; b += 4) {
-              float4 x[4];
+            for (int u = 0; u < G; ++u) {
+              const int v = st + u * NST;
+              if (u < PER && v < NVEC) x[0][u] = lds128(hi_base + v * 16);
+            }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int v = st + (b + u) * NST;
-                if (b + u < PER && v < NVEC) x[u] = lds128(hi_base + v * 16);
+            for (int b = 0; b < PER; b += G) {
+              const int cur = (b / G) & 1;
+#pragma unroll
+              for (int u = 0; u < G; ++u) {
+                const int v = st + (b + G + u) * NST;
+                if (b + G + u < PER && v < NVEC) x[cur ^ 1][u] = lds128(hi_base + v * 16);
               }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
+              for (int u = 0; u < G; ++u) {
                 const int v = st + (b + u) * NST;
                 if (b + u < PER && v < NVEC) {
+                  const float4 xv = x[cur][u];
                   float4 l;
-                  l.x = rn_tf32(x[u].x - trunc_tf32(x[u].x)); l.y = rn_tf32(x[u].y - trunc_tf32(x[u].y));
-                  l.z = rn_tf32(x[u].z - trunc_tf32(x[u].z)); l.w = rn_tf32(x[u].w - trunc_tf32(x[u].w));
+                  l.x = rn_tf32(xv.x - trunc_tf32(xv.x)); l.y = rn_tf32(xv.y - trunc_tf32(xv.y));
+                  l.z = rn_tf32(xv.z - trunc_tf32(xv.z)); l.w = rn_tf32(xv.w - trunc_tf32(xv.w));
                   sts128(hi_base + v * 16 + LO_OFF, l);
                 }
               }
