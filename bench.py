@@ -45,7 +45,7 @@ UNIT = "TFLOP/s"
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
 # one ncu capture of the same workload; the captures are summarised in profiles/).
 NCU_TRAFFIC_BYTES = {
-    "c2_ab": 2.54e9,     # profiles/gemm_tf32_matMul_AB_8192_traffic.md
+    "c2_ab": 2.53e9,     # profiles/gemm_tf32_matMul_AB_8192_traffic.md
 }
 
 

@@ -550,6 +550,34 @@ int cu32_conv3D_GemmR_texture_SGM(const int64_t* s, int n, const float* X, int I
   if (GM_slice <= 0) return CU32_E_ARG;
   return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
 }
+// The reference's V2 and Im2col-Winograd natives: same result through the same implicit GEMM.
+int cu32_conv3DV2(int, const int64_t* s, int n, const float* X, int IH, int IW, const float* W, int FH, int FW,
+                  float* Y, int OH, int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmV2R(int, const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                        const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC,
+                        int sh, int sw, int ph, int pw) {
+  (void)CW;
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+#define DRAGON_WINOGRAD_ALIAS(name)                                                                        \
+  int name(int, const int64_t* s, int n, const float* X, int IH, int IW, const float* W, const float* CW,  \
+           int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC, int ph, int pw) {              \
+    (void)CW;                                                                                              \
+    return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, 1, 1, ph, pw);                 \
+  }
+#define DRAGON_WINOGRAD_ALIAS_SGM(name)                                                                    \
+  int name(int, const int64_t* s, int n, const float* X, int IH, int IW, const float* W, const float* CW,  \
+           int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC, int ph, int pw, int GM_slice) {\
+    (void)CW;                                                                                              \
+    if (GM_slice <= 0) return CU32_E_ARG;                                                                  \
+    return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, 1, 1, ph, pw);                 \
+  }
+DRAGON_WINOGRAD_ALIAS(cu32_conv3D_Im2col_Winograd_s8_R_texture)
+DRAGON_WINOGRAD_ALIAS_SGM(cu32_conv3D_Im2col_WinogradR_s8_texture_SGM)
+DRAGON_WINOGRAD_ALIAS(cu32_conv3D_Im2col_Winograd_s16_R_texture)
+DRAGON_WINOGRAD_ALIAS_SGM(cu32_conv3D_Im2col_WinogradR_s16_texture_SGM)
 int cu32_conv3D_GemmR_W1(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
                          const float* CW, float* Y, int N, int IC, int OC) {
   (void)CW;

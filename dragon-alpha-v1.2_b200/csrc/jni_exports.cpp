@@ -163,6 +163,53 @@ CONV_GEMMR(conv3D_1GemmR, cu32_conv3D_GemmR)
 CONV_GEMMR(conv3D_1GemmR_1texture, cu32_conv3D_GemmR_texture)
 CONV_GEMMR_SGM(conv3D_1GemmR_1SGM, cu32_conv3D_GemmR_SGM)
 CONV_GEMMR_SGM(conv3D_1GemmR_1texture_1SGM, cu32_conv3D_GemmR_texture_SGM)
+// The V2 and Im2col-Winograd natives (reference: Cuda_conv3D/A.cu:89-111, :390-412, :429-637): same
+// arguments, same result; the Winograd ones tell Java whether they handled the shape - always.
+JNIEXPORT void JNICALL JNAME(conv3D, conv3DV2)(JNIEnv* env, jclass, jboolean useTexture, jlongArray streams,
+                                               jint length, jlong dX, jint IH, jint IW, jlong dW, jint FH,
+                                               jint FW, jlong dY, jint OH, jint OW, jint N, jint IC, jint OC,
+                                               jint sh, jint sw, jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3DV2(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), FH, FW, mptr(dY), OH, OW, N, IC,
+                          OC, sh, sw, ph, pw));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmV2R)(JNIEnv* env, jclass, jboolean useTexture,
+                                                      jlongArray streams, jint length, jlong dX, jint IH,
+                                                      jint IW, jlong dW, jlong dCW, jint FH, jint FW, jlong dY,
+                                                      jint OH, jint OW, jint N, jint IC, jint OC, jint sh,
+                                                      jint sw, jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_GemmV2R(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW,
+                                mptr(dY), OH, OW, N, IC, OC, sh, sw, ph, pw));
+}
+#define CONV_WINOGRAD(jname, cname)                                                                        \
+  JNIEXPORT jboolean JNICALL JNAME(conv3D, jname)(JNIEnv* env, jclass, jboolean useTexture,                \
+                                                  jlongArray streams, jint length, jlong dX, jint IH,      \
+                                                  jint IW, jlong dW, jlong dCW, jint FH, jint FW,          \
+                                                  jlong dY, jint OH, jint OW, jint N, jint IC, jint OC,    \
+                                                  jint ph, jint pw) {                                      \
+    Streams s(env, streams, length);                                                                       \
+    const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW,      \
+                         mptr(dY), OH, OW, N, IC, OC, ph, pw);                                             \
+    done(env, rc);                                                                                         \
+    return rc == 0 ? 1 : 0;                                                                                \
+  }
+#define CONV_WINOGRAD_SGM(jname, cname)                                                                    \
+  JNIEXPORT jboolean JNICALL JNAME(conv3D, jname)(JNIEnv* env, jclass, jboolean useTexture,                \
+                                                  jlongArray streams, jint length, jlong dX, jint IH,      \
+                                                  jint IW, jlong dW, jlong dCW, jint FH, jint FW,          \
+                                                  jlong dY, jint OH, jint OW, jint N, jint IC, jint OC,    \
+                                                  jint ph, jint pw, jint GM_slice) {                       \
+    Streams s(env, streams, length);                                                                       \
+    const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW,      \
+                         mptr(dY), OH, OW, N, IC, OC, ph, pw, GM_slice);                                   \
+    done(env, rc);                                                                                         \
+    return rc == 0 ? 1 : 0;                                                                                \
+  }
+CONV_WINOGRAD(conv3D_1Im2col_1Winograd_1s8_1R_1texture, cu32_conv3D_Im2col_Winograd_s8_R_texture)
+CONV_WINOGRAD_SGM(conv3D_1Im2col_1WinogradR_1s8_1texture_1SGM, cu32_conv3D_Im2col_WinogradR_s8_texture_SGM)
+CONV_WINOGRAD(conv3D_1Im2col_1Winograd_1s16_1R_1texture, cu32_conv3D_Im2col_Winograd_s16_R_texture)
+CONV_WINOGRAD_SGM(conv3D_1Im2col_1WinogradR_1s16_1texture_1SGM, cu32_conv3D_Im2col_WinogradR_s16_texture_SGM)
 JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmR_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length,
                                                         jlong dX, jint IH, jint IW, jlong dW, jlong dCW,
                                                         jlong dY, jint N, jint IC, jint OC) {

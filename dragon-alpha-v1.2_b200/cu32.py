@@ -80,6 +80,12 @@ SIGNATURES = {
     "cu32_conv3D_GemmR_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 10,
     "cu32_conv3D_GemmR_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_conv3D_GemmR_W1_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_conv3DV2": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_GemmV2R": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_conv3D_Im2col_Winograd_s8_R_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_conv3D_Im2col_WinogradR_s8_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_conv3D_Im2col_Winograd_s16_R_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_conv3D_Im2col_WinogradR_s16_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 8,
     "cu32_conv3D": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
     "cu32_conv3D_texture": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
     "cu32_conv3D_np": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
@@ -352,6 +358,53 @@ class Cuda_conv3D:
     def conv3D_W1(streamArray, length, dX, IH, IW, dW, dY, N, IC, OC):
         s, n = _streams(streamArray, length)
         _check(load().cu32_conv3D_W1(s, n, _p(dX), IH, IW, _p(dW), _p(dY), N, IC, OC), "conv3D_W1")
+
+    # ---- the V2 / Im2col-Winograd natives (Cuda_conv3D.java; Cuda_conv3D/A.cu:89-111, :390-637): same
+    # contraction under the names the Java engine prefers with its default flags
+    @staticmethod
+    def conv3DV2(useTexture, streamArray, length, dX, IH, IW, dW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3DV2(int(bool(useTexture)), s, n, _p(dX), IH, IW, _p(dW), FH, FW, _p(dY), OH, OW, N,
+                                    IC, OC, sh, sw, ph, pw), "conv3DV2")
+
+    @staticmethod
+    def conv3D_GemmV2R(useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw,
+                       ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmV2R(int(bool(useTexture)), s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW,
+                                          _p(dY), OH, OW, N, IC, OC, sh, sw, ph, pw), "conv3D_GemmV2R")
+
+    @staticmethod
+    def _winograd(name, useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, ph, pw,
+                  *gm_slice) -> bool:
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_" + name)(int(bool(useTexture)), s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW,
+                                               _p(dY), OH, OW, N, IC, OC, ph, pw, *gm_slice), name)
+        return True   # the Java native returns "handled"; every shape is
+
+    @staticmethod
+    def conv3D_Im2col_Winograd_s8_R_texture(useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH,
+                                            OW, N, IC, OC, ph, pw) -> bool:
+        return Cuda_conv3D._winograd("conv3D_Im2col_Winograd_s8_R_texture", useTexture, streamArray, length, dX, IH,
+                                     IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, ph, pw)
+
+    @staticmethod
+    def conv3D_Im2col_WinogradR_s8_texture_SGM(useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH,
+                                               OW, N, IC, OC, ph, pw, GM_slice) -> bool:
+        return Cuda_conv3D._winograd("conv3D_Im2col_WinogradR_s8_texture_SGM", useTexture, streamArray, length, dX,
+                                     IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, ph, pw, GM_slice)
+
+    @staticmethod
+    def conv3D_Im2col_Winograd_s16_R_texture(useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH,
+                                             OW, N, IC, OC, ph, pw) -> bool:
+        return Cuda_conv3D._winograd("conv3D_Im2col_Winograd_s16_R_texture", useTexture, streamArray, length, dX, IH,
+                                     IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, ph, pw)
+
+    @staticmethod
+    def conv3D_Im2col_WinogradR_s16_texture_SGM(useTexture, streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH,
+                                                OW, N, IC, OC, ph, pw, GM_slice) -> bool:
+        return Cuda_conv3D._winograd("conv3D_Im2col_WinogradR_s16_texture_SGM", useTexture, streamArray, length, dX,
+                                     IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, ph, pw, GM_slice)
 
     max_grid = 65535
     grid_slice = 32768

@@ -191,6 +191,41 @@ CU32_API int cu32_conv3D_np(const int64_t* streams, int length, const float* dX,
 CU32_API int cu32_conv3D_W1(const int64_t* streams, int length, const float* dX, int IH, int IW,
                    const float* dW, float* dY, int N, int IC, int OC);
 
+/* The reference's other forward-convolution natives, as further names for the same implicit GEMM.
+ * With default flags the Java engine sends most stride-1 3x3..9x9 convolutions to these
+ * (CudaFloat32EngineBase.java:2211-2255, :2300-2385) rather than to conv3D_GemmR; exporting them
+ * makes the library a drop-in for default-configured models.  They compute exactly what
+ * cu32_conv3D / cu32_conv3D_GemmR compute (the reference's V2 and Im2col-Winograd algorithms differ
+ * only in rounding); useTexture and GM_slice are accepted and ignored.
+ *   cu32_conv3DV2                              replaces JNI conv3DV2 (A.cu:89-111)
+ *   cu32_conv3D_GemmV2R                        replaces JNI conv3D_GemmV2R (A.cu:390-412)
+ *   cu32_conv3D_Im2col_Winograd_s8_R_texture   replaces JNI conv3D_Im2col_Winograd_s8_R_texture (A.cu:429-455)
+ *   cu32_conv3D_Im2col_WinogradR_s8_texture_SGM   ... (A.cu:458-530)
+ *   cu32_conv3D_Im2col_Winograd_s16_R_texture  ... (A.cu:539-565)
+ *   cu32_conv3D_Im2col_WinogradR_s16_texture_SGM  ... (A.cu:568-637)
+ * The Winograd natives are stride-1 only (no sh, sw) and return a jboolean "handled" to Java; here
+ * every shape is handled, so the JNI shim returns true whenever the return code is 0. */
+CU32_API int cu32_conv3DV2(int useTexture, const int64_t* streams, int length, const float* dX, int IH, int IW,
+                  const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
+                  int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_GemmV2R(int useTexture, const int64_t* streams, int length, const float* dX, int IH,
+                        int IW, const float* dW, const float* dCW, int FH, int FW, float* dY, int OH,
+                        int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_conv3D_Im2col_Winograd_s8_R_texture(int useTexture, const int64_t* streams, int length,
+                        const float* dX, int IH, int IW, const float* dW, const float* dCW, int FH,
+                        int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw);
+CU32_API int cu32_conv3D_Im2col_WinogradR_s8_texture_SGM(int useTexture, const int64_t* streams, int length,
+                        const float* dX, int IH, int IW, const float* dW, const float* dCW, int FH,
+                        int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw,
+                        int GM_slice);
+CU32_API int cu32_conv3D_Im2col_Winograd_s16_R_texture(int useTexture, const int64_t* streams, int length,
+                        const float* dX, int IH, int IW, const float* dW, const float* dCW, int FH,
+                        int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw);
+CU32_API int cu32_conv3D_Im2col_WinogradR_s16_texture_SGM(int useTexture, const int64_t* streams, int length,
+                        const float* dX, int IH, int IW, const float* dW, const float* dCW, int FH,
+                        int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw,
+                        int GM_slice);
+
 /* ------------------------------------------------------------------ library control
  * No counterpart in the reference (its only native-side switch is a compile-time macro). */
 

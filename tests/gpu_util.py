@@ -108,6 +108,22 @@ def conv(pkg, entry, X, W, sh, sw, ph, pw, OH=None, OW=None, GM_slice=None):
         if entry.endswith("SGM"):
             args.append(GM_slice or 128)
         getattr(cv, entry)(*args)
+    elif entry in ("conv3D_GemmV2R", "conv3D_Im2col_Winograd_s8_R_texture", "conv3D_Im2col_WinogradR_s8_texture_SGM",
+                   "conv3D_Im2col_Winograd_s16_R_texture", "conv3D_Im2col_WinogradR_s16_texture_SGM"):
+        dCW = torch.empty(FH * FW * IC * OC, device="cuda")
+        cv.kernel_remode(s[0], dW.data_ptr(), dCW.data_ptr(), FH, FW, OC, IC)
+        args = [True, s, 1, dX.data_ptr(), IH, IW, dW.data_ptr(), dCW.data_ptr(), FH, FW, out.ptr, OH, OW, N, IC, OC]
+        if entry == "conv3D_GemmV2R":
+            args += [sh, sw]
+        else:
+            assert sh == 1 and sw == 1, "the Winograd natives are stride-1 only"
+        args += [ph, pw]
+        if entry.endswith("SGM"):
+            args.append(GM_slice or 128)
+        handled = getattr(cv, entry)(*args)
+        assert entry == "conv3D_GemmV2R" or handled is True
+    elif entry == "conv3DV2":
+        cv.conv3DV2(False, s, 1, dX.data_ptr(), IH, IW, dW.data_ptr(), FH, FW, out.ptr, OH, OW, N, IC, OC, sh, sw, ph, pw)
     elif entry in ("conv3D", "conv3D_texture"):
         getattr(cv, entry)(s, 1, dX.data_ptr(), IH, IW, dW.data_ptr(), FH, FW, out.ptr, OH, OW, N, IC, OC, sh, sw, ph, pw)
     elif entry == "conv3D_np":

@@ -110,7 +110,7 @@ def _header_symbols():
 def test_library_exports_every_declared_symbol(pkg):
     lib = pkg.cu32.load()
     names = _header_symbols()
-    assert len(names) >= 33
+    assert len(names) >= 39
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/dragon_cu32.h but not exported"
     # the ctypes table covers the same surface
@@ -130,7 +130,10 @@ def test_jni_symbols_exported(pkg):
     want_conv = {"conv3D_kernel_1remode", "conv3D_conv3D", "conv3D_conv3D_1texture", "conv3D_conv3D_1np",
                  "conv3D_conv3D_1W1", "conv3D_conv3D_1GemmR", "conv3D_conv3D_1GemmR_1texture",
                  "conv3D_conv3D_1GemmR_1SGM", "conv3D_conv3D_1GemmR_1texture_1SGM", "conv3D_conv3D_1GemmR_1W1",
-                 "conv3D_conv3D_1GemmR_1W1_1SGM"}
+                 "conv3D_conv3D_1GemmR_1W1_1SGM", "conv3D_conv3DV2", "conv3D_conv3D_1GemmV2R",
+                 "conv3D_conv3D_1Im2col_1Winograd_1s8_1R_1texture", "conv3D_conv3D_1Im2col_1WinogradR_1s8_1texture_1SGM",
+                 "conv3D_conv3D_1Im2col_1Winograd_1s16_1R_1texture",
+                 "conv3D_conv3D_1Im2col_1WinogradR_1s16_1texture_1SGM"}
     missing = (want_matmul | want_bmm | want_conv) - syms
     assert not missing, missing
 

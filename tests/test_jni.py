@@ -134,6 +134,17 @@ def test_jni_matmul_and_conv_on_gpu(pkg, O, cuda):
         1, 1, 1, 1)
     rep = O.report(out.host((4, 8, 8, 8)), O.f64.conv3D(X, W, 8, 8, 1, 1, 1, 1))
     assert jni.thrown is None and rep["frob"] <= 1e-6, rep
+    # an Im2col-Winograd native: jboolean "handled" comes back true, same bits as conv3D_GemmR
+    base = out.host((4, 8, 8, 8)).copy()
+    out2 = G.Out(4 * 8 * 8 * 8)
+    wino = _fn(lib, "conv3D_conv3D_1Im2col_1Winograd_1s8_1R_1texture",
+               [ctypes.c_uint8, c_void_p, c_int32, c_int64, c_int32, c_int32, c_int64, c_int64, c_int32, c_int32, c_int64]
+               + [c_int32] * 7)
+    wino.restype = ctypes.c_uint8
+    handled = wino(jni.env, None, 1, ARRAY_HANDLE, 1, dX.data_ptr(), 8, 8, dW.data_ptr(), dCW.data_ptr(), 3, 3, out2.ptr,
+                   8, 8, 4, 16, 8, 1, 1)
+    assert handled == 1 and jni.thrown is None
+    assert np.array_equal(out2.host((4, 8, 8, 8)), base)
     torch.cuda.synchronize()
     assert np.array_equal(dCW.cpu().numpy().reshape(3, 3, 16, 8), O.ref_loops.kernel_remode(W))
     G.check_status(pkg)

@@ -325,6 +325,44 @@ def test_conv_entry_point_aliases(pkg, O, cuda):
         assert_accurate(O, G.conv(pkg, entry, X, W1, 1, 1, 0, 0), Y1, entry)
 
 
+V2_AND_WINOGRAD_ENTRIES = ("conv3DV2", "conv3D_GemmV2R", "conv3D_Im2col_Winograd_s8_R_texture",
+                           "conv3D_Im2col_WinogradR_s8_texture_SGM", "conv3D_Im2col_Winograd_s16_R_texture",
+                           "conv3D_Im2col_WinogradR_s16_texture_SGM")
+
+
+@pytest.mark.parametrize("case", [
+    # N, IH, IW, IC, OC, FH, FW, ph, pw  - stride-1 shapes the Java engine sends to the Im2col-Winograd natives:
+    # IC % 8 == 0, N*OH >= 32, FW + OW > 8 (s8: 2 <= FW <= 9) or > 16 (s16: 7 <= FW <= 9)
+    (4, 12, 12, 16, 64, 3, 3, 1, 1),
+    (2, 16, 20, 8, 72, 5, 5, 2, 2),
+    (2, 18, 18, 8, 32, 7, 7, 3, 3),
+    (2, 16, 16, 8, 32, 9, 9, 4, 4),
+    (4, 10, 14, 24, 64, 2, 4, 0, 1),
+])
+def test_v2_and_winograd_entry_points(pkg, O, cuda, case):
+    """The reference's other forward-conv natives are the same convolution (they differ from GemmR only
+    in rounding), so here they must return GemmR's bits and meet the same FP64 tolerance."""
+    N, IH, IW, IC, OC, FH, FW, ph, pw = case
+    rng = np.random.default_rng(23)
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * np.sqrt(2.0 / (FH * FW * IC))).astype(np.float32)
+    OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+    base = G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, ph, pw)
+    assert_accurate(O, base, O.f64.conv3D(X, W, OH, OW, 1, 1, ph, pw), f"GemmR {case}")
+    for entry in V2_AND_WINOGRAD_ENTRIES:
+        assert np.array_equal(G.conv(pkg, entry, X, W, 1, 1, ph, pw), base), entry
+
+
+def test_v2_entry_points_strided(pkg, O, cuda):
+    rng = np.random.default_rng(24)
+    X = rng.standard_normal((4, 17, 15, 12)).astype(np.float32)
+    W = rng.standard_normal((40, 3, 3, 12)).astype(np.float32) * 0.1
+    base = G.conv(pkg, "conv3D_GemmR", X, W, 2, 2, 1, 1)
+    assert_accurate(O, base, O.f64.conv3D(X, W, 9, 8, 2, 2, 1, 1), "GemmR s2")
+    for entry in ("conv3DV2", "conv3D_GemmV2R"):
+        assert np.array_equal(G.conv(pkg, entry, X, W, 2, 2, 1, 1), base), entry
+
+
 def test_kernel_remode_bit_exact(pkg, O, cuda):
     rng = np.random.default_rng(19)
     for (OC, FH, FW, IC) in [(4, 1, 1, 4), (12, 3, 3, 8), (256, 3, 3, 64), (36, 5, 3, 20), (33, 2, 2, 7)]:
