@@ -74,6 +74,18 @@ def matmul_sk(pkg, form, A, B, N, M, K, GZ, summary=True):
     return C, C0, Cbuf
 
 
+def bmm_t2(pkg, Q, Kt):
+    """C[b] = Q[b] * Kt[b]^T through batchMatMulT2 (Q [Batch, N, K], Kt [Batch, M, K])."""
+    Batch, N, K = Q.shape
+    M = Kt.shape[1]
+    dQ, dK = dev(Q), dev(Kt)
+    out = Out(Batch * N * M)
+    pkg.cu32.Cuda_batchMatMul.batchMatMulT2([stream()], 1, dQ.data_ptr(), dK.data_ptr(), out.ptr, Batch, N, M, M, K)
+    C = out.host((Batch, N, M))
+    check_status(pkg)
+    return C
+
+
 def f64_matmul(O, form, A, B):
     return {"AB": O.f64.matMul, "T1": O.f64.matMulT1, "T2": O.f64.matMulT2}[form](A, B)
 
