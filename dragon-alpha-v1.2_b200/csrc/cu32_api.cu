@@ -124,6 +124,8 @@ struct GemmCall {
   int gz;                   // split-K slices (1 = none)
   bool x3;                  // FP32-accurate (true) or single-pass TF32
   cudaStream_t stream;
+  const float* bias;        // optional row vector (n_store floats) added in the epilogue; needs gz == 1, batch == 1
+  int bias_width;           // true width of the rows: columns beyond it are stored as zeros
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -158,6 +160,11 @@ static int run_gemm(const GemmCall& c) {
   if (c.M <= 0 || c.N <= 0 || c.K <= 0 || c.batch <= 0 || c.gz < 1 || c.gz > 65535) return CU32_E_DIM;
   if ((c.lda & 3) || (c.ldb & 3) || (c.sA & 3) || (c.sB & 3) || !aligned16(c.A) || !aligned16(c.B))
     return CU32_E_ALIGN;
+  if (c.bias) {
+    if (c.gz != 1 || c.batch != 1) return CU32_E_ARG;
+    if (c.bias_width <= 0 || c.bias_width > c.n_store) return CU32_E_DIM;
+    if (!aligned16(c.bias) || (c.n_store & 3)) return CU32_E_ALIGN;
+  }
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
@@ -179,6 +186,8 @@ static int run_gemm(const GemmCall& c) {
 
   p.C = c.C;
   p.Cbuf = c.Cbuf;
+  p.bias = c.bias;
+  p.bias_width = c.bias_width;
   p.ldc = c.ldc;
   p.c_stride = c.sC;
   p.M = c.M;
@@ -200,6 +209,7 @@ static int run_gemm(const GemmCall& c) {
     p.prefetch = d;
   }
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
+  if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;   // the bias is applied on the vector store paths only
   if (p.vec4_ok) {
     // Output maps for the TMA-store epilogue: (columns, rows, batch) with the caller's pitch.
     const uint64_t zs_c = c.gz > 1 ? 1 : nb;
@@ -237,7 +247,8 @@ static int check_streams(const int64_t* streams, int length, cudaStream_t* s0) {
 enum MatForm { FORM_AB, FORM_T1, FORM_T2 };
 
 static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length, int GridZ,
-                      const float* dA, const float* dB, float* dC, float* dCbuf, int N, int M, int K) {
+                      const float* dA, const float* dB, float* dC, float* dCbuf, int N, int M, int K,
+                      const float* dBias = nullptr, int width = 0) {
   cudaStream_t st;
   if (int rc = check_streams(streams, length, &st)) return rc;
   if (N <= 0 || M <= 0 || K <= 0) return CU32_E_DIM;
@@ -249,6 +260,7 @@ static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length,
   c.batch = 1; c.sA = 0; c.sB = 0;
   c.sC = static_cast<long long>(N) * M;  // distance between split-K partial buffers
   c.gz = GridZ; c.x3 = x3; c.stream = st;
+  c.bias = dBias; c.bias_width = width;
   switch (form) {
     case FORM_AB: c.a_mn = false; c.lda = K; c.b_mn = true;  c.ldb = M; break;
     case FORM_T1: c.a_mn = true;  c.lda = N; c.b_mn = true;  c.ldb = M; break;
@@ -258,9 +270,12 @@ static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length,
 }
 
 // ------------------------------------------------------------------ split-K buffer summation
-// C += sum_p Cbuf[p], Kahan-compensated, 4 floats per thread per step.
+// C += sum_p Cbuf[p], Kahan-compensated, 4 floats per thread per step.  BIAS: the sum then takes
+// the bias row (one more FP32 add, exactly what a separate bias kernel would do to the stored
+// sum) and the padding columns (col >= width inside each row of row_len floats) become zero.
+template <bool BIAS>
 __global__ void skbuf_summary_kernel(const float* __restrict__ Cbuf, float* __restrict__ C, int part,
-                                     long long sizeC) {
+                                     long long sizeC, const float* __restrict__ bias, int row_len, int width) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < sizeC;
        i += stride) {
@@ -275,6 +290,14 @@ __global__ void skbuf_summary_kernel(const float* __restrict__ Cbuf, float* __re
         y = v.z - comp.z; t = sum.z + y; comp.z = (t - sum.z) - y; sum.z = t;
         y = v.w - comp.w; t = sum.w + y; comp.w = (t - sum.w) - y; sum.w = t;
       }
+      if (BIAS) {   // row_len is a multiple of 4, so the four elements share a row
+        const int col = static_cast<int>(i % row_len);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col));
+        sum.x = (col + 0 < width) ? sum.x + b.x : 0.f;
+        sum.y = (col + 1 < width) ? sum.y + b.y : 0.f;
+        sum.z = (col + 2 < width) ? sum.z + b.z : 0.f;
+        sum.w = (col + 3 < width) ? sum.w + b.w : 0.f;
+      }
       *reinterpret_cast<float4*>(C + i) = sum;
     } else {
       for (long long j = i; j < sizeC; ++j) {
@@ -284,6 +307,10 @@ __global__ void skbuf_summary_kernel(const float* __restrict__ Cbuf, float* __re
           const float t = sum + y;
           comp = (t - sum) - y;
           sum = t;
+        }
+        if (BIAS) {
+          const int col = static_cast<int>(j % row_len);
+          sum = (col < width) ? sum + bias[col] : 0.f;
         }
         C[j] = sum;
       }
@@ -311,7 +338,7 @@ __global__ void remode_kernel(const float* __restrict__ W, float* __restrict__ C
 // ------------------------------------------------------------------ convolution
 static int conv_any(bool x3, const int64_t* streams, int length, const float* dX, int IH, int IW,
                     const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
-                    int sh, int sw, int ph, int pw) {
+                    int sh, int sw, int ph, int pw, const float* dBias = nullptr, int width = 0) {
   load_env_once();
   cudaStream_t st;
   if (int rc = check_streams(streams, length, &st)) return rc;
@@ -320,6 +347,10 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
       sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
     return CU32_E_DIM;
   if ((IC & 3) || !aligned16(dX) || !aligned16(dW)) return CU32_E_ALIGN;
+  if (dBias) {
+    if (width <= 0 || width > OC) return CU32_E_DIM;
+    if (!aligned16(dBias) || (OC & 3)) return CU32_E_ALIGN;
+  }
   const long long GM = static_cast<long long>(N) * OH * OW;
   const long long GK = static_cast<long long>(FH) * FW * IC;
   if (GM >= (1LL << 31) || GK >= (1LL << 31) || static_cast<long long>(N) * IH * IW * IC >= (1LL << 31))
@@ -333,6 +364,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
     c.M = static_cast<int>(GM); c.N = OC; c.K = IC; c.n_store = OC;
     c.lda = IC; c.ldb = IC; c.ldc = OC; c.a_mn = false; c.b_mn = false;
     c.batch = 1; c.sA = 0; c.sB = 0; c.sC = 0; c.gz = 1; c.x3 = x3; c.stream = st;
+    c.bias = dBias; c.bias_width = width;
     return run_gemm(c);
   }
 
@@ -378,6 +410,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   // Filters W[OC][FH*FW*IC]: reduction axis contiguous.
   if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas, false)) return rc;
 
+  p.bias = dBias; p.bias_width = width;
   p.C = dY; p.Cbuf = nullptr; p.ldc = OC; p.c_stride = 0;
   p.M = static_cast<int>(GM); p.N = OC;
   p.conv_icb = (IC + 31) / 32;
@@ -388,6 +421,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   p.kc = x3 ? g_kc.load() : g_kc_fast.load();
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
+  if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;
   if (p.vec4_ok) {
     if (int rc = make_map3(&p.tmC, dY, OC, static_cast<uint64_t>(GM), 1, OC, static_cast<uint64_t>(GM) * OC, 32, 32, false)) return rc;
     p.tma_store = 1;
@@ -440,18 +474,51 @@ int cu32_matMulT2_mma(const int64_t* s, int n, const float* A, const float* B, f
   return matmul_any(FORM_T2, false, s, n, 1, A, B, C, nullptr, N, M, K);
 }
 
-int cu32_SKbuf_summary(int64_t stream, const float* dCbuf, float* dC, int part, int sizeC) {
+static int summary_any(int64_t stream, const float* dCbuf, float* dC, int part, int sizeC, const float* dBias,
+                       int row_len, int width) {
   if (!dC || (part > 0 && !dCbuf)) return CU32_E_NULL;
   if (part < 0 || sizeC <= 0) return CU32_E_DIM;
   if (!aligned16(dC) || !aligned16(dCbuf) || (sizeC & 3)) return CU32_E_ALIGN;
-  if (part == 0) return CU32_OK;
+  if (dBias) {
+    if (row_len <= 0 || width <= 0 || width > row_len || sizeC % row_len) return CU32_E_DIM;
+    if (!aligned16(dBias) || (row_len & 3)) return CU32_E_ALIGN;
+  } else if (part == 0) {
+    return CU32_OK;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
   const int threads = 256;
   long long blocks = (static_cast<long long>(sizeC) / 4 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
-  skbuf_summary_kernel<<<static_cast<unsigned>(blocks), threads, 0, st>>>(dCbuf, dC, part, sizeC);
+  if (dBias)
+    skbuf_summary_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, st>>>(dCbuf, dC, part, sizeC, dBias,
+                                                                                 row_len, width);
+  else
+    skbuf_summary_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, st>>>(dCbuf, dC, part, sizeC, nullptr,
+                                                                                  4, 4);
   return static_cast<int>(cudaPeekAtLastError());
+}
+
+int cu32_SKbuf_summary(int64_t stream, const float* dCbuf, float* dC, int part, int sizeC) {
+  return summary_any(stream, dCbuf, dC, part, sizeC, nullptr, 0, 0);
+}
+
+// ---- contraction + bias row in one pass (no counterpart among the reference's natives: the Java
+// engine runs Cuda_function.linear_dual2D_row(C, bias, 1, 1, 0) as a second kernel)
+int cu32_matMul_biased(const int64_t* s, int n, const float* A, const float* B, float* C, const float* Bias,
+                       int N, int M, int K, int width) {
+  if (!Bias) return CU32_E_NULL;
+  return matmul_any(FORM_AB, true, s, n, 1, A, B, C, nullptr, N, M, K, Bias, width);
+}
+int cu32_matMul_mma_biased(const int64_t* s, int n, const float* A, const float* B, float* C, const float* Bias,
+                           int N, int M, int K, int width) {
+  if (!Bias) return CU32_E_NULL;
+  return matmul_any(FORM_AB, false, s, n, 1, A, B, C, nullptr, N, M, K, Bias, width);
+}
+int cu32_SKbuf_summary_biased(int64_t stream, const float* dCbuf, float* dC, const float* Bias, int part,
+                              int sizeC, int M, int width) {
+  if (!Bias) return CU32_E_NULL;
+  return summary_any(stream, dCbuf, dC, part, sizeC, Bias, M, width);
 }
 
 // ---- batched
@@ -561,6 +628,13 @@ int cu32_conv3D_GemmR_texture_SGM(const int64_t* s, int n, const float* X, int I
   (void)CW;
   if (GM_slice <= 0) return CU32_E_ARG;
   return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_conv3D_GemmR_biased(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
+                             const float* CW, int FH, int FW, float* Y, int OH, int OW, int N, int IC, int OC,
+                             int sh, int sw, int ph, int pw, const float* Bias, int width) {
+  (void)CW;
+  if (!Bias) return CU32_E_NULL;
+  return conv_any(true, s, n, X, IH, IW, W, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw, Bias, width);
 }
 // The reference's V2 and Im2col-Winograd natives: same result through the same implicit GEMM.
 int cu32_conv3DV2(int, const int64_t* s, int n, const float* X, int IH, int IW, const float* W, int FH, int FW,

@@ -49,6 +49,8 @@ struct GemmParams {
   CUtensorMap tmC;      // output C: dims (N, M, batches), box (32, 32, 1), 128B swizzle
   CUtensorMap tmCbuf;   // split-K partial buffers: dims (N, M, gz-1), same box
   float* C;             // output of batch 0 / split-K slice 0
+  const float* bias;    // optional row vector added to every output row before the store (gz == 1 only)
+  int bias_width;       // columns < bias_width get acc + bias[col]; columns >= bias_width are stored as 0
   float* Cbuf;          // split-K: outputs of slices 1..gz-1, c_stride floats apart
   long long ldc;        // row pitch of C in floats
   long long c_stride;   // floats between consecutive batches (or Cbuf slices)
@@ -117,8 +119,8 @@ struct GemmCfg {
   static constexpr bool REALLOC = CW > 64;   // drainers need > 128 registers
   // register budgets after reallocation (256 threads each side, 64 K registers per SM):
   // the TMEM-writing splitters hold 64 split values, so they keep more than the plain ones
-  static constexpr int REGS_MOVERS = TS ? 96 : 64;
-  static constexpr int REGS_DRAINERS = TS ? 160 : 192;
+  static constexpr int REGS_MOVERS = TS ? 96 : 72;
+  static constexpr int REGS_DRAINERS = TS ? 160 : 184;
   static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN");
   static_assert(TMEM_NEED <= 512, "TMEM");
   static_assert(STAGES >= 2, "stages");
@@ -601,6 +603,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
                 }
               }
             }
+            // the tensor core reads these tiles through the async proxy: without this fence a
+            // store can still be in flight when the MMA that the arrive below releases reads it
+            fence_proxy_async_smem();
           } else if (X3) {
 #pragma unroll 4
             for (int v = VEC0 + st; v < NVEC; v += NST) {
@@ -681,6 +686,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         }
       }
       if (!alive) break;
+      // ---- fused bias row (optional): what the engine's linear_dual2D_row(C, bias, 1, 1, 0) does right
+      // after the product - one FP32 add per element, padding columns forced to zero.  Applied to
+      // each 4-column vector on its way out, so that no more than a few bias values are live.
+      auto with_bias = [&](int j, float4 v) -> float4 {
+        if (p.bias == nullptr) return v;
+        const int c = w.col0 + h * CW + j;   // a multiple of 4, like p.N: all four columns exist or none
+        if (c >= p.N) return v;
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c));
+        v.x = (c + 0 < p.bias_width) ? v.x + b.x : 0.0f;
+        v.y = (c + 1 < p.bias_width) ? v.y + b.y : 0.0f;
+        v.z = (c + 2 < p.bias_width) ? v.z + b.z : 0.0f;
+        v.w = (c + 3 < p.bias_width) ? v.w + b.w : 0.0f;
+        return v;
+      };
       // ---- store; the MMA warp is already filling the TMEM buffers with the next
       // tile's chunks meanwhile
       if (p.tma_store) {
@@ -700,8 +719,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
 #pragma unroll
             for (int c = 0; c < 8; ++c)
               sts128(stg + lane * 128 + ((c ^ (lane & 7)) * 16),
-                     make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1], acc[g * 32 + c * 4 + 2],
-                                 acc[g * 32 + c * 4 + 3]));
+                     with_bias(g * 32 + c * 4, make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1],
+                                                           acc[g * 32 + c * 4 + 2], acc[g * 32 + c * 4 + 3])));
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -719,7 +738,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
 #pragma unroll
             for (int j = 0; j < CW; j += 4) {
               if (j + 3 < ncols) {
-                *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                *reinterpret_cast<float4*>(dst + j) = with_bias(j, make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]));
               } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)

@@ -163,6 +163,35 @@ CONV_GEMMR(conv3D_1GemmR, cu32_conv3D_GemmR)
 CONV_GEMMR(conv3D_1GemmR_1texture, cu32_conv3D_GemmR_texture)
 CONV_GEMMR_SGM(conv3D_1GemmR_1SGM, cu32_conv3D_GemmR_SGM)
 CONV_GEMMR_SGM(conv3D_1GemmR_1texture_1SGM, cu32_conv3D_GemmR_texture_SGM)
+// Contraction + bias row in one pass.  These natives do not exist in the reference's Java classes; a
+// maintainer who wants the fusion declares them and calls them from
+// CudaFloat32EngineBase.matMul_biased / conv3D_biased instead of the two-kernel sequence.
+JNIEXPORT void JNICALL JNAME(matMul, matMul_1biased)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                     jlong dA, jlong dB, jlong dC, jlong dBias, jint N, jint M,
+                                                     jint K, jint width) {
+  Streams s(env, streams, length);
+  done(env, cu32_matMul_biased(s.h, s.n, cptr(dA), cptr(dB), mptr(dC), cptr(dBias), N, M, K, width));
+}
+JNIEXPORT void JNICALL JNAME(matMul, matMul_1mma_1biased)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                          jlong dA, jlong dB, jlong dC, jlong dBias, jint N,
+                                                          jint M, jint K, jint width) {
+  Streams s(env, streams, length);
+  done(env, cu32_matMul_mma_biased(s.h, s.n, cptr(dA), cptr(dB), mptr(dC), cptr(dBias), N, M, K, width));
+}
+JNIEXPORT void JNICALL JNAME(matMul, SKbuf_1summary_1biased)(JNIEnv* env, jclass, jlong stream, jlong dCbuf,
+                                                             jlong dC, jlong dBias, jint part, jint sizeC,
+                                                             jint M, jint width) {
+  done(env, cu32_SKbuf_summary_biased(stream, cptr(dCbuf), mptr(dC), cptr(dBias), part, sizeC, M, width));
+}
+JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmR_1biased)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                            jlong dX, jint IH, jint IW, jlong dW, jlong dCW,
+                                                            jint FH, jint FW, jlong dY, jint OH, jint OW, jint N,
+                                                            jint IC, jint OC, jint sh, jint sw, jint ph, jint pw,
+                                                            jlong dBias, jint width) {
+  Streams s(env, streams, length);
+  done(env, cu32_conv3D_GemmR_biased(s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW, mptr(dY), OH, OW, N,
+                                     IC, OC, sh, sw, ph, pw, cptr(dBias), width));
+}
 // The V2 and Im2col-Winograd natives (reference: Cuda_conv3D/A.cu:89-111, :390-412, :429-637): same
 // arguments, same result; the Winograd ones tell Java whether they handled the shape - always.
 JNIEXPORT void JNICALL JNAME(conv3D, conv3DV2)(JNIEnv* env, jclass, jboolean useTexture, jlongArray streams,

@@ -80,6 +80,10 @@ SIGNATURES = {
     "cu32_conv3D_GemmR_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 10,
     "cu32_conv3D_GemmR_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_conv3D_GemmR_W1_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_conv3D_GemmR_biased": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 9 + [_fp, _I],
     "cu32_conv3DV2": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
     "cu32_conv3D_GemmV2R": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 9,
     "cu32_conv3D_Im2col_Winograd_s8_R_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 7,
@@ -243,6 +247,24 @@ class Cuda_matMul:
     def SKbuf_summary(stream, dCbuf, dC, part, sizeC):
         _check(load().cu32_SKbuf_summary(int(stream), _p(dCbuf), _p(dC), part, sizeC), "SKbuf_summary")
 
+    # ---- contraction + bias row in one pass: what the engine's matMul_biased does with two kernels
+    # (CudaFloat32EngineBase.java:1594-1688); these natives do not exist in the reference
+    @staticmethod
+    def matMul_biased(streamArray, length, dA, dB, dC, dBias, N, M, K, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMul_biased(s, n, _p(dA), _p(dB), _p(dC), _p(dBias), N, M, K, width), "matMul_biased")
+
+    @staticmethod
+    def matMul_mma_biased(streamArray, length, dA, dB, dC, dBias, N, M, K, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_matMul_mma_biased(s, n, _p(dA), _p(dB), _p(dC), _p(dBias), N, M, K, width),
+               "matMul_mma_biased")
+
+    @staticmethod
+    def SKbuf_summary_biased(stream, dCbuf, dC, dBias, part, sizeC, M, width):
+        _check(load().cu32_SKbuf_summary_biased(int(stream), _p(dCbuf), _p(dC), _p(dBias), part, sizeC, M, width),
+               "SKbuf_summary_biased")
+
 
 class Cuda_batchMatMul:
     """Mirror of z.dragon.engine.cuda.impl.math.Cuda_batchMatMul."""
@@ -358,6 +380,15 @@ class Cuda_conv3D:
     def conv3D_W1(streamArray, length, dX, IH, IW, dW, dY, N, IC, OC):
         s, n = _streams(streamArray, length)
         _check(load().cu32_conv3D_W1(s, n, _p(dX), IH, IW, _p(dW), _p(dY), N, IC, OC), "conv3D_W1")
+
+    @staticmethod
+    def conv3D_GemmR_biased(streamArray, length, dX, IH, IW, dW, dCW, FH, FW, dY, OH, OW, N, IC, OC, sh, sw, ph, pw,
+                            dBias, width):
+        """conv3D_GemmR plus the bias row of conv3D_biased (CudaFloat32EngineBase.java:2389-2542) in one
+        pass; not a native of the reference."""
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_conv3D_GemmR_biased(s, n, _p(dX), IH, IW, _p(dW), _p(dCW), FH, FW, _p(dY), OH, OW, N, IC,
+                                               OC, sh, sw, ph, pw, _p(dBias), width), "conv3D_GemmR_biased")
 
     # ---- the V2 / Im2col-Winograd natives (Cuda_conv3D.java; Cuda_conv3D/A.cu:89-111, :390-637): same
     # contraction under the names the Java engine prefers with its default flags

@@ -226,6 +226,28 @@ CU32_API int cu32_conv3D_Im2col_WinogradR_s16_texture_SGM(int useTexture, const 
                         int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw,
                         int GM_slice);
 
+/* ------------------------------------------------------------------ contraction + bias row
+ * No counterpart among the reference's natives.  The Java engine's matMul_biased / conv3D_biased
+ * (CudaFloat32EngineBase.java:1594-1688, :2389-2542) run the contraction and then, as a second
+ * kernel on the same stream, Cuda_function.linear_dual2D_row(C, Bias, row_lengthv, 1, 1, 0, C,
+ * lengthv, width, stride) (Cuda_function/type1_linear_dual2D_row.cuh:41-70): every row gets the
+ * bias vector added and the padding columns (width <= col < stride) are zeroed.  These entry points
+ * do both in one pass: the add happens on the FP32 value the contraction would have stored, so the
+ * result has the same bits as the two-kernel sequence, and one read and one write of C are saved.
+ *   Bias: M (resp. OC) floats, 16-byte aligned; width: true row width, 0 < width <= M (resp. OC).
+ * Split-K: run cu32_matMulSK as before and replace SKbuf_summary + linear_dual2D_row by
+ * cu32_SKbuf_summary_biased (part may be 0: then it is the bias add alone). */
+CU32_API int cu32_matMul_biased(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                       const float* dBias, int N, int M, int K, int width);
+CU32_API int cu32_matMul_mma_biased(const int64_t* streams, int length, const float* dA, const float* dB,
+                           float* dC, const float* dBias, int N, int M, int K, int width);
+CU32_API int cu32_SKbuf_summary_biased(int64_t stream, const float* dCbuf, float* dC, const float* dBias,
+                              int part, int sizeC, int M, int width);
+CU32_API int cu32_conv3D_GemmR_biased(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                             const float* dW, const float* dCW, int FH, int FW, float* dY, int OH,
+                             int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
+                             const float* dBias, int width);
+
 /* ------------------------------------------------------------------ library control
  * No counterpart in the reference (its only native-side switch is a compile-time macro). */
 

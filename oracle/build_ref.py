@@ -6,6 +6,8 @@ where they lie; nothing is copied into this repository):
   libref_matmul.so   Cuda_matMul:      CPU check loops (test.cuh) + SIMT kernels/dispatchers
   libref_bmm.so      Cuda_batchMatMul: same
   libref_conv.so     Cuda_conv3D:      same (about 25 minutes; only with --conv)
+  libref_function.so Cuda_function:    only linear_dual2D_row, the bias-row add that follows the
+                                       contractions in matMul_biased / conv3D_biased (seconds)
 
 The CPU loops pin oracle/cu32_oracle.c (tests/test_oracle.py compares them bit for bit) and
 serve as the timed CPU baseline of the benchmark; the GPU dispatchers give the reference's
@@ -29,6 +31,7 @@ PROJECTS = {
     "matmul": ("ref_wrap_matmul.cu", "Cuda_matMul/Cuda_matMul", "libref_matmul.so"),
     "bmm": ("ref_wrap_bmm.cu", "Cuda_batchMatMul/Cuda_batchMatMul", "libref_bmm.so"),
     "conv": ("ref_wrap_conv.cu", "Cuda_conv3D/Cuda_conv3D", "libref_conv.so"),
+    "function": ("ref_wrap_function.cu", "Cuda_function/Cuda_function", "libref_function.so"),
 }
 
 # The conv project was written on a case-insensitive file system: these includes differ in
@@ -76,6 +79,6 @@ if __name__ == "__main__":
     ap.add_argument("--conv", action="store_true", help="also build Cuda_conv3D (about 25 minutes)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
-    names = ["matmul", "bmm"] + (["conv"] if a.conv else [])
+    names = ["matmul", "bmm", "function"] + (["conv"] if a.conv else [])
     for p in build(Path(a.reference), names, a.force):
         print(p)

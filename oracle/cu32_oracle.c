@@ -12,6 +12,8 @@
  *                                        Cuda_batchMatMul/test.cuh:69-89
  *   buf_summary (Kahan)                  Cuda_matMul/Cuda_matMul/SKbufsum.cuh:29-68
  *   filter remode W[OC,FH,FW,IC] -> CW[FH,FW,IC,OC]   Cuda_conv3D/conv3D_kernel_remode_V1.cuh:50-196
+ *   linear_dual2D_row (the bias-row add the engine applies right after matMul / conv3D;
+ *   a GPU kernel, restated element by element)        Cuda_function/Cuda_function/type1_linear_dual2D_row.cuh:41-70
  * Loop order and accumulation type follow the reference exactly (k outermost, FP32 "+=" into
  * C), so that on the same inputs the results are bit-identical to the reference routines
  * compiled with the same compiler flags; oracle/build_ref.py builds those routines from the
@@ -172,6 +174,21 @@ void oracle_buf_summary(const float* Cbuf, float* C, int part, int sizeC) {
       v = t;
     }
     C[i] = v;
+  }
+}
+
+/* Y[i] = alpha*X1[i] + beta*X2[i % row_lengthv] + gamma for every element of the padded
+ * [height][stride] matrix, then zero where the column (i % stride) is at or beyond width.
+ * With the coefficients the engine uses for a bias add (1, 1, 0) every product is exact and
+ * the result is the single rounding of X1 + X2, whatever the contraction into FMAs. */
+void oracle_linear_dual2D_row(const float* X1, const float* X2, int row_lengthv, float alpha, float beta,
+                              float gamma, float* Y, int lengthv, int width, int stride) {
+  for (int i = 0; i < lengthv; i++) {
+    volatile float a = alpha * X1[i];
+    volatile float b = beta * X2[i % row_lengthv];
+    volatile float y = a + b;
+    y = y + gamma;
+    Y[i] = ((i % stride) < width) ? y : 0.0f;
   }
 }
 

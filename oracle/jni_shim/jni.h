@@ -8,6 +8,9 @@
 typedef int32_t jint;
 typedef int64_t jlong;
 typedef uint8_t jboolean;
+typedef int8_t jbyte;
+typedef uint16_t jchar;
+typedef int16_t jshort;
 typedef float jfloat;
 typedef double jdouble;
 struct _jobject {};

@@ -145,6 +145,17 @@ class ref_loops:
         return C
 
     @staticmethod
+    def linear_dual2D_row(X1, X2, alpha, beta, gamma, width):
+        """X1 [height, stride] (stride = padded row length), X2 [stride]: Y = alpha*X1 + beta*X2 + gamma per
+        row, columns >= width zeroed (Cuda_function/type1_linear_dual2D_row.cuh:41-70)."""
+        X1, X2 = _c32(X1), _c32(X2)
+        height, stride = X1.shape
+        Y = np.empty_like(X1)
+        lib().oracle_linear_dual2D_row(_f(X1), _f(X2), int(X2.size), c_float(alpha), c_float(beta), c_float(gamma),
+                                       _f(Y), height * stride, int(width), stride)
+        return Y
+
+    @staticmethod
     def kernel_remode(W):
         W = _c32(W)
         OC, FH, FW, IC = W.shape
@@ -249,7 +260,7 @@ def report(C, C64) -> dict:
 
 # ------------------------------------------------------------------ reference's own routines
 def ref_native(name: str):
-    """ctypes handle on oracle/_ref/libref_<name>.so ('matmul', 'bmm', 'conv'), or None if
+    """ctypes handle on oracle/_ref/libref_<name>.so ('matmul', 'bmm', 'conv', 'function'), or None if
     that build is absent (it needs the reference tree; see oracle/build_ref.py)."""
     p = REF_DIR / f"libref_{name}.so"
     if not p.exists():

@@ -1,0 +1,180 @@
+"""Contraction + bias row in one pass (the fusion of the engine's matMul_biased / conv3D_biased).
+
+The oracle is the two-step sequence the Java engine runs: the contraction, then
+Cuda_function.linear_dual2D_row(C, Bias, row_lengthv, 1, 1, 0, C, lengthv, width, stride)
+(CudaFloat32EngineBase.java:1594-1688, :2389-2542; Cuda_function/type1_linear_dual2D_row.cuh:41-70).
+The fused entry points must return the same bits as this library's contraction followed by the
+restated bias kernel, and meet the FP64 tolerance of the contraction itself."""
+import ctypes
+
+import numpy as np
+import pytest
+
+
+# ------------------------------------------------------------------ CPU: the restated bias kernel
+def test_linear_dual2D_row_oracle_known_answers(O):
+    X1 = np.arange(24, dtype=np.float32).reshape(3, 8) * 0.5
+    X2 = np.array([1, -2, 3, -4, 5, -6, 7, -8], np.float32)
+    Y = O.ref_loops.linear_dual2D_row(X1, X2, 1.0, 1.0, 0.0, 6)
+    want = X1 + X2
+    want[:, 6:] = 0          # padding columns of the [height][stride] matrix are zeroed
+    assert np.array_equal(Y, want)
+    # general coefficients
+    Y = O.ref_loops.linear_dual2D_row(X1, X2, 2.0, -0.5, 0.25, 8)
+    assert np.array_equal(Y, (np.float32(2) * X1 + np.float32(-0.5) * X2) + np.float32(0.25))
+    # with (1, 1, 0) the result is the single rounding of the exact sum
+    rng = np.random.default_rng(5)
+    X1 = rng.standard_normal((7, 12)).astype(np.float32) * 1e3
+    X2 = rng.standard_normal(12).astype(np.float32)
+    Y = O.ref_loops.linear_dual2D_row(X1, X2, 1.0, 1.0, 0.0, 12)
+    assert np.array_equal(Y, (X1.astype(np.float64) + X2.astype(np.float64)).astype(np.float32))
+
+
+def test_biased_argument_errors_without_gpu(pkg):
+    lib = pkg.cu32.load()
+    s = (ctypes.c_int64 * 1)(0)
+    P = lambda a: ctypes.cast(a, ctypes.POINTER(ctypes.c_float))
+    ok = 0x10000
+    f = lib.cu32_matMul_biased
+    assert f(s, 1, P(ok), P(ok), P(ok), None, 8, 8, 8, 8) == -1           # null bias
+    assert f(s, 1, P(ok), P(ok), P(ok), P(ok), 8, 8, 8, 0) == -2          # width out of range
+    assert f(s, 1, P(ok), P(ok), P(ok), P(ok), 8, 8, 8, 9) == -2
+    assert f(s, 1, P(ok), P(ok), P(ok), P(ok + 4), 8, 8, 8, 8) == -4      # bias not 16-byte aligned
+    g = lib.cu32_SKbuf_summary_biased
+    assert g(0, P(ok), P(ok), None, 1, 64, 8, 8) == -1
+    assert g(0, P(ok), P(ok), P(ok), 1, 64, 8, 9) == -2                   # width > row length
+    assert g(0, P(ok), P(ok), P(ok), 1, 60, 8, 8) == -2                   # sizeC not a whole number of rows
+    assert g(0, P(ok), P(ok), P(ok), 1, 72, 6, 6) == -4                   # row length not a multiple of 4
+    h = lib.cu32_conv3D_GemmR_biased
+    assert h(s, 1, P(ok), 8, 8, P(ok), P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 1, 1, 1, 1, None, 8) == -1
+
+
+# ------------------------------------------------------------------ GPU: bit-exact against the two-step sequence
+def _bias_then_pad(O, C, bias, width):
+    return O.ref_loops.linear_dual2D_row(C.reshape(-1, C.shape[-1]), bias, 1.0, 1.0, 0.0, width).reshape(C.shape)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(132, 260, 96, 258), (512, 512, 256, 512), (300, 36, 200, 33), (64, 1028, 72, 1028)])
+@pytest.mark.parametrize("mma", [False, True])
+def test_matmul_biased_equals_two_step_sequence(pkg, O, cuda, shape, mma):
+    import gpu_util as G
+    N, M, K, width = shape
+    A, B = G.rand_pm1((N, K), 41), G.rand_pm1((K, M), 42)
+    B[:, width:] = 0                                     # the engine keeps padding columns zero
+    bias = np.zeros(M, np.float32)
+    bias[:width] = np.random.default_rng(43).standard_normal(width).astype(np.float32)
+    plain = G.matmul(pkg, "AB", A, B, N, M, K, mma=mma)
+    want = _bias_then_pad(O, plain, bias, width)
+    dA, dB, dbias = G.dev(A), G.dev(B), G.dev(bias)
+    out = G.Out(N * M)
+    mm = pkg.cu32.Cuda_matMul
+    (mm.matMul_mma_biased if mma else mm.matMul_biased)([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr,
+                                                        dbias.data_ptr(), N, M, K, width)
+    got = out.host((N, M))
+    G.check_status(pkg)
+    assert np.array_equal(got, want)
+    if not mma:
+        C64 = O.f64.matMul(A, B) + bias.astype(np.float64)
+        C64[:, width:] = 0
+        rep = O.report(got, C64)
+        assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, rep
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 8])
+def test_matmul_biased_every_tile(pkg, O, cuda, tile):
+    import gpu_util as G
+    pkg.cu32.tune("tile", tile)
+    N, M, K, width = 300, 520, 136, 517
+    A, B = G.rand_pm1((N, K), 44), G.rand_pm1((K, M), 45)
+    bias = G.rand_pm1((M,), 46)
+    plain = G.matmul(pkg, "AB", A, B, N, M, K)
+    dA, dB, dbias = G.dev(A), G.dev(B), G.dev(bias)
+    out = G.Out(N * M)
+    pkg.cu32.Cuda_matMul.matMul_biased([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr, dbias.data_ptr(), N, M,
+                                       K, width)
+    got = out.host((N, M))
+    G.check_status(pkg)
+    assert np.array_equal(got, _bias_then_pad(O, plain, bias, width)), tile
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("part", [0, 1, 5])
+def test_skbuf_summary_biased(pkg, O, cuda, part):
+    import gpu_util as G
+    N, M, width = 36, 40, 38
+    rng = np.random.default_rng(47)
+    C = rng.standard_normal((N, M)).astype(np.float32)
+    Cbuf = rng.standard_normal((max(part, 1), N, M)).astype(np.float32)
+    bias = rng.standard_normal(M).astype(np.float32)
+    want = _bias_then_pad(O, O.ref_loops.buf_summary(Cbuf[:part], C, part, N * M).reshape(N, M), bias, width)
+    dC, dCbuf, dbias = G.dev(C), G.dev(Cbuf), G.dev(bias)
+    pkg.cu32.Cuda_matMul.SKbuf_summary_biased(G.stream(), dCbuf.data_ptr(), dC.data_ptr(), dbias.data_ptr(), part,
+                                              N * M, M, width)
+    cuda.cuda.synchronize()
+    assert np.array_equal(dC.cpu().numpy(), want)
+
+
+@pytest.mark.gpu
+def test_splitk_then_biased_summary_matches_engine_sequence(pkg, O, cuda):
+    """matMulSK + SKbuf_summary_biased == matMulSK + SKbuf_summary + linear_dual2D_row (engine :1641-1688)."""
+    import gpu_util as G
+    N, M, K, GZ, width = 132, 260, 2052, 4, 258
+    A, B = G.rand_pm1((N, K), 48), G.rand_pm1((K, M), 49)
+    bias = G.rand_pm1((M,), 50)
+    C, C0, Cbuf = G.matmul_sk(pkg, "AB", A, B, N, M, K, GZ)          # summed by the plain SKbuf_summary
+    want = _bias_then_pad(O, C, bias, width)
+    dC, dCbuf, dbias = G.dev(C0), G.dev(Cbuf), G.dev(bias)
+    pkg.cu32.Cuda_matMul.SKbuf_summary_biased(G.stream(), dCbuf.data_ptr(), dC.data_ptr(), dbias.data_ptr(), GZ - 1,
+                                              N * M, M, width)
+    cuda.cuda.synchronize()
+    assert np.array_equal(dC.cpu().numpy(), want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [(4, 12, 12, 16, 24, 3, 3, 1, 1, 1, 1, 22), (2, 9, 9, 8, 64, 3, 3, 2, 2, 1, 1, 64),
+                                  (4, 10, 10, 32, 132, 1, 1, 1, 1, 0, 0, 130)])
+def test_conv_biased_equals_two_step_sequence(pkg, O, cuda, case):
+    import gpu_util as G
+    torch = cuda
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, width = case
+    rng = np.random.default_rng(51)
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+    W[width:] = 0
+    bias = rng.standard_normal(OC).astype(np.float32)
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    plain = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
+    want = _bias_then_pad(O, plain, bias, width)
+    dX, dW, dbias = G.dev(X), G.dev(W), G.dev(bias)
+    dCW = torch.empty(W.size, device="cuda")
+    out = G.Out(N * OH * OW * OC)
+    pkg.cu32.Cuda_conv3D.conv3D_GemmR_biased([G.stream()], 1, dX.data_ptr(), IH, IW, dW.data_ptr(), dCW.data_ptr(), FH, FW,
+                                             out.ptr, OH, OW, N, IC, OC, sh, sw, ph, pw, dbias.data_ptr(), width)
+    got = out.host((N, OH, OW, OC))
+    G.check_status(pkg)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.gpu
+def test_bias_kernel_restatement_against_reference_kernel(pkg, O, cuda):
+    """Pins the restated linear_dual2D_row: the reference's own kernel, compiled from the reference tree for
+    sm_100a (oracle/_ref/libref_function.so), gives the same bits on the same inputs."""
+    import gpu_util as G
+    ref = O.ref_native("function")
+    if ref is None:
+        pytest.skip("oracle/_ref/libref_function.so not built")
+    rng = np.random.default_rng(52)
+    for (height, stride, width) in [(3, 8, 6), (40, 260, 258), (700, 132, 132), (5, 4, 1)]:
+        X1 = (rng.standard_normal((height, stride)) * 100).astype(np.float32)
+        X2 = rng.standard_normal(stride).astype(np.float32)
+        d1, d2 = G.dev(X1), G.dev(X2)
+        dY = cuda.empty((height, stride), device="cuda")
+        fn = ref.ref_gpu_linear_dual2D_row
+        fn.argtypes = [ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_float,
+                       ctypes.c_float, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        assert fn(G.stream(), d1.data_ptr(), d2.data_ptr(), stride, 1.0, 1.0, 0.0, dY.data_ptr(), height * stride, width,
+                  stride) == 0
+        cuda.cuda.synchronize()
+        assert np.array_equal(dY.cpu().numpy(), O.ref_loops.linear_dual2D_row(X1, X2, 1.0, 1.0, 0.0, width))

@@ -110,7 +110,7 @@ def _header_symbols():
 def test_library_exports_every_declared_symbol(pkg):
     lib = pkg.cu32.load()
     names = _header_symbols()
-    assert len(names) >= 39
+    assert len(names) >= 43
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/dragon_cu32.h but not exported"
     # the ctypes table covers the same surface
@@ -134,7 +134,9 @@ def test_jni_symbols_exported(pkg):
                  "conv3D_conv3D_1Im2col_1Winograd_1s8_1R_1texture", "conv3D_conv3D_1Im2col_1WinogradR_1s8_1texture_1SGM",
                  "conv3D_conv3D_1Im2col_1Winograd_1s16_1R_1texture",
                  "conv3D_conv3D_1Im2col_1WinogradR_1s16_1texture_1SGM"}
-    missing = (want_matmul | want_bmm | want_conv) - syms
+    want_fused = {"matMul_matMul_1biased", "matMul_matMul_1mma_1biased", "matMul_SKbuf_1summary_1biased",
+                  "conv3D_conv3D_1GemmR_1biased"}   # no counterpart in the reference's Java classes
+    missing = (want_matmul | want_bmm | want_conv | want_fused) - syms
     assert not missing, missing
 
 

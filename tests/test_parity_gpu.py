@@ -173,6 +173,26 @@ def test_prefetch_distances(pkg, O, cuda, dist):
             assert np.array_equal(C, base["sk"]) and np.array_equal(S, base["S"]), dist
 
 
+def test_results_repeat_bit_for_bit_on_every_tile(pkg, O, cuda):
+    """Every tile shape walks K in the same order, so all of them return the same bits, run after run.
+    A hand-over that is not properly fenced (a lo tile read by the tensor core while a store to it is still in
+    flight, a TMEM buffer recycled early) shows up here as a few hundred elements that differ in one run of many,
+    long before it costs enough accuracy to fail a tolerance."""
+    w = pkg.workloads.config4(N=8)
+    X, W = w.X.numpy(), w.W.numpy()
+    A, B = G.rand_pm1((1024, 2304), 1), G.rand_pm1((2304, 520), 2)
+    cases = {"conv": lambda: G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, 1, 1),
+             "matMul": lambda: G.matmul(pkg, "AB", A, B, 1024, 520, 2304)}
+    for name, fn in cases.items():
+        pkg.cu32.tune("tile", 4)
+        base = fn()
+        for tile in (0, 1, 2, 3, 4, 8):
+            pkg.cu32.tune("tile", tile)
+            for rep in range(16):
+                Y = fn()
+                assert np.array_equal(Y, base), (name, tile, rep, int((Y != base).sum()), float(np.abs(Y - base).max()))
+
+
 def test_config1_full_size(pkg, O, cuda):
     w = pkg.workloads.config1()
     A, B = w.A.numpy(), w.B.numpy()
