@@ -20,7 +20,7 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
-Other workloads (for profiling and the reports in profiles/): c1, c2_t1, c2_t2, c2_ragged,
+Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged,
 c3_qk, c3_pv, c4, c5.
 """
 from __future__ import annotations
@@ -154,7 +154,7 @@ class Workload:
         st = lambda: [torch.cuda.current_stream().cuda_stream]
         self.kernels_per_step = 1
         self.cpu_case = None
-        if name in ("c1", "c2_ab", "c2_t1", "c2_t2", "c2_ragged", "c5"):
+        if name in ("c1", "c2_ab", "c2_bias", "c2_t1", "c2_t2", "c2_ragged", "c5"):
             if name == "c1":
                 w = W.config1()
             elif name == "c2_ragged":
@@ -162,7 +162,7 @@ class Workload:
             elif name == "c5":
                 w = W.config5(K=1048576 // 8)   # one GPU's K shard of the 8-GPU configuration
             else:
-                w = W.config2({"c2_ab": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name], size)
+                w = W.config2({"c2_ab": "AB", "c2_bias": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name], size)
             self.hosts = [w.A.pin_memory(), w.B.pin_memory()]
             self.dev_in = [torch.empty_like(h, device="cuda") for h in self.hosts]
             for d, h in zip(self.dev_in, self.hosts):
@@ -180,6 +180,12 @@ class Workload:
                     mm.matMulT1SK(s, 1, gz, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), self.cbuf.data_ptr(), w.N, w.M, w.K)
                     mm.SKbuf_summary(s[0], self.cbuf.data_ptr(), dC.data_ptr(), gz - 1, w.N * w.M)
                 self.launch = launch
+            elif name == "c2_bias":
+                # the engine's matMul_biased as one kernel: product, bias row and padding zeroing
+                g = torch.Generator().manual_seed(2002)
+                self.bias = torch.randn(w.M, generator=g).cuda()
+                self.launch = lambda: mm.matMul_biased(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                                                       self.bias.data_ptr(), w.N, w.M, w.K, w.M)
             else:
                 self.launch = lambda: fn(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.N, w.M, w.K)
             lg = getattr(w, "logical", (w.N, w.M, w.K))

@@ -132,8 +132,8 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Tile choice: estimated time = waves over the 148 SMs x work per CTA / measured per-CTA
 // rate.  The rates are FP32-accurate TFLOP/s measured at 8192^3 on a B200 with every SM
-// busy (the 128x64 figure is scaled from the 128x128 one); padded rows and columns count
-// as work, so narrow outputs pick narrow tiles and small problems pick small tiles.
+// busy; padded rows and columns count as work, so narrow outputs pick narrow tiles and
+// small problems pick small tiles.
 static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;

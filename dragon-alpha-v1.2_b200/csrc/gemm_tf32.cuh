@@ -8,11 +8,13 @@
 // split-K slice rides on blockIdx.z, and the A operand can be gathered from an
 // NHWC feature map by an im2col-mode tensor map.
 //
-// Arithmetic.  Each FP32 input x is split in shared memory into
-//     hi = tf32_round(x)          lo = tf32_round(x - hi)
-// and the product is formed as  lo*hi + hi*lo + hi*hi  on tcgen05.mma kind::tf32
-// (the lo*lo term, below 2^-22 relative, is dropped).  The tensor core
-// accumulates in FP32 inside TMEM, but truncates the accumulator after every
+// Arithmetic.  Each FP32 input x is used as
+//     hi = tf32_trunc(x)          lo = tf32_round(x - hi)
+// where hi is what the tensor core itself makes of an FP32 operand (it ignores the low
+// 13 mantissa bits), so the tile as TMA wrote it serves as hi and only lo is written, next
+// to it in shared memory.  The product is formed as  lo*hi + hi*lo + hi*hi  on
+// tcgen05.mma kind::tf32 (the lo*lo term, below 2^-20 relative, is dropped).  The tensor
+// core accumulates in FP32 inside TMEM, but truncates the accumulator after every
 // instruction; it is therefore only trusted for `kc` k-blocks (one "chunk"):
 // drain warps then add the chunk to FP32 register accumulators with
 // round-to-nearest adds, so the length of any truncating accumulation chain is
@@ -26,7 +28,7 @@
 // Roles inside a CTA of 16 warps:
 //   warp 0        TMA producer      global -> shared (raw FP32 tiles, 128B swizzle)
 //   warp 1        MMA issuer        one thread issues tcgen05.mma, commits to mbarriers
-//   warps 2..7    splitters         shared -> shared: raw -> (hi in place, lo beside it)
+//   warps 2..7    splitters         shared -> shared: raw tile -> lo tile beside it
 //   warps 8..15   drainers          TMEM -> registers (sum of chunks) -> global
 // With CTAS == 2 two CTAs of a cluster form one 256-row tile: each loads and
 // splits its own half of A and of B, the even CTA issues cta_group::2 MMAs, and
@@ -388,9 +390,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    // Measured cost to this thread: ~70 cycles per MMA, ~125 per commit, a few hundred per
-    // barrier wait, against at most 1536 cycles of execution per k-block - so commits are
-    // kept to the minimum (one paired commit instead of two for a CTA pair).
+    // Measured cost to this thread, per k-block of 12 MMAs (1536 cycles of execution on the
+    // 256-column pair tile): about 390 cycles to issue them from one elect.sync region, about
+    // 100 for the commits (one paired commit instead of two for a CTA pair); the rest of the
+    // time it waits for operands.
     if (rank == 0) {
       const bool leader = lane == 0;   // the one thread that issues (and whose commits track) the MMAs
       constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN && !Cfg::TS, Cfg::B_MN);
