@@ -93,3 +93,45 @@ def test_fuzz_conv(pkg, O, cuda):
         OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
         Y = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
         _acc(O, Y, O.f64.conv3D(X, W, OH, OW, sh, sw, ph, pw), f"conv N{N} {IH}x{IW}x{IC}->{OC} f{FH}x{FW} s{sh},{sw} p{ph},{pw}")
+
+
+def test_fuzz_biased(pkg, O, cuda):
+    """Random shapes and widths through the fused bias entry points: same bits as the two-step sequence
+    (contraction, then the restated linear_dual2D_row)."""
+    mm, cv = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_conv3D
+    rng = np.random.default_rng(77)
+    s = [G.stream()]
+    for case in range(24):
+        N = int(rng.integers(1, 160)) * 4
+        M = int(rng.integers(1, 160)) * 4
+        K = int(rng.choice([4, 32, 36, 100, 516]))
+        width = M - int(rng.choice([0, 0, 1, 2, 3]))
+        A = rng.standard_normal((N, K)).astype(np.float32)
+        B = rng.standard_normal((K, M)).astype(np.float32)
+        B[:, width:] = 0
+        bias = rng.standard_normal(M).astype(np.float32)
+        plain = G.matmul(pkg, "AB", A, B, N, M, K)
+        want = O.ref_loops.linear_dual2D_row(plain, bias, 1.0, 1.0, 0.0, width)
+        dA, dB, db = G.dev(A), G.dev(B), G.dev(bias)
+        out = G.Out(N * M)
+        mm.matMul_biased(s, 1, dA.data_ptr(), dB.data_ptr(), out.ptr, db.data_ptr(), N, M, K, width)
+        assert np.array_equal(out.host((N, M)), want), (N, M, K, width)
+    for case in range(8):
+        N, IH, IW = int(rng.integers(1, 5)), int(rng.integers(5, 14)), int(rng.integers(5, 14))
+        IC, OC = int(rng.integers(1, 10)) * 4, int(rng.integers(1, 40)) * 4
+        F = int(rng.choice([1, 3, 5])); st = int(rng.choice([1, 2])); pad = F // 2
+        width = OC - int(rng.choice([0, 1, 3]))
+        X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+        W = (rng.standard_normal((OC, F, F, IC)) * 0.1).astype(np.float32)
+        W[width:] = 0
+        bias = rng.standard_normal(OC).astype(np.float32)
+        OH, OW = (IH + 2 * pad - F) // st + 1, (IW + 2 * pad - F) // st + 1
+        plain = G.conv(pkg, "conv3D_GemmR", X, W, st, st, pad, pad)
+        want = O.ref_loops.linear_dual2D_row(plain.reshape(-1, OC), bias, 1.0, 1.0, 0.0, width).reshape(plain.shape)
+        dX, dW, db = G.dev(X), G.dev(W), G.dev(bias)
+        dCW = torch.empty(W.size, device="cuda")
+        out = G.Out(N * OH * OW * OC)
+        cv.conv3D_GemmR_biased(s, 1, dX.data_ptr(), IH, IW, dW.data_ptr(), dCW.data_ptr(), F, F, out.ptr, OH, OW, N, IC, OC,
+                               st, st, pad, pad, db.data_ptr(), width)
+        assert np.array_equal(out.host((N, OH, OW, OC)), want), (N, IH, IW, IC, OC, F, st, width)
+    G.check_status(pkg)
