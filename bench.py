@@ -282,7 +282,7 @@ class Workload:
         c = self.cpu_case
         if c is not None and c[0] in ("AB", "T2") and c[1] >= 2048 and self.kernels_per_step == 1:
             self.row_blocks = (c[0], c[1], c[2], c[3])
-            self.nblk = 8
+            self.nblk = int(os.environ.get("DRAGON_BENCH_E2E_BLOCKS", "32"))   # row blocks of the copy/compute/copy pipeline
             self.s_in, self.s_out = self.torch.cuda.Stream(), self.torch.cuda.Stream()
         self.h2d = sum(h.numel() * 4 for h in self.hosts)
         self.d2h = self.out.numel() * 4
