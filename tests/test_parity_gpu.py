@@ -193,6 +193,40 @@ def test_results_repeat_bit_for_bit_on_every_tile(pkg, O, cuda):
                 assert np.array_equal(Y, base), (name, tile, rep, int((Y != base).sum()), float(np.abs(Y - base).max()))
 
 
+def test_extreme_extents(pkg, O, cuda):
+    """Long thin problems: more row tiles, batches and split-K slices than a 16-bit grid axis could index,
+    and a reduction of a million - the extents the tile index and the tensor maps have to carry."""
+    torch = cuda
+    mm, bm = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_batchMatMul
+    s = [G.stream()]
+    g = torch.Generator(device="cuda").manual_seed(99)
+    # 1 Mi + 4 rows, 8 columns: 8193 row tiles of the 128-row tile
+    N, M, K = (1 << 20) + 4, 8, 36
+    A = torch.randn(N, K, device="cuda", generator=g); B = torch.randn(K, M, device="cuda", generator=g)
+    C = torch.full((N, M), float("nan"), device="cuda")
+    mm.matMul(s, 1, A.data_ptr(), B.data_ptr(), C.data_ptr(), N, M, K)
+    ref = A.double() @ B.double()
+    assert ((C.double() - ref).norm() / ref.norm()).item() <= 1e-6 and bool(torch.isfinite(C).all())
+    # 70 000 batches of 4x4x4
+    Bt = 70000
+    Q = torch.randn(Bt, 4, 4, device="cuda", generator=g); Kt = torch.randn(Bt, 4, 4, device="cuda", generator=g)
+    S = torch.full((Bt, 4, 4), float("nan"), device="cuda")
+    bm.batchMatMulT2(s, 1, Q.data_ptr(), Kt.data_ptr(), S.data_ptr(), Bt, 4, 4, 4, 4)
+    ref = Q.double() @ Kt.double().transpose(1, 2)
+    assert ((S.double() - ref).norm() / ref.norm()).item() <= 1e-6 and bool(torch.isfinite(S).all())
+    # K = 1 Mi through split-K with the engine's own slice count, 64x64 output
+    N, M, K = 64, 64, 1 << 20
+    A = torch.randn(K, N, device="cuda", generator=g); B = torch.randn(K, M, device="cuda", generator=g)
+    GZ = pkg.engine.matMulT1_gridZ(N, M, K, 148)
+    assert GZ > 1
+    C = torch.full((N, M), float("nan"), device="cuda"); Cbuf = torch.full((GZ - 1, N, M), float("nan"), device="cuda")
+    mm.matMulT1SK(s, 1, GZ, A.data_ptr(), B.data_ptr(), C.data_ptr(), Cbuf.data_ptr(), N, M, K)
+    mm.SKbuf_summary(s[0], Cbuf.data_ptr(), C.data_ptr(), GZ - 1, N * M)
+    ref = A.double().T @ B.double()
+    assert ((C.double() - ref).norm() / ref.norm()).item() <= 1e-6 and bool(torch.isfinite(C).all())
+    G.check_status(pkg)
+
+
 def test_config1_full_size(pkg, O, cuda):
     w = pkg.workloads.config1()
     A, B = w.A.numpy(), w.B.numpy()
