@@ -23,7 +23,6 @@ static std::atomic<int> g_kc{2};
 static std::atomic<int> g_kc_fast{4};
 static std::atomic<int> g_tile{-1};
 static std::atomic<int> g_l2hint{0};
-static std::atomic<int> g_prefetch{-1};  // L2 prefetch distance in k-blocks; -1 = by shape, 0 = off
 
 static void load_env_once() {
   static std::once_flag once;
@@ -31,7 +30,6 @@ static void load_env_once() {
     if (const char* s = std::getenv("DRAGON_CU32_KC")) { int v = std::atoi(s); if (v >= 1) g_kc = v; }
     if (const char* s = std::getenv("DRAGON_CU32_KC_FAST")) { int v = std::atoi(s); if (v >= 1) g_kc_fast = v; }
     if (const char* s = std::getenv("DRAGON_CU32_L2HINT")) { int v = std::atoi(s); if (v >= 0 && v <= 2) g_l2hint = v; }
-    if (const char* s = std::getenv("DRAGON_CU32_PREFETCH")) { int v = std::atoi(s); if (v >= -1 && v <= 64) g_prefetch = v; }
     if (const char* s = std::getenv("DRAGON_CU32_TILE")) { int v = std::atoi(s); if (v >= -1 && v < TILE_COUNT) g_tile = v; }
   });
 }
@@ -198,16 +196,6 @@ static int run_gemm(const GemmCall& c) {
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
-  {
-    // Short reductions are memory-bound: run an L2 prefetch about 112 KB of this CTA's traffic
-    // (loads plus its share of the output) ahead of the loads.  Long ones gain nothing from it.
-    const int nkb_tile = (p.nkb_total + c.gz - 1) / c.gz;
-    const int bn_cta = bn / ctas;
-    const long long per_kb = 4LL * 32 * (128 + bn_cta) + 4LL * 128 * bn_cta / nkb_tile;
-    int d = g_prefetch.load();
-    if (d < 0) d = nkb_tile <= 16 ? static_cast<int>(std::min<long long>(16, std::max<long long>(1, (112 * 1024 + per_kb / 2) / per_kb))) : 0;
-    p.prefetch = d;
-  }
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;   // the bias is applied on the vector store paths only
   if (p.vec4_ok) {
@@ -740,7 +728,6 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "kc_fast")) { if (value < 1) return CU32_E_ARG; g_kc_fast = value; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { if (value < -1 || value >= TILE_COUNT) return CU32_E_ARG; g_tile = value; return CU32_OK; }
   if (!std::strcmp(key, "l2hint")) { if (value < 0 || value > 2) return CU32_E_ARG; g_l2hint = value; return CU32_OK; }
-  if (!std::strcmp(key, "prefetch")) { if (value < -1 || value > 64) return CU32_E_ARG; g_prefetch = value; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {
@@ -750,7 +737,6 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "kc_fast")) { *value = g_kc_fast; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { *value = g_tile; return CU32_OK; }
   if (!std::strcmp(key, "l2hint")) { *value = g_l2hint; return CU32_OK; }
-  if (!std::strcmp(key, "prefetch")) { *value = g_prefetch; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_read_status(int* status) {

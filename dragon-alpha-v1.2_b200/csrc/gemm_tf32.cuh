@@ -65,7 +65,6 @@ struct GemmParams {
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
   int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
   int l2_hints;         // load A with evict-last and B with evict-first L2 priority
-  int prefetch;         // tiled operands: k-blocks by which an L2 prefetch runs ahead of the loads (0 = off)
   int* status;          // device word, 0 = ok; first give-up code otherwise
 #ifdef DRAGON_TRACE
   long long* trace;     // 2 CTAs x 12 events x 256 timestamps (tracing builds only)
@@ -284,46 +283,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       // L2, evict each other in exactly the order they are needed again).
       const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : 0ull;
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
-      // L2 prefetch cursor: walks the same (tile, k-block) sequence p.prefetch positions ahead
-      // of the loads, across tile boundaries.  For short-K, memory-bound shapes the loads
-      // otherwise wait several thousand cycles behind the output writes, and shared memory
-      // has no room for more stages; a prefetch needs none.
-      const int pf_dist = Cfg::IM2COL ? 0 : p.prefetch;
-      long long pf_t = tile_first;
-      int pf_i = 0;
-      bool pf_valid = pf_dist > 0 && pf_t < total_tiles;
-      TileWork pf_w = pf_valid ? decode(pf_t) : TileWork{};
-      auto pf_advance = [&]() {
-        if (pf_valid && ++pf_i >= pf_w.nkb) {
-          pf_t += tile_step;
-          pf_i = 0;
-          pf_valid = pf_t < total_tiles;
-          if (pf_valid) pf_w = decode(pf_t);
-        }
-      };
-      for (int d = 0; d < pf_dist; ++d) pf_advance();
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == STAGES) ? 0u : s + 1, ph ^= (s == 0)) {
-          if (pf_valid) {
-            const int kp = (pf_w.kb0 + pf_i) * Cfg::BK;
-            if (elect_one()) {
-              if (Cfg::A_MN) {
-#pragma unroll
-                for (int j = 0; j < Cfg::BM / 32; ++j) tma_prefetch_3d(&p.tmA, pf_w.row0 + 32 * j, kp, pf_w.batch);
-              } else {
-                tma_prefetch_3d(&p.tmA, kp, pf_w.row0, pf_w.batch);
-              }
-              if (Cfg::B_MN) {
-#pragma unroll
-                for (int j = 0; j < Cfg::BN_CTA / 32; ++j) tma_prefetch_3d(&p.tmB, pf_w.bcol0 + 32 * j, kp, pf_w.batch);
-              } else {
-                tma_prefetch_3d(&p.tmB, kp, pf_w.bcol0, pf_w.batch);
-              }
-            }
-            __syncwarp();
-            pf_advance();
-          }
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
             if (leader) give_up(ROLE_TMA, s, i);
             alive = false;

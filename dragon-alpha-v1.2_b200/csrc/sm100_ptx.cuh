@@ -126,12 +126,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
       : "memory");
 }
-// Bring the box at these coordinates into L2 only (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map),
-               "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
 // im2col-mode load of an NHWC tensor: coordinates (c, w, h, n) name the first
 // pixel of the run, offsets (ow, oh) the filter tap.
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap* map,

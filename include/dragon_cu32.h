@@ -261,9 +261,6 @@ CU32_API int cu32_conv3D_GemmR_biased(const int64_t* streams, int length, const 
  *              shape (default)
  *   "l2hint"   L2 eviction priority of the operand loads: 0 = none (default; measured best),
  *              1 = A evict-last and B evict-first, 2 = A evict-last only
- *   "prefetch" k-blocks by which an L2 prefetch of the operand tiles runs ahead of the loads:
- *              -1 = by shape (default: about 112 KB of a CTA's traffic ahead when a tile's
- *              reduction has at most 16 k-blocks, off otherwise), 0 = off, 1..64 = fixed
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
 CU32_API int cu32_tune(const char* key, int value);
 CU32_API int cu32_get_tune(const char* key, int* value);

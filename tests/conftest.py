@@ -55,7 +55,6 @@ def _default_tuning(request):
         p.cu32.tune("tile", -1)
         p.cu32.tune("kc", DEFAULT_KC["kc"])
         p.cu32.tune("kc_fast", DEFAULT_KC["kc_fast"])
-        p.cu32.tune("prefetch", -1)
 
 
 DEFAULT_KC = {"kc": 2, "kc_fast": 4}

@@ -143,36 +143,6 @@ def test_chunk_lengths(pkg, O, cuda, kc):
     assert rep["frob"] <= 1e-5 and np.isfinite(C).all(), rep
 
 
-@pytest.mark.parametrize("dist", [0, 1, 3, 64])
-def test_prefetch_distances(pkg, O, cuda, dist):
-    """The L2 prefetch cursor runs ahead of the loads across tile, batch and slice boundaries and past
-    the end of the work list; it only warms the cache, so every distance gives the same bits."""
-    rng = np.random.default_rng(31)
-    shapes = [("AB", 300, 520, 200), ("T1", 260, 136, 96), ("T2", 516, 260, 72)]
-    base = {}
-    for d in (-1, dist):
-        pkg.cu32.tune("prefetch", d)
-        for form, N, M, K in shapes:
-            sa, sb = G.mm_shapes(form, N, M, K)
-            A, B = G.rand_pm1(sa, 5), G.rand_pm1(sb, 6)
-            C = G.matmul(pkg, form, A, B, N, M, K)
-            if d == -1:
-                assert_accurate(O, C, G.f64_matmul(O, form, A, B), f"{form} prefetch auto")
-                base[form] = C
-            else:
-                assert np.array_equal(C, base[form]), (form, dist)
-        A, B = G.rand_pm1((1028, 132), 7), G.rand_pm1((1028, 260), 8)
-        C, _, _ = G.matmul_sk(pkg, "T1", A, B, 132, 260, 1028, 4)
-        Q = rng.standard_normal((5, 132, 64)).astype(np.float32) if d == -1 else base["Q"]
-        Kt = rng.standard_normal((5, 132, 64)).astype(np.float32) if d == -1 else base["Kt"]
-        S = G.bmm_t2(pkg, Q, Kt)
-        if d == -1:
-            base.update(sk=C, Q=Q, Kt=Kt, S=S)
-            assert_accurate(O, S, O.f64.batchMatMulT2(Q, Kt), "bmm prefetch auto")
-        else:
-            assert np.array_equal(C, base["sk"]) and np.array_equal(S, base["S"]), dist
-
-
 def test_results_repeat_bit_for_bit_on_every_tile(pkg, O, cuda):
     """Every tile shape walks K in the same order, so all of them return the same bits, run after run.
     A hand-over that is not properly fenced (a lo tile read by the tensor core while a store to it is still in
