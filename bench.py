@@ -60,11 +60,47 @@ def peaks():
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
+    """SM clock and clock-event reasons sampled DURING the timed region (read-only queries).  NVML is
+    polled from a thread every few milliseconds, so that even a 50 ms region gets a dozen samples; if the
+    NVML bindings are missing, `nvidia-smi -lms` is the fallback (about one sample per 100 ms)."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str | None = None):
         self.proc = None
+        self.thread = None
+        self.samples = []          # (sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = None
+            if uuid:
+                try:
+                    h = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+                except Exception:
+                    h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self._nvml = pynvml
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append((float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
+                                             int(reasons_fn(h))))
+                    except Exception:
+                        pass
+                    self._stop.wait(0.004)
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -73,6 +109,23 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            nv = self._nvml
+            bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+            for n, const in (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"),
+                             ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+                             ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
+                             ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap")):
+                bits[n] = int(getattr(nv, const, bits[n]))
+            sm = [x[0] for x in self.samples]
+            seen = 0
+            for _, r in self.samples:
+                seen |= r
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(n for n in names if seen & bits[n]), "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -83,7 +136,6 @@ class ClockSampler:
             self.proc.kill()
             out, _ = self.proc.communicate()
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 6:
@@ -96,7 +148,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------ CPU baseline (reference loops)
@@ -371,7 +423,12 @@ def main():
     if st != 0:
         raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    gpu_uuid = None
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+    except Exception:
+        pass
+    sampler = ClockSampler(local_rank, gpu_uuid) if rank == 0 else None
     ms = time_steps(torch, dist, wl.launch, a.steps, world)
     clocks = sampler.stop() if sampler else None
     st = pkg.cu32.read_status()
