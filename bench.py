@@ -340,19 +340,25 @@ class Workload:
         self.d2h = self.out.numel() * 4
 
 
-def time_steps(torch, dist, fn, steps, world):
+def time_steps(torch, dist, fn, steps, world, on_start=None, on_stop=None):
     """barrier + sync, `steps` launches bracketed by CUDA events on the current stream, sync +
-    barrier; returns the max over ranks of the elapsed milliseconds."""
+    barrier; returns the max over ranks of the elapsed milliseconds.  `on_start` / `on_stop` run
+    right around the timed launches (after the opening barrier, before the closing one) - the
+    clock sampler hooks in there so that it sees the GPU under load only."""
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    if on_start:
+        on_start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    if on_stop:
+        on_stop()
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -428,9 +434,18 @@ def main():
         gpu_uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
     except Exception:
         pass
-    sampler = ClockSampler(local_rank, gpu_uuid) if rank == 0 else None
-    ms = time_steps(torch, dist, wl.launch, a.steps, world)
-    clocks = sampler.stop() if sampler else None
+    box = {}
+
+    def start_sampler():
+        if rank == 0:
+            box["sampler"] = ClockSampler(local_rank, gpu_uuid)
+
+    def stop_sampler():
+        if "sampler" in box:
+            box["clocks"] = box["sampler"].stop()
+
+    ms = time_steps(torch, dist, wl.launch, a.steps, world, start_sampler, stop_sampler)
+    clocks = box.get("clocks")
     st = pkg.cu32.read_status()
     if st != 0:
         raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
