@@ -143,6 +143,24 @@ class Cu32Engine:
         gz = matMul_gridZ(N, M, K, self.sm_count)
         return self._run(Cuda_matMul.matMul, Cuda_matMul.matMul_mma, Cuda_matMul.matMulSK, gz, C, A, B, N, M, K)
 
+    def matMul_biased(self, C, A, B, N, M, K, Bias, width):
+        """CudaFloat32EngineBase.matMul_biased (:1594-1688) with the bias row fused: one native instead of
+        product + linear_dual2D_row when K is not split, matMulSK + SKbuf_summary_biased when it is.
+        The split decision is the engine's own (same as matMul)."""
+        gz = matMul_gridZ(N, M, K, self.sm_count)
+        sa, n = self._stream_array(N, M)
+        if gz == 1:
+            fn = Cuda_matMul.matMul_mma_biased if (self.tf32 and N > 127 and M > 127 and K % 8 == 0) \
+                else Cuda_matMul.matMul_biased
+            fn(sa, n, A, B, C, Bias, N, M, K, width)
+            return 1
+        part, sizeC = gz - 1, N * M
+        Cbuf, keep = self.malloc(sizeC * part)
+        self._keep.append(keep)
+        Cuda_matMul.matMulSK(sa, n, gz, A, B, C, Cbuf, N, M, K)
+        Cuda_matMul.SKbuf_summary_biased(sa[0], Cbuf, C, Bias, part, sizeC, M, width)
+        return gz
+
     def matMulT1(self, C, A, B, N, M, K):
         gz = matMulT1_gridZ(N, M, K, self.sm_count)
         return self._run(Cuda_matMul.matMulT1, Cuda_matMul.matMulT1_mma, Cuda_matMul.matMulT1SK, gz, C, A, B, N, M, K)

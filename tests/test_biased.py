@@ -178,3 +178,43 @@ def test_bias_kernel_restatement_against_reference_kernel(pkg, O, cuda):
                   stride) == 0
         cuda.cuda.synchronize()
         assert np.array_equal(dY.cpu().numpy(), O.ref_loops.linear_dual2D_row(X1, X2, 1.0, 1.0, 0.0, width))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(256, 512, 1024), (64, 128, 32768)])
+def test_fullconnect_layer_forward_and_backward_through_the_engine_mirror(pkg, O, cuda, shape):
+    """One fully-connected layer the way the Java engine runs it: forward Y = X*W + b (matMul_biased, fused here),
+    weight gradient dW = X^T * dY (matMulT1, split-K by the engine's rule) and data gradient dX = dY * W^T
+    (matMulT2) - the contractions behind fullconnect / fullconnect_deltaW / fullconnect_deltaX
+    (Engine.java:1425-1467), all through natives this library exports."""
+    import gpu_util as G
+    torch = cuda
+    batch, IW, OW = shape            # K of the weight gradient is the batch
+    keep = []
+
+    def malloc(n):
+        t = torch.empty(n, device="cuda")
+        keep.append(t)
+        return t.data_ptr(), t
+    eng = pkg.engine.Cu32Engine(148, malloc, [G.stream()])
+    g = torch.Generator().manual_seed(61)
+    X = torch.randn((batch, IW), generator=g)
+    W = torch.randn((IW, OW), generator=g) * 0.05
+    b = torch.randn(OW, generator=g)
+    dY = torch.randn((batch, OW), generator=g)
+    dX_, dW_, db_, ddY = X.cuda(), W.cuda(), b.cuda(), dY.cuda()
+    Y = G.Out(batch * OW)
+    eng.matMul_biased(Y.ptr, dX_.data_ptr(), dW_.data_ptr(), batch, OW, IW, db_.data_ptr(), OW)
+    gW = G.Out(IW * OW)
+    gz = eng.matMulT1(gW.ptr, dX_.data_ptr(), ddY.data_ptr(), IW, OW, batch)
+    gX = G.Out(batch * IW)
+    eng.matMulT2(gX.ptr, ddY.data_ptr(), dW_.data_ptr(), batch, IW, OW)
+    G.check_status(pkg)
+    X64, W64, dY64 = X.double().numpy(), W.double().numpy(), dY.double().numpy()
+    for name, got, want in (("forward", Y.host((batch, OW)), X64 @ W64 + b.double().numpy()),
+                            ("deltaW", gW.host((IW, OW)), X64.T @ dY64),
+                            ("deltaX", gX.host((batch, IW)), dY64 @ W64.T)):
+        rep = O.report(got, want)
+        assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (name, gz, rep)
+    if batch >= 32768:
+        assert gz > 1          # the long-K weight gradient takes the split-K branch
