@@ -20,7 +20,7 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
-Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged,
+Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx,
 c3_qk, c3_pv, c4, c5.
 """
 from __future__ import annotations
@@ -285,6 +285,24 @@ class Workload:
             self.flops = w.flops
             self.bytes = w.algorithmic_bytes
             self.desc = f"conv3D_GemmR N={d['N']} {d['IH']}x{d['IW']}x{d['IC']} -> {d['OC']}, 3x3 s1 p1 (remode + GEMM)"
+            self.images = d["N"]
+        elif name == "c4_dx":
+            # data gradient of config 4 (stride 1): same sizes and FLOPs, deltaY in, deltaX out, W read in place
+            w = W.config4(N=images)
+            d = w.dims
+            g = torch.Generator().manual_seed(4004)
+            dYh = torch.randn((d["N"], d["OH"], d["OW"], d["OC"]), generator=g)
+            self.hosts = [dYh.pin_memory(), w.W.pin_memory()]
+            self.dev_in = [h.cuda() for h in self.hosts]
+            self.out = torch.empty((d["N"], d["IH"], d["IW"], d["IC"]), device="cuda")
+            ddY, dW, dDX = self.dev_in[0], self.dev_in[1], self.out
+            dx = pkg.cu32.Cuda_dconv3D_deltaX
+            self.launch = lambda: dx.dconv3D_deltaX_s1(st(), 1, ddY.data_ptr(), d["OH"], d["OW"], dW.data_ptr(), d["FH"],
+                                                       d["FW"], dDX.data_ptr(), d["IH"], d["IW"], d["N"], d["IC"], d["OC"],
+                                                       w.ph, w.pw)
+            self.flops = w.flops
+            self.bytes = w.algorithmic_bytes
+            self.desc = f"dconv3D_deltaX_s1 N={d['N']} {d['OH']}x{d['OW']}x{d['OC']} -> {d['IC']}, 3x3 s1 p1"
             self.images = d["N"]
         else:
             raise SystemExit(f"unknown workload {name}")

@@ -217,7 +217,7 @@ static int run_gemm(const GemmCall& c) {
   // Batches (or split-K slices) are folded into the kernel's tile index.
   const int zs = c.gz > 1 ? c.gz : c.batch;
   if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
-  else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, p, zs, c.stream);
+  else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, false, p, zs, c.stream);
   else if (!c.a_mn)           e = launch_gemm_kk(tile, c.x3, false, p, zs, c.stream);
   else return CU32_E_ARG;
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -326,7 +326,11 @@ __global__ void remode_kernel(const float* __restrict__ W, float* __restrict__ C
 // ------------------------------------------------------------------ convolution
 static int conv_any(bool x3, const int64_t* streams, int length, const float* dX, int IH, int IW,
                     const float* dW, int FH, int FW, float* dY, int OH, int OW, int N, int IC, int OC,
-                    int sh, int sw, int ph, int pw, const float* dBias = nullptr, int width = 0) {
+                    int sh, int sw, int ph, int pw, const float* dBias = nullptr, int width = 0,
+                    bool flip = false) {
+  // flip: the filter is stored as W[IC][FH][FW][OC] (input channel outermost, output channel
+  // contiguous) and applied rotated by 180 degrees - the data-gradient of a stride-1 convolution
+  // written as a forward convolution of deltaY (see deconv_s1_any).
   load_env_once();
   cudaStream_t st;
   if (int rc = check_streams(streams, length, &st)) return rc;
@@ -350,7 +354,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
     GemmCall c{};
     c.A = dX; c.B = dW; c.C = dY; c.Cbuf = nullptr;
     c.M = static_cast<int>(GM); c.N = OC; c.K = IC; c.n_store = OC;
-    c.lda = IC; c.ldb = IC; c.ldc = OC; c.a_mn = false; c.b_mn = false;
+    c.lda = IC; c.ldb = flip ? OC : IC; c.ldc = OC; c.a_mn = false; c.b_mn = flip;   // flip: W is [IC][OC]
     c.batch = 1; c.sA = 0; c.sB = 0; c.sC = 0; c.gz = 1; c.x3 = x3; c.stream = st;
     c.bias = dBias; c.bias_width = width;
     return run_gemm(c);
@@ -395,8 +399,28 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
         static_cast<long long>(N) * IH * IW * IC * 4 < 131072)
       reinterpret_cast<uint64_t*>(&p.tmA)[1] &= ~(1ULL << 21);
   }
-  // Filters W[OC][FH*FW*IC]: reduction axis contiguous.
-  if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas, false)) return rc;
+  if (!flip) {
+    // Filters W[OC][FH*FW*IC]: reduction axis contiguous.
+    if (int rc = make_map3(&p.tmB, dW, static_cast<uint64_t>(GK), OC, 1, GK, GK * OC, 32, bn / ctas, false)) return rc;
+  } else {
+    // Filters W[IC][FH][FW][OC] read in place as one [IC x OC] matrix per tap, OC contiguous:
+    // dims (oc, ic, tap) with pitches (1, FH*FW*OC, OC); 32 x 32 boxes in the 32-byte-unit swizzle.
+    if ((OC & 3)) return CU32_E_ALIGN;
+    {
+      // dims ordered by increasing pitch: (oc, tap, ic) with pitches (1, OC, FH*FW*OC) floats; a load
+      // takes 32 oc x 1 tap x 32 ic, which lands as the 32 x 32 MN-major slab the tensor core expects
+      cuuint64_t dims[3] = {static_cast<cuuint64_t>(OC), static_cast<cuuint64_t>(FH) * FW, static_cast<cuuint64_t>(IC)};
+      cuuint64_t strides[2] = {static_cast<cuuint64_t>(OC) * 4, static_cast<cuuint64_t>(FH) * FW * OC * 4};
+      cuuint32_t box[3] = {32, 1, 32};
+      cuuint32_t estr[3] = {1, 1, 1};
+      CUresult r = g_encode_tiled(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(dW), dims, strides,
+                                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+    }
+    p.conv_flip = 1;
+  }
+  p.conv_taps = FH * FW;
 
   p.bias = dBias; p.bias_width = width;
   p.C = dY; p.Cbuf = nullptr; p.ldc = OC; p.c_stride = 0;
@@ -419,9 +443,26 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   cudaError_t e;
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
-  e = launch_gemm_kk(tile, x3, true, p, 1, st);
+  e = flip ? launch_gemm_kn(tile, x3, true, p, 1, st) : launch_gemm_kk(tile, x3, true, p, 1, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(cudaPeekAtLastError());
+}
+
+// Data gradient of a stride-1 convolution: deltaX[n,ih,iw,ic] = sum_{fh,fw,oc}
+// deltaY[n, ih+ph-fh, iw+pw-fw, oc] * W[oc,fh,fw,ic] (zero outside deltaY) - a forward convolution of
+// deltaY (OC channels in, IC channels out) with padding (FH-1-ph, FW-1-pw) and the filter rotated by
+// 180 degrees and read "transposed" in place.  The filter rotation is a reversal of the tap index in
+// the TMA producer; nothing is re-laid-out or copied.
+static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, int OH, int OW, const float* dW,
+                         int FH, int FW, float* dDX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  if (!dDY || !dW || !dDX) return CU32_E_NULL;
+  if (FH <= 0 || FW <= 0 || ph < 0 || pw < 0 || IC <= 0 || OC <= 0) return CU32_E_DIM;
+  if ((IC & 3) || (OC & 3)) return CU32_E_ALIGN;
+  if (ph > FH - 1 || pw > FW - 1) return CU32_E_GEOMETRY;   // padding larger than the filter reach
+  if (IH != OH - 1 + FH - 2 * ph || IW != OW - 1 + FW - 2 * pw) return CU32_E_DIM;
+  if (FH > 16 || FW > 16) return CU32_E_GEOMETRY;           // the tap index travels in the batch coordinate
+  return conv_any(true, streams, length, dDY, OH, OW, dW, FH, FW, dDX, IH, IW, N, /*in*/ OC, /*out*/ IC, 1, 1,
+                  FH - 1 - ph, FW - 1 - pw, nullptr, 0, true);
 }
 
 }  // namespace dragon
@@ -652,6 +693,57 @@ DRAGON_WINOGRAD_ALIAS(cu32_conv3D_Im2col_Winograd_s8_R_texture)
 DRAGON_WINOGRAD_ALIAS_SGM(cu32_conv3D_Im2col_WinogradR_s8_texture_SGM)
 DRAGON_WINOGRAD_ALIAS(cu32_conv3D_Im2col_Winograd_s16_R_texture)
 DRAGON_WINOGRAD_ALIAS_SGM(cu32_conv3D_Im2col_WinogradR_s16_texture_SGM)
+// ---- data gradient of the stride-1 convolution (the reference's Cuda_dconv3D_deltaX natives that
+// need no stride handling); W is the forward filter W[OC][FH][FW][IC], read in place
+int cu32_dconv3D_deltaX_s1(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH, int FW,
+                           float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);
+}
+int cu32_dconv3D_deltaX_s1_texture(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                                   int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);
+}
+int cu32_dconv3D_deltaX_s1_SGM(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                               int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw,
+                               int GM_slice) {
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);
+}
+int cu32_dconv3D_deltaX_s1_texture_SGM(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W,
+                                       int FH, int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph,
+                                       int pw, int GM_slice) {
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);
+}
+int cu32_dconv3D_deltaX_V2_s1(int, const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                              int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);
+}
+int cu32_dconv3D_deltaX_W1(const int64_t* s, int n, const float* dY, const float* W, float* dX, int IH, int IW,
+                           int N, int IC, int OC) {
+  return deconv_s1_any(s, n, dY, IH, IW, W, 1, 1, dX, IH, IW, N, IC, OC, 0, 0);
+}
+int cu32_dconv3D_deltaX_W1_SGM(const int64_t* s, int n, const float* dY, const float* W, float* dX, int IH, int IW,
+                               int N, int IC, int OC, int GM_slice) {
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return deconv_s1_any(s, n, dY, IH, IW, W, 1, 1, dX, IH, IW, N, IC, OC, 0, 0);
+}
+#define DRAGON_DX_WINOGRAD(name)                                                                                \
+  int name(int, const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH, int FW,       \
+           float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {                                  \
+    return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);                           \
+  }
+#define DRAGON_DX_WINOGRAD_SGM(name)                                                                            \
+  int name(int, const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH, int FW,       \
+           float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice) {                    \
+    if (GM_slice <= 0) return CU32_E_ARG;                                                                       \
+    return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw);                           \
+  }
+DRAGON_DX_WINOGRAD(cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture)
+DRAGON_DX_WINOGRAD_SGM(cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM)
+DRAGON_DX_WINOGRAD(cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture)
+DRAGON_DX_WINOGRAD_SGM(cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM)
+
 int cu32_conv3D_GemmR_W1(const int64_t* s, int n, const float* X, int IH, int IW, const float* W,
                          const float* CW, float* Y, int N, int IC, int OC) {
   (void)CW;

@@ -40,7 +40,8 @@ inline int tile_bn(int cfg) {
 //   NN : A[K][M], B[K][N]   (matMulT1, batchMatMulT1)
 cudaError_t launch_gemm_kk(int tile_cfg, bool x3, bool im2col, const GemmParams& p, int grid_z,
                            cudaStream_t stream);
-cudaError_t launch_gemm_kn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
+cudaError_t launch_gemm_kn(int tile_cfg, bool x3, bool im2col, const GemmParams& p, int grid_z,
+                           cudaStream_t stream);
 cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
 
 // Shared-memory bytes one stage of the given configuration uses (for reporting).

@@ -73,6 +73,8 @@ struct GemmParams {
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
   // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
   int conv_OW, conv_OH, conv_FW, conv_IC, conv_icb, conv_sw, conv_sh, conv_pw, conv_ph;
+  int conv_taps;        // FH * FW
+  int conv_flip;        // B is one MN-major [IC x OC] matrix per tap (tensor map (oc, tap, ic)), taps applied in reverse
 };
 
 #ifdef DRAGON_TRACE
@@ -298,9 +300,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           // im2col coordinates: k-block -> (filter tap, block of 32 channels inside the tap);
           // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
           // rows and images inside the tensor map's traversal box.
-          int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0;
+          int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0, btap = 0;
           if (Cfg::IM2COL) {
             const int tap = (w.kb0 + i) / p.conv_icb;
+            btap = tap;
             ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
             fh = tap / p.conv_FW;
             fw = tap - fh * p.conv_FW;
@@ -326,7 +329,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             } else {
               tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
             }
-            if (Cfg::B_MN) {
+            if (Cfg::B_MN && Cfg::IM2COL) {
+              // data gradient: this k-block is 32 input channels of tap (fh, fw); the filter tap
+              // that multiplies it is the mirrored one, FH*FW - 1 - tap
+#pragma unroll
+              for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
+                tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, p.conv_taps - 1 - btap, ic0, pol_b);
+            } else if (Cfg::B_MN) {
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
                 tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, k0, w.batch, pol_b);

@@ -163,6 +163,75 @@ CONV_GEMMR(conv3D_1GemmR, cu32_conv3D_GemmR)
 CONV_GEMMR(conv3D_1GemmR_1texture, cu32_conv3D_GemmR_texture)
 CONV_GEMMR_SGM(conv3D_1GemmR_1SGM, cu32_conv3D_GemmR_SGM)
 CONV_GEMMR_SGM(conv3D_1GemmR_1texture_1SGM, cu32_conv3D_GemmR_texture_SGM)
+// ---- Cuda_dconv3D_deltaX, the stride-1 natives (reference: Cuda_dconv3D_deltaX/A.cu:21-277, :837-1040)
+#define JNAME_DX(method) Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_##method
+#define DX_S1(jname, cname)                                                                               \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dDY,  \
+                                         jint OH, jint OW, jlong dW, jint FH, jint FW, jlong dDX, jint IH, \
+                                         jint IW, jint N, jint IC, jint OC, jint ph, jint pw) {            \
+    Streams s(env, streams, length);                                                                       \
+    done(env, cname(s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, IW, N, IC, OC, ph, pw)); \
+  }
+#define DX_S1_SGM(jname, cname)                                                                            \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dDY,  \
+                                         jint OH, jint OW, jlong dW, jint FH, jint FW, jlong dDX, jint IH, \
+                                         jint IW, jint N, jint IC, jint OC, jint ph, jint pw,              \
+                                         jint GM_slice) {                                                  \
+    Streams s(env, streams, length);                                                                       \
+    done(env, cname(s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, IW, N, IC, OC, ph, pw,   \
+                    GM_slice));                                                                            \
+  }
+DX_S1(dconv3D_1deltaX_1s1, cu32_dconv3D_deltaX_s1)
+DX_S1(dconv3D_1deltaX_1s1_1texture, cu32_dconv3D_deltaX_s1_texture)
+DX_S1_SGM(dconv3D_1deltaX_1s1_1SGM, cu32_dconv3D_deltaX_s1_SGM)
+DX_S1_SGM(dconv3D_1deltaX_1s1_1texture_1SGM, cu32_dconv3D_deltaX_s1_texture_SGM)
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1V2_1s1)(JNIEnv* env, jclass, jboolean useTexture,
+                                                         jlongArray streams, jint length, jlong dDY, jint OH,
+                                                         jint OW, jlong dW, jint FH, jint FW, jlong dDX, jint IH,
+                                                         jint IW, jint N, jint IC, jint OC, jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_V2_s1(useTexture ? 1 : 0, s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH,
+                                      IW, N, IC, OC, ph, pw));
+}
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                     jlong dDY, jlong dW, jlong dDX, jint IH, jint IW, jint N,
+                                                     jint IC, jint OC) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_W1(s.h, s.n, cptr(dDY), cptr(dW), mptr(dDX), IH, IW, N, IC, OC));
+}
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1W1_1SGM)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                          jlong dDY, jlong dW, jlong dDX, jint IH, jint IW,
+                                                          jint N, jint IC, jint OC, jint GM_slice) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_W1_SGM(s.h, s.n, cptr(dDY), cptr(dW), mptr(dDX), IH, IW, N, IC, OC, GM_slice));
+}
+#define DX_WINOGRAD(jname, cname)                                                                          \
+  JNIEXPORT jboolean JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, jboolean useTexture, jlongArray streams, \
+                                             jint length, jlong dDY, jint OH, jint OW, jlong dW, jint FH,  \
+                                             jint FW, jlong dDX, jint IH, jint IW, jint N, jint IC,        \
+                                             jint OC, jint ph, jint pw) {                                  \
+    Streams s(env, streams, length);                                                                       \
+    const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, \
+                         IW, N, IC, OC, ph, pw);                                                           \
+    done(env, rc);                                                                                         \
+    return rc == 0 ? 1 : 0;                                                                                \
+  }
+#define DX_WINOGRAD_SGM(jname, cname)                                                                      \
+  JNIEXPORT jboolean JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, jboolean useTexture, jlongArray streams, \
+                                             jint length, jlong dDY, jint OH, jint OW, jlong dW, jint FH,  \
+                                             jint FW, jlong dDX, jint IH, jint IW, jint N, jint IC,        \
+                                             jint OC, jint ph, jint pw, jint GM_slice) {                   \
+    Streams s(env, streams, length);                                                                       \
+    const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, \
+                         IW, N, IC, OC, ph, pw, GM_slice);                                                 \
+    done(env, rc);                                                                                         \
+    return rc == 0 ? 1 : 0;                                                                                \
+  }
+DX_WINOGRAD(Im2col_1Winograd_1s8_1texture, cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture)
+DX_WINOGRAD_SGM(Im2col_1Winograd_1s8_1texture_1SGM, cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM)
+DX_WINOGRAD(Im2col_1Winograd_1s16_1texture, cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture)
+DX_WINOGRAD_SGM(Im2col_1Winograd_1s16_1texture_1SGM, cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM)
+
 // Contraction + bias row in one pass.  These natives do not exist in the reference's Java classes; a
 // maintainer who wants the fusion declares them and calls them from
 // CudaFloat32EngineBase.matMul_biased / conv3D_biased instead of the two-kernel sequence.

@@ -80,6 +80,17 @@ SIGNATURES = {
     "cu32_conv3D_GemmR_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _fp] + [_I] * 10,
     "cu32_conv3D_GemmR_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_conv3D_GemmR_W1_SGM": [_sp, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I, _I],
+    "cu32_dconv3D_deltaX_s1": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_s1_texture": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_s1_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaX_s1_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaX_V2_s1": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_W1": [_sp, _I, _fp, _fp, _fp] + [_I] * 5,
+    "cu32_dconv3D_deltaX_W1_SGM": [_sp, _I, _fp, _fp, _fp] + [_I] * 6,
+    "cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -453,3 +464,84 @@ class Cuda_conv3D:
         if bm <= Cuda_conv3D.max_grid:
             return -1
         return Cuda_conv3D.grid_slice << (7 if flag else 6)
+
+
+class Cuda_dconv3D_deltaX:
+    """Mirror of the stride-1 natives of z.dragon.engine.cuda.impl.math.Cuda_dconv3D_deltaX (the data gradient
+    of the forward convolution; reference: Cuda_dconv3D_deltaX/A.cu:21-277, :837-1040).  The natives for
+    strides > 1 (kernelSplit, ksIms*, crossAdd) are not covered."""
+
+    @staticmethod
+    def _s1(name, lead, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, *tail):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_" + name)(*lead, s, n, _p(d_deltaY), OH, OW, _p(dW), FH, FW, _p(d_deltaX), IH, IW,
+                                               N, IC, OC, ph, pw, *tail), name)
+
+    @staticmethod
+    def dconv3D_deltaX_s1(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw):
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_s1", (), streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH,
+                                IW, N, IC, OC, ph, pw)
+
+    @staticmethod
+    def dconv3D_deltaX_s1_texture(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph,
+                                  pw):
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_s1_texture", (), streamArray, length, d_deltaY, OH, OW, dW, FH, FW,
+                                d_deltaX, IH, IW, N, IC, OC, ph, pw)
+
+    @staticmethod
+    def dconv3D_deltaX_s1_SGM(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw,
+                              GM_slice):
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_s1_SGM", (), streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX,
+                                IH, IW, N, IC, OC, ph, pw, GM_slice)
+
+    @staticmethod
+    def dconv3D_deltaX_s1_texture_SGM(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC,
+                                      ph, pw, GM_slice):
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_s1_texture_SGM", (), streamArray, length, d_deltaY, OH, OW, dW, FH, FW,
+                                d_deltaX, IH, IW, N, IC, OC, ph, pw, GM_slice)
+
+    @staticmethod
+    def dconv3D_deltaX_V2_s1(useTexture, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC,
+                             OC, ph, pw):
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_V2_s1", (int(bool(useTexture)),), streamArray, length, d_deltaY, OH, OW,
+                                dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw)
+
+    @staticmethod
+    def dconv3D_deltaX_W1(streamArray, length, d_deltaY, dW, d_deltaX, IH, IW, N, IC, OC):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_W1(s, n, _p(d_deltaY), _p(dW), _p(d_deltaX), IH, IW, N, IC, OC),
+               "dconv3D_deltaX_W1")
+
+    @staticmethod
+    def dconv3D_deltaX_W1_SGM(streamArray, length, d_deltaY, dW, d_deltaX, IH, IW, N, IC, OC, GM_slice):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_W1_SGM(s, n, _p(d_deltaY), _p(dW), _p(d_deltaX), IH, IW, N, IC, OC, GM_slice),
+               "dconv3D_deltaX_W1_SGM")
+
+    @staticmethod
+    def Im2col_Winograd_s8_texture(useTexture, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N,
+                                   IC, OC, ph, pw) -> bool:
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_Im2col_Winograd_s8_texture", (int(bool(useTexture)),), streamArray,
+                                length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw)
+        return True
+
+    @staticmethod
+    def Im2col_Winograd_s8_texture_SGM(useTexture, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW,
+                                       N, IC, OC, ph, pw, GM_slice) -> bool:
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM", (int(bool(useTexture)),), streamArray,
+                                length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, GM_slice)
+        return True
+
+    @staticmethod
+    def Im2col_Winograd_s16_texture(useTexture, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N,
+                                    IC, OC, ph, pw) -> bool:
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_Im2col_Winograd_s16_texture", (int(bool(useTexture)),), streamArray,
+                                length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw)
+        return True
+
+    @staticmethod
+    def Im2col_Winograd_s16_texture_SGM(useTexture, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH,
+                                        IW, N, IC, OC, ph, pw, GM_slice) -> bool:
+        Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM", (int(bool(useTexture)),), streamArray,
+                                length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, GM_slice)
+        return True

@@ -226,6 +226,54 @@ CU32_API int cu32_conv3D_Im2col_WinogradR_s16_texture_SGM(int useTexture, const 
                         int FW, float* dY, int OH, int OW, int N, int IC, int OC, int ph, int pw,
                         int GM_slice);
 
+/* ------------------------------------------------------------------ Cuda_dconv3D_deltaX, stride 1
+ * Data gradient of the forward convolution above for stride 1 (file:line below are in
+ * engine-cuda-base/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/):
+ *   deltaX[n,ih,iw,ic] = sum_{fh,fw,oc} deltaY[n, ih+ph-fh, iw+pw-fw, oc] * W[oc,fh,fw,ic], zero outside deltaY;
+ *   deltaY[N,OH,OW,OC], W[OC,FH,FW,IC] (the forward filter, unchanged), deltaX[N,IH,IW,IC],
+ *   IH = OH - 1 + FH - 2*ph (and likewise for the width); IC % 4 == 0, OC % 4 == 0.
+ * It runs as a forward implicit GEMM over deltaY with padding (FH-1-ph, FW-1-pw) and the filter taps
+ * reversed, W being read where it lies.  The natives of that project that handle strides > 1
+ * (kernelSplit, ksIms*, crossAdd and their remode helpers) are not covered.
+ *   cu32_dconv3D_deltaX_s1[_texture][_SGM]   replace JNI dconv3D_deltaX_s1 (A.cu:21-42), _s1_SGM (:45-94),
+ *                                            _s1_texture (:97-120), _s1_texture_SGM (:123-174)
+ *   cu32_dconv3D_deltaX_W1[_SGM]             replace JNI dconv3D_deltaX_W1 (:177-196), _W1_SGM (:199-240): 1x1 filter
+ *   cu32_dconv3D_deltaX_V2_s1                replaces JNI dconv3D_deltaX_V2_s1 (:243-277)
+ *   cu32_dconv3D_deltaX_Im2col_Winograd_s8/s16_texture[_SGM]   replace JNI Im2col_Winograd_* (:837-1040); the
+ *                                            JNI shim returns "handled" = true whenever the return code is 0
+ * useTexture and GM_slice are accepted and ignored. */
+CU32_API int cu32_dconv3D_deltaX_s1(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC,
+                           int OC, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_s1_texture(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC,
+                           int OC, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_s1_SGM(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC,
+                           int OC, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_s1_texture_SGM(const int64_t* streams, int length, const float* d_deltaY, int OH,
+                           int OW, const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N,
+                           int IC, int OC, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_V2_s1(int useTexture, const int64_t* streams, int length, const float* d_deltaY,
+                           int OH, int OW, const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW,
+                           int N, int IC, int OC, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_W1(const int64_t* streams, int length, const float* d_deltaY, const float* dW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC);
+CU32_API int cu32_dconv3D_deltaX_W1_SGM(const int64_t* streams, int length, const float* d_deltaY, const float* dW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture(int useTexture, const int64_t* streams, int length,
+                           const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM(int useTexture, const int64_t* streams, int length,
+                           const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture(int useTexture, const int64_t* streams, int length,
+                           const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM(int useTexture, const int64_t* streams, int length,
+                           const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
+                           float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
+
 /* ------------------------------------------------------------------ contraction + bias row
  * No counterpart among the reference's natives.  The Java engine's matMul_biased / conv3D_biased
  * (CudaFloat32EngineBase.java:1594-1688, :2389-2542) run the contraction and then, as a second

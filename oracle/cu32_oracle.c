@@ -12,6 +12,7 @@
  *                                        Cuda_batchMatMul/test.cuh:69-89
  *   buf_summary (Kahan)                  Cuda_matMul/Cuda_matMul/SKbufsum.cuh:29-68
  *   filter remode W[OC,FH,FW,IC] -> CW[FH,FW,IC,OC]   Cuda_conv3D/conv3D_kernel_remode_V1.cuh:50-196
+ *   deconv3D_deltaX_img2col_s1 (float accumulator)   engine-cuda-base/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:154-196
  *   linear_dual2D_row (the bias-row add the engine applies right after matMul / conv3D;
  *   a GPU kernel, restated element by element)        Cuda_function/Cuda_function/type1_linear_dual2D_row.cuh:41-70
  * Loop order and accumulation type follow the reference exactly (k outermost, FP32 "+=" into
@@ -175,6 +176,55 @@ void oracle_buf_summary(const float* Cbuf, float* C, int part, int sizeC) {
     }
     C[i] = v;
   }
+}
+
+/* Data gradient of the stride-1 convolution, the reference's check loop: for every input pixel and
+ * channel, a float accumulator over k = (oc, fh, fw) in that order, the filter applied rotated:
+ * deltaX[n,ih,iw,ic] = sum deltaY[n, ih-(FH-1-ph)+fh, iw-(FW-1-pw)+fw, oc] * W[oc, FH-1-fh, FW-1-fw, ic]. */
+void oracle_deconv3D_deltaX_img2col_s1(const float* deltaY, int OH, int OW, const float* W, int FH, int FW,
+                                       float* deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  const int oph = FH - ph - 1, opw = FW - pw - 1;
+  const int GK = OC * FH * FW;
+  for (int ic = 0; ic < IC; ic++)
+    for (int j = 0; j < N * IH * IW; j++) {
+      const int n = j / (IH * IW), jr = j % (IH * IW);
+      const int ih = jr / IW, iw = jr % IW;
+      float v = 0;
+      for (int k = 0; k < GK; k++) {
+        const int oc = k / (FH * FW), kr = k % (FH * FW);
+        const int fh = kr / FW, fw = kr % FW;
+        const int oh = ih - oph + fh, ow = iw - opw + fw;
+        if (oh < 0 || ow < 0 || oh >= OH || ow >= OW) continue;
+        v += deltaY[(((size_t)n * OH + oh) * OW + ow) * OC + oc] *
+             W[(((size_t)oc * FH + (FH - 1 - fh)) * FW + (FW - 1 - fw)) * IC + ic];
+      }
+      deltaX[(((size_t)n * IH + ih) * IW + iw) * IC + ic] = v;
+    }
+}
+
+/* The same gradient with an FP64 accumulator (accuracy oracle). */
+void oracle_deconv3D_deltaX_s1_f64(const float* deltaY, int OH, int OW, const float* W, int FH, int FW,
+                                   double* deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  for (int n = 0; n < N; n++)
+    for (int ih = 0; ih < IH; ih++)
+      for (int iw = 0; iw < IW; iw++) {
+        double* out = deltaX + (((size_t)n * IH + ih) * IW + iw) * IC;
+        for (int ic = 0; ic < IC; ic++) out[ic] = 0.0;
+        for (int fh = 0; fh < FH; fh++) {
+          const int oh = ih + ph - fh;
+          if (oh < 0 || oh >= OH) continue;
+          for (int fw = 0; fw < FW; fw++) {
+            const int ow = iw + pw - fw;
+            if (ow < 0 || ow >= OW) continue;
+            const float* dy = deltaY + (((size_t)n * OH + oh) * OW + ow) * OC;
+            for (int oc = 0; oc < OC; oc++) {
+              const float* w = W + (((size_t)oc * FH + fh) * FW + fw) * IC;
+              const double d = dy[oc];
+              for (int ic = 0; ic < IC; ic++) out[ic] += d * (double)w[ic];
+            }
+          }
+        }
+      }
 }
 
 /* Y[i] = alpha*X1[i] + beta*X2[i % row_lengthv] + gamma for every element of the padded

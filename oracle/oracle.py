@@ -145,6 +145,17 @@ class ref_loops:
         return C
 
     @staticmethod
+    def deconv3D_deltaX_img2col_s1(deltaY, W, IH, IW, ph, pw):
+        """deltaY [N, OH, OW, OC], W [OC, FH, FW, IC] -> deltaX [N, IH, IW, IC], the reference's float-accumulator
+        check loop for the stride-1 data gradient (Cuda_dconv3D_deltaX/test.cuh:154-196)."""
+        deltaY, W = _c32(deltaY), _c32(W)
+        N, OH, OW, OC = deltaY.shape
+        _, FH, FW, IC = W.shape
+        dX = np.zeros((N, IH, IW, IC), np.float32)
+        lib().oracle_deconv3D_deltaX_img2col_s1(_f(deltaY), OH, OW, _f(W), FH, FW, _f(dX), IH, IW, N, IC, OC, ph, pw)
+        return dX
+
+    @staticmethod
     def linear_dual2D_row(X1, X2, alpha, beta, gamma, width):
         """X1 [height, stride] (stride = padded row length), X2 [stride]: Y = alpha*X1 + beta*X2 + gamma per
         row, columns >= width zeroed (Cuda_function/type1_linear_dual2D_row.cuh:41-70)."""
@@ -235,6 +246,19 @@ class f64:
 
 
 # ------------------------------------------------------------------ metrics
+def f64_deconv3D_deltaX_s1(deltaY, W, IH, IW, ph, pw):
+    """FP64 data gradient of the stride-1 convolution (accuracy oracle for the deltaX entry points)."""
+    deltaY, W = _c32(deltaY), _c32(W)
+    N, OH, OW, OC = deltaY.shape
+    _, FH, FW, IC = W.shape
+    dX = np.zeros((N, IH, IW, IC), np.float64)
+    lib().oracle_deconv3D_deltaX_s1_f64(_f(deltaY), OH, OW, _f(W), FH, FW, _d(dX), IH, IW, N, IC, OC, ph, pw)
+    return dX
+
+
+f64.deconv3D_deltaX_s1 = staticmethod(f64_deconv3D_deltaX_s1)
+
+
 def frob_rel(C, C64) -> float:
     C64 = np.asarray(C64, np.float64)
     d = np.asarray(C, np.float64) - C64
