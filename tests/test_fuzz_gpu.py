@@ -135,3 +135,28 @@ def test_fuzz_biased(pkg, O, cuda):
                                st, st, pad, pad, db.data_ptr(), width)
         assert np.array_equal(out.host((N, OH, OW, OC)), want), (N, IH, IW, IC, OC, F, st, width)
     G.check_status(pkg)
+
+
+def test_fuzz_deltax(pkg, O, cuda):
+    """Random stride-1 geometries through the data-gradient entry point, each against the FP64 oracle."""
+    dx = pkg.cu32.Cuda_dconv3D_deltaX
+    rng = np.random.default_rng(88)
+    s = [G.stream()]
+    for case in range(30):
+        N = int(rng.integers(1, 6))
+        FH, FW = int(rng.integers(1, 8)), int(rng.integers(1, 8))
+        ph, pw = int(rng.integers(0, FH)), int(rng.integers(0, FW))
+        IH = int(rng.integers(max(1, FH - 2 * ph), 20 + FH))
+        IW = int(rng.integers(max(1, FW - 2 * pw), 20 + FW))
+        OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+        if OH < 1 or OW < 1:
+            continue
+        IC, OC = int(rng.integers(1, 48)) * 4, int(rng.integers(1, 48)) * 4
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+        ddY, dW = G.dev(dY), G.dev(W)
+        out = G.Out(N * IH * IW * IC)
+        dx.dconv3D_deltaX_s1(s, 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), FH, FW, out.ptr, IH, IW, N, IC, OC, ph, pw)
+        _acc(O, out.host((N, IH, IW, IC)), O.f64.deconv3D_deltaX_s1(dY, W, IH, IW, ph, pw),
+             f"deltaX {(N, IH, IW, IC, OC, FH, FW, ph, pw)}")
+    G.check_status(pkg)
