@@ -148,3 +148,37 @@ def test_jni_matmul_and_conv_on_gpu(pkg, O, cuda):
     torch.cuda.synchronize()
     assert np.array_equal(dCW.cpu().numpy().reshape(3, 3, 16, 8), O.ref_loops.kernel_remode(W))
     G.check_status(pkg)
+
+
+@pytest.mark.gpu
+def test_jni_deltax_on_gpu(pkg, O, cuda):
+    """The stride-1 data-gradient natives under their JNI names (class Cuda_dconv3D_deltaX)."""
+    import gpu_util as G
+    lib = pkg.cu32.load()
+    jni = FakeJNI([G.stream()])
+    rng = np.random.default_rng(9)
+    N, IH, IW, IC, OC, F, p = 2, 10, 9, 8, 12, 3, 1
+    dY = rng.standard_normal((N, IH, IW, OC)).astype(np.float32)
+    W = rng.standard_normal((OC, F, F, IC)).astype(np.float32) * 0.1
+    ddY, dW = G.dev(dY), G.dev(W)
+    want = O.f64.deconv3D_deltaX_s1(dY, W, IH, IW, p, p)
+    sig = [c_void_p, c_int32, c_int64, c_int32, c_int32, c_int64, c_int32, c_int32, c_int64] + [c_int32] * 7
+    out = G.Out(N * IH * IW * IC)
+    f = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_dconv3D_1deltaX_1s1")
+    f.argtypes = [c_void_p, c_void_p] + sig
+    f.restype = None
+    f(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out.ptr, IH, IW, N, IC, OC, p, p)
+    base = out.host((N, IH, IW, IC)).copy()
+    rep = O.report(base, want)
+    assert jni.thrown is None and rep["frob"] <= 1e-6, rep
+    out2 = G.Out(N * IH * IW * IC)
+    w = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_Im2col_1Winograd_1s8_1texture")
+    w.argtypes = [c_void_p, c_void_p, ctypes.c_uint8] + sig
+    w.restype = ctypes.c_uint8
+    assert w(jni.env, None, 1, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out2.ptr, IH, IW, N, IC, OC,
+             p, p) == 1
+    assert np.array_equal(out2.host((N, IH, IW, IC)), base)
+    # inconsistent geometry becomes a CudaException(-2), nothing is launched
+    f(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out.ptr, IH + 1, IW, N, IC, OC, p, p)
+    assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
+    G.check_status(pkg)
