@@ -1,7 +1,8 @@
 """Generate the golden fixtures in this directory from the REFERENCE'S OWN CPU routines.
 
 Run in a container that has the reference tree: ``python oracle/build_ref.py [--conv]`` builds
-the reference's test.cuh loops (multiply*, bmm*, CONV_3D_NAIVE, CONV_3D_img2col) into
+the reference's test.cuh loops (multiply*, bmm*, CONV_3D_NAIVE, CONV_3D_img2col, and with --deltax
+deconv3D_deltaX_img2col_s1) into
 oracle/_ref/, and this script runs them on small seeded inputs and stores inputs' seeds,
 shapes and the outputs as .npz.  The fixtures then travel with the repository, so the CPU
 oracle (tests/test_oracle.py) and the GPU kernels (tests/test_parity_gpu.py) can be checked
@@ -46,6 +47,15 @@ CONV_CASES = {
     "conv_5x3_s2p2": (4, 11, 10, 4, 8, 5, 3, 2, 2, 2, 1),
     "conv_1x1": (4, 6, 6, 16, 20, 1, 1, 1, 1, 0, 0),
     "conv_3x3_np": (4, 8, 8, 36, 8, 3, 3, 1, 1, 0, 0),
+}
+
+
+DELTAX_CASES = {
+    # stride-1 data gradient: N, IH, IW, IC, OC, FH, FW, ph, pw
+    "dx_3x3_p1": (3, 9, 8, 8, 12, 3, 3, 1, 1),
+    "dx_5x3_p2p0": (2, 10, 11, 4, 8, 5, 3, 2, 0),
+    "dx_1x1": (4, 6, 6, 16, 20, 1, 1, 0, 0),
+    "dx_2x4_p1p3": (2, 7, 9, 12, 4, 2, 4, 1, 3),
 }
 
 
@@ -119,6 +129,24 @@ def main():
         out[name + "/img2col"] = Y2
     np.savez_compressed(HERE / "golden_conv.npz", **out)
     print("wrote golden_conv.npz:", len(out), "arrays")
+    make_deltax(O)
+
+
+def make_deltax(O):
+    """Stride-1 data gradient from the reference's deconv3D_deltaX_img2col_s1 (oracle/_ref/libref_deltax.so)."""
+    dx = O.ref_native("deltax")
+    if dx is None:
+        print("libref_deltax.so absent: deltaX fixtures not regenerated (python oracle/build_ref.py --deltax)")
+        return
+    out = {}
+    for name, (N, IH, IW, IC, OC, FH, FW, ph, pw) in DELTAX_CASES.items():
+        OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+        dY, W = golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        dX = np.zeros((N, IH, IW, IC), np.float32)
+        dx.ref_cpu_deconv3D_deltaX_img2col_s1(_p(dY), OH, OW, _p(W), FH, FW, _p(dX), IH, IW, N, IC, OC, ph, pw)
+        out[name] = dX
+    np.savez_compressed(HERE / "golden_deltax.npz", **out)
+    print("wrote golden_deltax.npz:", len(out), "cases")
 
 
 if __name__ == "__main__":

@@ -65,6 +65,15 @@ def test_deltax_oracle_against_reference_routine_when_built(O):
         assert np.array_equal(out, O.ref_loops.deconv3D_deltaX_img2col_s1(dY, W, IH, IW, ph, pw)), case
 
 
+def test_deltax_oracle_against_golden_fixture(O, golden):
+    """tests/golden/golden_deltax.npz holds the outputs of the reference's own check loop on seeded inputs."""
+    data = np.load(golden.HERE / "golden_deltax.npz")
+    for name, (N, IH, IW, IC, OC, FH, FW, ph, pw) in golden.DELTAX_CASES.items():
+        OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+        dY, W = golden.golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        assert np.array_equal(O.ref_loops.deconv3D_deltaX_img2col_s1(dY, W, IH, IW, ph, pw), data[name]), name
+
+
 def test_deltax_argument_errors_without_gpu(pkg):
     lib = pkg.cu32.load()
     s = (ctypes.c_int64 * 1)(0)
@@ -214,3 +223,15 @@ def test_deltax_against_reference_kernels(pkg, O, cuda):
     e_ref, e_our = O.frob_rel(R, want), O.frob_rel(got, want)
     assert e_ref <= 5e-6, e_ref
     assert e_our <= 1e-6 and O.frob_rel(got, R) <= 5e-6, (e_our, e_ref)
+
+
+@pytest.mark.gpu
+def test_deltax_against_golden_fixture(pkg, O, cuda, golden):
+    data = np.load(golden.HERE / "golden_deltax.npz")
+    for name, (N, IH, IW, IC, OC, FH, FW, ph, pw) in golden.DELTAX_CASES.items():
+        OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+        dY, W = golden.golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        entry = "dconv3D_deltaX_W1" if (FH, FW) == (1, 1) else "dconv3D_deltaX_s1"
+        got = _run(pkg, entry, dY, W, IH, IW, ph, pw)
+        assert O.frob_rel(got, data[name]) <= 2e-6, name          # the golden output carries FP32 accumulation error
+        assert O.same_percent(got, data[name], 1e-5) >= 0.999, name  # the reference's own gate, non-negative inputs
