@@ -197,6 +197,19 @@ class Cu32Engine:
         else:
             Cuda_conv3D.conv3D_GemmR_SGM(sa, 1, X, IH, IW, W, CW, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw, sl)
 
+    def conv3D_deltaX(self, deltaX, IH, IW, deltaY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw):
+        """Data gradient the way the Java engine runs its stride-1 branch (CudaFloat32EngineBase.java:3773-3820):
+        1x1 filters take the W1 native, everything else the zero-padding s1 native.  Strides > 1 use natives this
+        library does not export."""
+        if sh != 1 or sw != 1:
+            raise NotImplementedError("data gradient for strides > 1: natives of Cuda_dconv3D_deltaX not covered here")
+        from .cu32 import Cuda_dconv3D_deltaX as dx
+        sa = self.streams[:1]
+        if FH == 1 and FW == 1 and ph == 0 and pw == 0:
+            dx.dconv3D_deltaX_W1(sa, 1, deltaY, W, deltaX, IH, IW, N, IC, OC)
+        else:
+            dx.dconv3D_deltaX_s1(sa, 1, deltaY, OH, OW, W, FH, FW, deltaX, IH, IW, N, IC, OC, ph, pw)
+
     def release(self):
         """Drop the workspaces (the Java Syncer frees them after the streams complete)."""
         self._keep.clear()

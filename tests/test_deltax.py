@@ -235,3 +235,34 @@ def test_deltax_against_golden_fixture(pkg, O, cuda, golden):
         got = _run(pkg, entry, dY, W, IH, IW, ph, pw)
         assert O.frob_rel(got, data[name]) <= 2e-6, name          # the golden output carries FP32 accumulation error
         assert O.same_percent(got, data[name], 1e-5) >= 0.999, name  # the reference's own gate, non-negative inputs
+
+
+@pytest.mark.gpu
+def test_conv_layer_forward_and_data_gradient_through_the_engine_mirror(pkg, O, cuda):
+    import gpu_util as G
+    torch = cuda
+    keep = []
+
+    def malloc(n):
+        t = torch.empty(n, device="cuda")
+        keep.append(t)
+        return t.data_ptr(), t
+    eng = pkg.engine.Cu32Engine(148, malloc, [G.stream()])
+    rng = np.random.default_rng(66)
+    for (N, IH, IW, IC, OC, F, p) in [(4, 14, 14, 32, 64, 3, 1), (4, 10, 10, 16, 24, 1, 0)]:
+        OH, OW = IH + 2 * p - F + 1, IW + 2 * p - F + 1
+        X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+        W = (rng.standard_normal((OC, F, F, IC)) * 0.1).astype(np.float32)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        dX_, dW_, ddY = G.dev(X), G.dev(W), G.dev(dY)
+        Y = G.Out(N * OH * OW * OC)
+        eng.conv3D(Y.ptr, OH, OW, dX_.data_ptr(), IH, IW, dW_.data_ptr(), F, F, N, IC, OC, 1, 1, p, p)
+        gX = G.Out(N * IH * IW * IC)
+        eng.conv3D_deltaX(gX.ptr, IH, IW, ddY.data_ptr(), OH, OW, dW_.data_ptr(), F, F, N, IC, OC, 1, 1, p, p)
+        G.check_status(pkg)
+        for name, got, want in (("forward", Y.host((N, OH, OW, OC)), O.f64.conv3D(X, W, OH, OW, 1, 1, p, p)),
+                                ("deltaX", gX.host((N, IH, IW, IC)), O.f64.deconv3D_deltaX_s1(dY, W, IH, IW, p, p))):
+            rep = O.report(got, want)
+            assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (name, F, rep)
+    with pytest.raises(NotImplementedError):
+        eng.conv3D_deltaX(0, 8, 8, 0, 4, 4, 0, 3, 3, 1, 4, 4, 2, 2, 1, 1)
