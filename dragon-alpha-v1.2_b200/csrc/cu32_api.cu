@@ -418,9 +418,8 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
     }
-    p.conv_flip = 1;
+    p.tap_base = FH * FW - 1; p.tap_sy = -FW; p.tap_sx = -1; p.bmap_order = 0;   // rotated by 180 degrees
   }
-  p.conv_taps = FH * FW;
 
   p.bias = dBias; p.bias_width = width;
   p.C = dY; p.Cbuf = nullptr; p.ldc = OC; p.c_stride = 0;
@@ -463,6 +462,173 @@ static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, i
   if (FH > 16 || FW > 16) return CU32_E_GEOMETRY;           // the tap index travels in the batch coordinate
   return conv_any(true, streams, length, dDY, OH, OW, dW, FH, FW, dDX, IH, IW, N, /*in*/ OC, /*out*/ IC, 1, 1,
                   FH - 1 - ph, FW - 1 - pw, nullptr, 0, true);
+}
+
+// ------------------------------------------------------------------ kernel-split filter workspace
+// CW[y][x][...] for the sh*sw phases of the strided data gradient: phase (y, x) holds the taps
+// fh = y + (CFH_y - 1 - fhr) * sh, fw = x + (CFW_x - 1 - fwr) * sw of W[OC][FH][FW][IC] (zeros where the tap
+// does not exist), packed at the start of a slot of OC * mCFH * mCFW * IC floats.  V2 orders a phase as
+// [fhr][fwr][oc][ic], the older form as [oc][fhr][fwr][ic]; elements of a slot past the phase's own size
+// are left untouched, as in the reference.
+template <bool V2>
+__global__ void ks_remode_kernel(const float* __restrict__ W, int FH, int FW, float* __restrict__ CW, int mCFH,
+                                 int mCFW, int OC, int IC, int sh, int sw) {
+  const int by = blockIdx.y;
+  CW += static_cast<long long>(by) * OC * mCFH * mCFW * IC;
+  const int y = by / sw, x = by - y * sw;
+  const int CFH = (FH - y + sh - 1) / sh, CFW = (FW - x + sw - 1) / sw;
+  if (CFH <= 0 || CFW <= 0) return;
+  const long long n = static_cast<long long>(OC) * CFH * CFW * IC;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int oc, fhr, fwr, ic;
+    long long r = i;
+    if (V2) {
+      fhr = static_cast<int>(r / (static_cast<long long>(CFW) * OC * IC)); r -= static_cast<long long>(fhr) * CFW * OC * IC;
+      fwr = static_cast<int>(r / (static_cast<long long>(OC) * IC));       r -= static_cast<long long>(fwr) * OC * IC;
+      oc = static_cast<int>(r / IC); ic = static_cast<int>(r - static_cast<long long>(oc) * IC);
+    } else {
+      oc = static_cast<int>(r / (static_cast<long long>(CFH) * CFW * IC)); r -= static_cast<long long>(oc) * CFH * CFW * IC;
+      fhr = static_cast<int>(r / (static_cast<long long>(CFW) * IC));      r -= static_cast<long long>(fhr) * CFW * IC;
+      fwr = static_cast<int>(r / IC); ic = static_cast<int>(r - static_cast<long long>(fwr) * IC);
+    }
+    const int fh = y + (CFH - 1 - fhr) * sh, fw = x + (CFW - 1 - fwr) * sw;
+    CW[i] = (fh < FH && fw < FW) ? W[((static_cast<long long>(oc) * FH + fh) * FW + fw) * IC + ic] : 0.0f;
+  }
+}
+
+static int ks_remode_any(bool v2, int64_t stream, const float* dW, int FH, int FW, float* dCW, int CFH, int CFW, int OC,
+                         int IC, int sh, int sw) {
+  if (!dW || !dCW) return CU32_E_NULL;
+  if (FH <= 0 || FW <= 0 || OC <= 0 || IC <= 0 || sh <= 0 || sw <= 0) return CU32_E_DIM;
+  if (CFH != (FH + sh - 1) / sh || CFW != (FW + sw - 1) / sw) return CU32_E_DIM;
+  if (static_cast<long long>(sh) * sw > 65535) return CU32_E_DIM;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
+  const long long n = static_cast<long long>(OC) * CFH * CFW * IC;
+  long long bx = (n + 255) / 256;
+  if (bx > 148 * 8) bx = 148 * 8;
+  const dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(sh * sw));
+  if (v2) ks_remode_kernel<true><<<grid, 256, 0, st>>>(dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
+  else    ks_remode_kernel<false><<<grid, 256, 0, st>>>(dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+// Data gradient for any stride, as sh*sw stride-1 sub-problems ("kernel split"): the input pixels ih with
+// (ih + ph) % sh == y only ever meet the filter taps fh = y, y + sh, y + 2 sh, ...  For such a phase (y, x)
+//   deltaX[n, sh*u + y - ph, sw*v + x - pw, :] = sum_{t, r, oc} deltaY[n, u - t, v - r, oc] * W[oc, y + sh*t, x + sw*r, :]
+// which is a forward stride-1 convolution of deltaY with a CFH x CFW sub-filter (taps in reverse order) whose
+// output rows are strided pixels of deltaX.  Each phase is one launch of the same kernel: im2col A over deltaY
+// with the phase's corners, the sub-filter's [OC x IC] matrices picked tap by tap - from the forward filter where it
+// lies, or from the reference's kernel-split workspace CW[y][x][CFH][CFW][OC][IC] - and register stores to the
+// strided rows.
+static int ceil_div(int a, int b) { return a >= 0 ? (a + b - 1) / b : -((-a) / b); }
+
+static int deconv_strided_any(const int64_t* streams, int length, const float* dDY, int OH, int OW,
+                              const float* filt, bool filt_is_cw, int FH, int FW, float* dDX, int IH, int IW, int N,
+                              int IC, int OC, int sh, int sw, int ph, int pw) {
+  load_env_once();
+  cudaStream_t st;
+  if (int rc = check_streams(streams, length, &st)) return rc;
+  if (!dDY || !filt || !dDX) return CU32_E_NULL;
+  if (IH <= 0 || IW <= 0 || OH <= 0 || OW <= 0 || FH <= 0 || FW <= 0 || N <= 0 || IC <= 0 || OC <= 0 || sh <= 0 ||
+      sw <= 0 || ph < 0 || pw < 0)
+    return CU32_E_DIM;
+  if ((IC & 3) || (OC & 3) || !aligned16(dDY) || !aligned16(filt) || !aligned16(dDX)) return CU32_E_ALIGN;
+  if (IH + 2 * ph < FH || IW + 2 * pw < FW || OH != (IH + 2 * ph - FH) / sh + 1 || OW != (IW + 2 * pw - FW) / sw + 1)
+    return CU32_E_DIM;
+  if (static_cast<long long>(N) * IH * IW * IC >= (1LL << 31) || static_cast<long long>(N) * OH * OW * OC >= (1LL << 31))
+    return CU32_E_DIM;
+  if (sh > 16 || sw > 16 || FH > 256 || FW > 256) return CU32_E_GEOMETRY;
+  if (!load_driver_entry_points() || !g_encode_im2col) return CU32_E_DRIVER;
+  const int mCFH = (FH + sh - 1) / sh, mCFW = (FW + sw - 1) / sw;
+  cudaError_t e;
+  if (FH < sh || FW < sw) {   // some phases meet no tap at all: their pixels are zero
+    e = cudaMemsetAsync(dDX, 0, sizeof(float) * static_cast<size_t>(N) * IH * IW * IC, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  int* status = status_word_ptr(&e);
+  if (!status) return static_cast<int>(e);
+  for (int y = 0; y < sh; ++y)
+    for (int x = 0; x < sw; ++x) {
+      if (y >= FH || x >= FW) continue;
+      const int CFH = (FH - y + sh - 1) / sh, CFW = (FW - x + sw - 1) / sw;
+      const int u0 = ceil_div(ph - y, sh), v0 = ceil_div(pw - x, sw);
+      const int nu = IH - 1 + ph - y, nv = IW - 1 + pw - x;
+      if (nu < 0 || nv < 0) continue;
+      const int U = nu / sh - u0 + 1, V = nv / sw - v0 + 1;
+      if (U <= 0 || V <= 0) continue;
+      const int lower_h = u0 - (CFH - 1), lower_w = v0 - (CFW - 1);
+      const int upper_h = lower_h + (U - 1) - (OH - 1), upper_w = lower_w + (V - 1) - (OW - 1);
+      if (lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 || upper_w < -128 || upper_w > 127 ||
+          upper_h < -128 || upper_h > 127)
+        return CU32_E_GEOMETRY;
+      const long long GM = static_cast<long long>(N) * U * V;
+      int tile = pick_tile(GM, IC, 1);
+      if (tile_is_ts(tile)) tile = TILE_1x256;
+      const int ctas = tile_ctas(tile), bn = tile_bn(tile);
+      GemmParams p;
+      std::memset(&p, 0, sizeof(p));
+      {
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(OC), static_cast<cuuint64_t>(OW), static_cast<cuuint64_t>(OH),
+                              static_cast<cuuint64_t>(N)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(OC) * 4, static_cast<cuuint64_t>(OW) * OC * 4,
+                                 static_cast<cuuint64_t>(OH) * OW * OC * 4};
+        int lower[2] = {lower_w, lower_h};
+        int upper[2] = {upper_w, upper_h};
+        cuuint32_t trav[4] = {1, 1, 1, 1};
+        CUresult r = g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dDY), dims, strides,
+                                     lower, upper, 32, 128, trav, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+        int drv = 0;   // same driver workaround as in conv_any
+        if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
+            static_cast<long long>(N) * OH * OW * OC * 4 < 131072)
+          reinterpret_cast<uint64_t*>(&p.tmA)[1] &= ~(1ULL << 21);
+      }
+      if (filt_is_cw) {
+        // this phase's slot of CW: [CFH][CFW][OC][IC], taps already reversed by ks_remodev2
+        const float* base = filt + static_cast<long long>(y * sw + x) * OC * mCFH * mCFW * IC;
+        if (int rc = make_map3(&p.tmB, base, IC, OC, static_cast<uint64_t>(CFH) * CFW, IC,
+                               static_cast<uint64_t>(OC) * IC, 32, 32, true))
+          return rc;
+        p.bmap_order = 1; p.tap_base = 0; p.tap_sy = CFW; p.tap_sx = 1;
+      } else {
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(IC), static_cast<cuuint64_t>(FH) * FW, static_cast<cuuint64_t>(OC)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(IC) * 4, static_cast<cuuint64_t>(FH) * FW * IC * 4};
+        cuuint32_t box[3] = {32, 1, 32};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = g_encode_tiled(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(filt), dims, strides,
+                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+        p.bmap_order = 0;
+        p.tap_base = (y + (CFH - 1) * sh) * FW + x + (CFW - 1) * sw;
+        p.tap_sy = -sh * FW;
+        p.tap_sx = -sw;
+      }
+      p.C = dDX + (static_cast<long long>(u0 * sh + y - ph) * IW + (v0 * sw + x - pw)) * IC;
+      p.Cbuf = nullptr; p.ldc = IC; p.c_stride = 0;
+      p.os_on = 1; p.os_uv = U * V; p.os_v = V;
+      p.os_sn = static_cast<long long>(IH) * IW * IC;
+      p.os_su = static_cast<long long>(sh) * IW * IC;
+      p.os_sv = static_cast<long long>(sw) * IC;
+      p.M = static_cast<int>(GM); p.N = IC;
+      p.conv_icb = (OC + 31) / 32;
+      p.nkb_total = CFH * CFW * p.conv_icb;
+      p.tiles_m = static_cast<int>((GM + 128 * ctas - 1) / (128 * ctas));
+      p.tiles_n = (IC + bn - 1) / bn;
+      p.gz = 1;
+      p.kc = g_kc.load();
+      p.vec4_ok = 1;
+      p.tma_store = 0;
+      p.conv_OW = V; p.conv_OH = U; p.conv_FW = CFW; p.conv_IC = OC;
+      p.conv_sw = 1; p.conv_sh = 1; p.conv_pw = -lower_w; p.conv_ph = -lower_h;
+      p.status = status;
+      e = launch_gemm_kn(tile, true, true, p, 1, st);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+  return static_cast<int>(cudaPeekAtLastError());
 }
 
 }  // namespace dragon
@@ -728,6 +894,64 @@ int cu32_dconv3D_deltaX_W1_SGM(const int64_t* s, int n, const float* dY, const f
   if (GM_slice <= 0) return CU32_E_ARG;
   return deconv_s1_any(s, n, dY, IH, IW, W, 1, 1, dX, IH, IW, N, IC, OC, 0, 0);
 }
+// any stride, forward filter read in place (the reference's scatter-add formulation, A.cu:731-834)
+int cu32_dconv3D_deltaX_crossAdd(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                                 int FW, float* dX, int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph,
+                                 int pw) {
+  return deconv_strided_any(s, n, dY, OH, OW, W, false, FH, FW, dX, IH, IW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_dconv3D_deltaX_crossAdd_SGM(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                                     int FW, float* dX, int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph,
+                                     int pw, int GM_slice) {
+  if (GM_slice <= 0) return CU32_E_ARG;
+  return deconv_strided_any(s, n, dY, OH, OW, W, false, FH, FW, dX, IH, IW, N, IC, OC, sh, sw, ph, pw);
+}
+int cu32_ks_remode(int64_t stream, const float* dW, int FH, int FW, float* dCW, int CFH, int CFW, int OC, int IC,
+                   int sh, int sw) {
+  return ks_remode_any(false, stream, dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
+}
+int cu32_ks_remodev2(int64_t stream, const float* dW, int FH, int FW, float* dCW, int CFH, int CFW, int OC, int IC,
+                     int sh, int sw) {
+  return ks_remode_any(true, stream, dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
+}
+// kernel-split natives: the filter arrives as the ks_remodev2 workspace
+#define DRAGON_DX_KS(name)                                                                                       \
+  int name(const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW, int FH, int FW, float* dX, \
+           int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {                              \
+    return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, sh, sw, ph, pw);        \
+  }
+#define DRAGON_DX_KS_SGM(name)                                                                                   \
+  int name(const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW, int FH, int FW, float* dX, \
+           int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph, int pw, int GM_slice) {                \
+    if (GM_slice <= 0) return CU32_E_ARG;                                                                        \
+    return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, sh, sw, ph, pw);        \
+  }
+#define DRAGON_DX_KS2(name)                                                                                      \
+  int name(const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW, int FH, int FW, float* dX, \
+           int IH, int IW, int N, int IC, int OC, int ph, int pw) {                                              \
+    return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, 2, 2, ph, pw);          \
+  }
+#define DRAGON_DX_KS2_SGM(name)                                                                                  \
+  int name(const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW, int FH, int FW, float* dX, \
+           int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice) {                                \
+    if (GM_slice <= 0) return CU32_E_ARG;                                                                        \
+    return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, 2, 2, ph, pw);          \
+  }
+DRAGON_DX_KS(cu32_dconv3D_deltaX_kernelSplit)
+DRAGON_DX_KS_SGM(cu32_dconv3D_deltaX_kernelSplit_SGM)
+DRAGON_DX_KS(cu32_dconv3D_deltaX_ksImsR)
+DRAGON_DX_KS_SGM(cu32_dconv3D_deltaX_ksImsR_SGM)
+DRAGON_DX_KS(cu32_dconv3D_deltaX_ksImsR_texture)
+DRAGON_DX_KS_SGM(cu32_dconv3D_deltaX_ksImsR_texture_SGM)
+DRAGON_DX_KS2(cu32_dconv3D_deltaX_ksIms2R)
+DRAGON_DX_KS2_SGM(cu32_dconv3D_deltaX_ksIms2R_SGM)
+DRAGON_DX_KS2(cu32_dconv3D_deltaX_ksIms2R_texture)
+DRAGON_DX_KS2_SGM(cu32_dconv3D_deltaX_ksIms2R_texture_SGM)
+int cu32_dconv3D_deltaX_ksV2_Ims2R(int, const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW,
+                                   int FH, int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+  return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, 2, 2, ph, pw);
+}
+
 #define DRAGON_DX_WINOGRAD(name)                                                                                \
   int name(int, const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH, int FW,       \
            float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {                                  \

@@ -73,8 +73,15 @@ struct GemmParams {
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
   // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
   int conv_OW, conv_OH, conv_FW, conv_IC, conv_icb, conv_sw, conv_sh, conv_pw, conv_ph;
-  int conv_taps;        // FH * FW
-  int conv_flip;        // B is one MN-major [IC x OC] matrix per tap (tensor map (oc, tap, ic)), taps applied in reverse
+  // Data-gradient forms (im2col A, MN-major B): the filter is a stack of [K x N] matrices, one per tap.
+  // The tap a k-block needs is tap_base + tap_sy * fh + tap_sx * fw (fh, fw: the tap of the im2col load), which
+  // expresses reversed and strided tap orders over a filter that stays where it is.
+  int tap_base, tap_sy, tap_sx;
+  int bmap_order;       // 0: B map coordinates (n, tap, k) - filter W[k][tap][n];  1: (n, k, tap) - filter CW[tap][k][n]
+  // Strided output rows (data gradient for strides > 1): row -> (image, u, v) -> element offset
+  // image * os_sn + u * os_su + v * os_sv; stores go straight from registers.
+  int os_on, os_uv, os_v;
+  long long os_sn, os_su, os_sv;
 };
 
 #ifdef DRAGON_TRACE
@@ -300,10 +307,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           // im2col coordinates: k-block -> (filter tap, block of 32 channels inside the tap);
           // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
           // rows and images inside the tensor map's traversal box.
-          int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0, btap = 0;
+          int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0;
           if (Cfg::IM2COL) {
             const int tap = (w.kb0 + i) / p.conv_icb;
-            btap = tap;
             ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
             fh = tap / p.conv_FW;
             fw = tap - fh * p.conv_FW;
@@ -330,11 +336,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
             }
             if (Cfg::B_MN && Cfg::IM2COL) {
-              // data gradient: this k-block is 32 input channels of tap (fh, fw); the filter tap
-              // that multiplies it is the mirrored one, FH*FW - 1 - tap
+              // data gradient: this k-block is 32 input channels of tap (fh, fw) of the im2col walk;
+              // the filter matrix that multiplies it sits at a tap index given by the host
+              const int btap = p.tap_base + p.tap_sy * fh + p.tap_sx * fw;
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-                tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, p.conv_taps - 1 - btap, ic0, pol_b);
+                if (p.bmap_order == 0) tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, btap, ic0, pol_b);
+                else                   tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, ic0, btap, pol_b);
             } else if (Cfg::B_MN) {
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
@@ -706,7 +714,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       } else {
         const int row = w.row0 + q * 32 + lane;
         if (row < p.M) {
-          float* dst = w.out + static_cast<long long>(row) * p.ldc + w.col0 + h * CW;
+          long long row_off = static_cast<long long>(row) * p.ldc;
+          if (p.os_on) {
+            const int img = row / p.os_uv, r = row - img * p.os_uv;
+            const int u = r / p.os_v, v = r - u * p.os_v;
+            row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
+          }
+          float* dst = w.out + row_off + w.col0 + h * CW;
           const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
           if (p.vec4_ok) {
 #pragma unroll

@@ -232,6 +232,57 @@ DX_WINOGRAD_SGM(Im2col_1Winograd_1s8_1texture_1SGM, cu32_dconv3D_deltaX_Im2col_W
 DX_WINOGRAD(Im2col_1Winograd_1s16_1texture, cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture)
 DX_WINOGRAD_SGM(Im2col_1Winograd_1s16_1texture_1SGM, cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM)
 
+// ---- Cuda_dconv3D_deltaX for strides > 1 (reference: Cuda_dconv3D_deltaX/A.cu:280-834)
+JNIEXPORT void JNICALL JNAME_DX(ks_1remode)(JNIEnv* env, jclass, jlong stream, jlong dW, jint FH, jint FW, jlong dCW,
+                                            jint CFH, jint CFW, jint OC, jint IC, jint sh, jint sw) {
+  done(env, cu32_ks_remode(stream, cptr(dW), FH, FW, mptr(dCW), CFH, CFW, OC, IC, sh, sw));
+}
+JNIEXPORT void JNICALL JNAME_DX(ks_1remodev2)(JNIEnv* env, jclass, jlong stream, jlong dW, jint FH, jint FW,
+                                              jlong dCW, jint CFH, jint CFW, jint OC, jint IC, jint sh, jint sw) {
+  done(env, cu32_ks_remodev2(stream, cptr(dW), FH, FW, mptr(dCW), CFH, CFW, OC, IC, sh, sw));
+}
+#define DX_HEAD jlongArray streams, jint length, jlong dDY, jint OH, jint OW, jlong dF, jint FH, jint FW, jlong dDX, \
+                jint IH, jint IW, jint N, jint IC, jint OC
+#define DX_PASS s.h, s.n, cptr(dDY), OH, OW, cptr(dF), FH, FW, mptr(dDX), IH, IW, N, IC, OC
+#define DX_KS(jname, cname)                                                                                      \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, DX_HEAD, jint sh, jint sw, jint ph, jint pw) {     \
+    Streams s(env, streams, length);                                                                             \
+    done(env, cname(DX_PASS, sh, sw, ph, pw));                                                                   \
+  }
+#define DX_KS_SGM(jname, cname)                                                                                  \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, DX_HEAD, jint sh, jint sw, jint ph, jint pw,       \
+                                         jint GM_slice) {                                                        \
+    Streams s(env, streams, length);                                                                             \
+    done(env, cname(DX_PASS, sh, sw, ph, pw, GM_slice));                                                         \
+  }
+#define DX_KS2(jname, cname)                                                                                     \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, DX_HEAD, jint ph, jint pw) {                       \
+    Streams s(env, streams, length);                                                                             \
+    done(env, cname(DX_PASS, ph, pw));                                                                           \
+  }
+#define DX_KS2_SGM(jname, cname)                                                                                 \
+  JNIEXPORT void JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, DX_HEAD, jint ph, jint pw, jint GM_slice) {        \
+    Streams s(env, streams, length);                                                                             \
+    done(env, cname(DX_PASS, ph, pw, GM_slice));                                                                 \
+  }
+DX_KS(dconv3D_1deltaX_1kernelSplit, cu32_dconv3D_deltaX_kernelSplit)
+DX_KS_SGM(dconv3D_1deltaX_1kernelSplit_1SGM, cu32_dconv3D_deltaX_kernelSplit_SGM)
+DX_KS(dconv3D_1deltaX_1ksImsR, cu32_dconv3D_deltaX_ksImsR)
+DX_KS_SGM(dconv3D_1deltaX_1ksImsR_1SGM, cu32_dconv3D_deltaX_ksImsR_SGM)
+DX_KS(dconv3D_1deltaX_1ksImsR_1texture, cu32_dconv3D_deltaX_ksImsR_texture)
+DX_KS_SGM(dconv3D_1deltaX_1ksImsR_1texture_1SGM, cu32_dconv3D_deltaX_ksImsR_texture_SGM)
+DX_KS2(dconv3D_1deltaX_1ksIms2R, cu32_dconv3D_deltaX_ksIms2R)
+DX_KS2_SGM(dconv3D_1deltaX_1ksIms2R_1SGM, cu32_dconv3D_deltaX_ksIms2R_SGM)
+DX_KS2(dconv3D_1deltaX_1ksIms2R_1texture, cu32_dconv3D_deltaX_ksIms2R_texture)
+DX_KS2_SGM(dconv3D_1deltaX_1ksIms2R_1texture_1SGM, cu32_dconv3D_deltaX_ksIms2R_texture_SGM)
+DX_KS(dconv3D_1deltaX_1crossAdd, cu32_dconv3D_deltaX_crossAdd)
+DX_KS_SGM(dconv3D_1deltaX_1crossAdd_1SGM, cu32_dconv3D_deltaX_crossAdd_SGM)
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksV2_1Ims2R)(JNIEnv* env, jclass, jboolean useTexture, DX_HEAD,
+                                                              jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_ksV2_Ims2R(useTexture ? 1 : 0, DX_PASS, ph, pw));
+}
+
 // Contraction + bias row in one pass.  These natives do not exist in the reference's Java classes; a
 // maintainer who wants the fusion declares them and calls them from
 // CudaFloat32EngineBase.matMul_biased / conv3D_biased instead of the two-kernel sequence.

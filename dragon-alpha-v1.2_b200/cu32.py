@@ -91,6 +91,21 @@ SIGNATURES = {
     "cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
     "cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
     "cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_ks_remode": [c_int64, _fp, _I, _I, _fp] + [_I] * 6,
+    "cu32_ks_remodev2": [c_int64, _fp, _I, _I, _fp] + [_I] * 6,
+    "cu32_dconv3D_deltaX_kernelSplit": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaX_kernelSplit_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_dconv3D_deltaX_ksImsR": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaX_ksImsR_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_dconv3D_deltaX_ksImsR_texture": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaX_ksImsR_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_dconv3D_deltaX_ksIms2R": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_ksIms2R_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaX_ksIms2R_texture": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_ksIms2R_texture_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaX_ksV2_Ims2R": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
+    "cu32_dconv3D_deltaX_crossAdd": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaX_crossAdd_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 10,
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -468,8 +483,8 @@ class Cuda_conv3D:
 
 class Cuda_dconv3D_deltaX:
     """Mirror of the stride-1 natives of z.dragon.engine.cuda.impl.math.Cuda_dconv3D_deltaX (the data gradient
-    of the forward convolution; reference: Cuda_dconv3D_deltaX/A.cu:21-277, :837-1040).  The natives for
-    strides > 1 (kernelSplit, ksIms*, crossAdd) are not covered."""
+    of the forward convolution; reference: Cuda_dconv3D_deltaX/A.cu:21-277, :837-1040) and, further down, of the
+    natives for strides > 1 (ks_remode*, kernelSplit, ksIms*, crossAdd; A.cu:280-834)."""
 
     @staticmethod
     def _s1(name, lead, streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, *tail):
@@ -545,3 +560,45 @@ class Cuda_dconv3D_deltaX:
         Cuda_dconv3D_deltaX._s1("dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM", (int(bool(useTexture)),), streamArray,
                                 length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, GM_slice)
         return True
+
+    # ---- strides > 1: the kernel-split natives take the ks_remodev2 workspace, crossAdd the filter itself
+    @staticmethod
+    def ks_remode(stream, dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw):
+        _check(load().cu32_ks_remode(int(stream), _p(dW), FH, FW, _p(dCW), CFH, CFW, OC, IC, sh, sw), "ks_remode")
+
+    @staticmethod
+    def ks_remodev2(stream, dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw):
+        _check(load().cu32_ks_remodev2(int(stream), _p(dW), FH, FW, _p(dCW), CFH, CFW, OC, IC, sh, sw), "ks_remodev2")
+
+    @staticmethod
+    def _ks(name, lead, streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC, OC, *tail):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_dconv3D_deltaX_" + name)(*lead, s, n, _p(d_deltaY), OH, OW, _p(dF), FH, FW,
+                                                              _p(d_deltaX), IH, IW, N, IC, OC, *tail), name)
+
+
+def _add_ks_methods():
+    def strided(name):
+        def f(streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw, *gm):
+            Cuda_dconv3D_deltaX._ks(name, (), streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC,
+                                    OC, sh, sw, ph, pw, *gm)
+        return staticmethod(f)
+
+    def stride2(name):
+        def f(streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, *gm):
+            Cuda_dconv3D_deltaX._ks(name, (), streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC,
+                                    OC, ph, pw, *gm)
+        return staticmethod(f)
+    for nm in ("kernelSplit", "kernelSplit_SGM", "ksImsR", "ksImsR_SGM", "ksImsR_texture", "ksImsR_texture_SGM", "crossAdd",
+               "crossAdd_SGM"):
+        setattr(Cuda_dconv3D_deltaX, "dconv3D_deltaX_" + nm, strided(nm))
+    for nm in ("ksIms2R", "ksIms2R_SGM", "ksIms2R_texture", "ksIms2R_texture_SGM"):
+        setattr(Cuda_dconv3D_deltaX, "dconv3D_deltaX_" + nm, stride2(nm))
+
+    def ksv2(useTexture, streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw):
+        Cuda_dconv3D_deltaX._ks("ksV2_Ims2R", (int(bool(useTexture)),), streamArray, length, d_deltaY, OH, OW, dCW, FH, FW,
+                                d_deltaX, IH, IW, N, IC, OC, ph, pw)
+    Cuda_dconv3D_deltaX.dconv3D_deltaX_ksV2_Ims2R = staticmethod(ksv2)
+
+
+_add_ks_methods()

@@ -198,14 +198,22 @@ class Cu32Engine:
             Cuda_conv3D.conv3D_GemmR_SGM(sa, 1, X, IH, IW, W, CW, FH, FW, Y, OH, OW, N, IC, OC, sh, sw, ph, pw, sl)
 
     def conv3D_deltaX(self, deltaX, IH, IW, deltaY, OH, OW, W, FH, FW, N, IC, OC, sh, sw, ph, pw):
-        """Data gradient the way the Java engine runs its stride-1 branch (CudaFloat32EngineBase.java:3773-3820):
-        1x1 filters take the W1 native, everything else the zero-padding s1 native.  Strides > 1 use natives this
-        library does not export."""
-        if sh != 1 or sw != 1:
-            raise NotImplementedError("data gradient for strides > 1: natives of Cuda_dconv3D_deltaX not covered here")
+        """Data gradient the way the Java engine runs it (CudaFloat32EngineBase.java:3773-3900).  Stride 1: 1x1
+        filters take the W1 native, everything else the zero-padding s1 native.  Strides > 1: rearrange the filter
+        into the kernel-split workspace CW[sh][sw][CFH][CFW][OC][IC] with ks_remodev2 on streams[0], then the
+        Ims2R native for stride 2 x 2 and the ImsR native otherwise."""
         from .cu32 import Cuda_dconv3D_deltaX as dx
         sa = self.streams[:1]
-        if FH == 1 and FW == 1 and ph == 0 and pw == 0:
+        if sh != 1 or sw != 1:
+            CFH, CFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+            CW, keep = self.malloc(OC * CFH * CFW * IC * sh * sw)
+            self._keep.append(keep)
+            dx.ks_remodev2(self.streams[0], W, FH, FW, CW, CFH, CFW, OC, IC, sh, sw)
+            if sh == 2 and sw == 2:
+                dx.dconv3D_deltaX_ksIms2R(sa, 1, deltaY, OH, OW, CW, FH, FW, deltaX, IH, IW, N, IC, OC, ph, pw)
+            else:
+                dx.dconv3D_deltaX_ksImsR(sa, 1, deltaY, OH, OW, CW, FH, FW, deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw)
+        elif FH == 1 and FW == 1 and ph == 0 and pw == 0:
             dx.dconv3D_deltaX_W1(sa, 1, deltaY, W, deltaX, IH, IW, N, IC, OC)
         else:
             dx.dconv3D_deltaX_s1(sa, 1, deltaY, OH, OW, W, FH, FW, deltaX, IH, IW, N, IC, OC, ph, pw)

@@ -233,8 +233,7 @@ CU32_API int cu32_conv3D_Im2col_WinogradR_s16_texture_SGM(int useTexture, const 
  *   deltaY[N,OH,OW,OC], W[OC,FH,FW,IC] (the forward filter, unchanged), deltaX[N,IH,IW,IC],
  *   IH = OH - 1 + FH - 2*ph (and likewise for the width); IC % 4 == 0, OC % 4 == 0.
  * It runs as a forward implicit GEMM over deltaY with padding (FH-1-ph, FW-1-pw) and the filter taps
- * reversed, W being read where it lies.  The natives of that project that handle strides > 1
- * (kernelSplit, ksIms*, crossAdd and their remode helpers) are not covered.
+ * reversed, W being read where it lies.  (Strides > 1: next section.)
  *   cu32_dconv3D_deltaX_s1[_texture][_SGM]   replace JNI dconv3D_deltaX_s1 (A.cu:21-42), _s1_SGM (:45-94),
  *                                            _s1_texture (:97-120), _s1_texture_SGM (:123-174)
  *   cu32_dconv3D_deltaX_W1[_SGM]             replace JNI dconv3D_deltaX_W1 (:177-196), _W1_SGM (:199-240): 1x1 filter
@@ -273,6 +272,43 @@ CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture(int useTexture, con
 CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM(int useTexture, const int64_t* streams, int length,
                            const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
                            float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
+
+/* ------------------------------------------------------------------ Cuda_dconv3D_deltaX, any stride
+ * deltaX[n,ih,iw,ic] = sum over (oh,ow,fh,fw,oc) with oh*sh - ph + fh == ih and ow*sw - pw + fw == iw of
+ * deltaY[n,oh,ow,oc] * W[oc,fh,fw,ic];  OH = (IH + 2*ph - FH) / sh + 1 (likewise OW).  Computed as sh*sw stride-1
+ * sub-problems, one per residue of (ih + ph, iw + pw) modulo the stride, each a launch of the contraction kernel
+ * whose output rows are the strided pixels of that residue class.
+ *   cu32_ks_remode / cu32_ks_remodev2   replace JNI ks_remode (A.cu:280-291) and ks_remodev2 (:294-306): the filter
+ *       workspace CW[sh*sw][...] of OC*CFH*CFW*IC floats per phase, CFH = ceil(FH/sh), CFW = ceil(FW/sw), bit for
+ *       bit the reference's layouts (v1: [oc][fhr][fwr][ic], v2: [fhr][fwr][oc][ic], taps reversed)
+ *   cu32_dconv3D_deltaX_kernelSplit[_SGM], _ksImsR[_SGM|_texture|_texture_SGM]   replace JNI (:314-386, :389-540);
+ *       dCW is the ks_remodev2 workspace, which is what the Java engine passes (CudaFloat32EngineBase.java:3824-3900)
+ *   cu32_dconv3D_deltaX_ksIms2R[_SGM|_texture|_texture_SGM], _ksV2_Ims2R   replace JNI (:543-728): stride 2 x 2
+ *   cu32_dconv3D_deltaX_crossAdd[_SGM]   replace JNI (:731-834): takes the forward filter W itself (read in place)
+ * The reference's Ims natives require IH % sh == 0 and IW % sw == 0; these do not. */
+CU32_API int cu32_ks_remode(int64_t stream, const float* dW, int FH, int FW, float* dCW, int CFH, int CFW, int OC,
+                   int IC, int sh, int sw);
+CU32_API int cu32_ks_remodev2(int64_t stream, const float* dW, int FH, int FW, float* dCW, int CFH, int CFW, int OC,
+                     int IC, int sh, int sw);
+#define CU32_DX_KS_ARGS const int64_t* streams, int length, const float* d_deltaY, int OH, int OW, const float* dCW, \
+                        int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC, int OC
+CU32_API int cu32_dconv3D_deltaX_kernelSplit(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_kernelSplit_SGM(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_ksImsR(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_ksImsR_SGM(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_ksImsR_texture(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_ksImsR_texture_SGM(CU32_DX_KS_ARGS, int sh, int sw, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_ksIms2R(CU32_DX_KS_ARGS, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_ksIms2R_SGM(CU32_DX_KS_ARGS, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_ksIms2R_texture(CU32_DX_KS_ARGS, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_ksIms2R_texture_SGM(CU32_DX_KS_ARGS, int ph, int pw, int GM_slice);
+CU32_API int cu32_dconv3D_deltaX_ksV2_Ims2R(int useTexture, CU32_DX_KS_ARGS, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_crossAdd(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC,
+                           int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaX_crossAdd_SGM(const int64_t* streams, int length, const float* d_deltaY, int OH,
+                           int OW, const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N,
+                           int IC, int OC, int sh, int sw, int ph, int pw, int GM_slice);
 
 /* ------------------------------------------------------------------ contraction + bias row
  * No counterpart among the reference's natives.  The Java engine's matMul_biased / conv3D_biased

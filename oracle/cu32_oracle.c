@@ -13,6 +13,9 @@
  *   buf_summary (Kahan)                  Cuda_matMul/Cuda_matMul/SKbufsum.cuh:29-68
  *   filter remode W[OC,FH,FW,IC] -> CW[FH,FW,IC,OC]   Cuda_conv3D/conv3D_kernel_remode_V1.cuh:50-196
  *   deconv3D_deltaX_img2col_s1 (float accumulator)   engine-cuda-base/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/test.cuh:154-196
+ *   deconv3D_deltaX_img2col (any stride)             same file, :109-152
+ *   ks_remode / ks_remodev2 (filter workspace of the strided data gradient; GPU kernels, restated element by
+ *   element)                                         dconv3D_dX_kernelSplit_remode_v1.cuh:28-66, _v2.cuh:31-66
  *   linear_dual2D_row (the bias-row add the engine applies right after matMul / conv3D;
  *   a GPU kernel, restated element by element)        Cuda_function/Cuda_function/type1_linear_dual2D_row.cuh:41-70
  * Loop order and accumulation type follow the reference exactly (k outermost, FP32 "+=" into
@@ -200,6 +203,80 @@ void oracle_deconv3D_deltaX_img2col_s1(const float* deltaY, int OH, int OW, cons
       }
       deltaX[(((size_t)n * IH + ih) * IW + iw) * IC + ic] = v;
     }
+}
+
+/* Any stride, the reference's check loop: deltaY is thought of as dilated by the stride (OH_p rows), the rotated
+ * filter walks it, positions that fall between the dilated pixels are skipped; float accumulator, k = (oc, fh, fw). */
+void oracle_deconv3D_deltaX_img2col(const float* deltaY, int OH, int OW, const float* W, int FH, int FW,
+                                    float* deltaX, int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph,
+                                    int pw) {
+  const int OH_p = OH + (OH - 1) * (sh - 1), OW_p = OW + (OW - 1) * (sw - 1);
+  const int oph = FH - ph - 1, opw = FW - pw - 1;
+  const int GK = OC * FH * FW;
+  for (int ic = 0; ic < IC; ic++)
+    for (int j = 0; j < N * IH * IW; j++) {
+      const int n = j / (IH * IW), jr = j % (IH * IW);
+      const int ih = jr / IW, iw = jr % IW;
+      float v = 0;
+      for (int k = 0; k < GK; k++) {
+        const int oc = k / (FH * FW), kr = k % (FH * FW);
+        const int fh = kr / FW, fw = kr % FW;
+        const int oh = ih - oph + fh, ow = iw - opw + fw;
+        if (oh < 0 || ow < 0 || oh >= OH_p || ow >= OW_p) continue;
+        if (oh % sh != 0 || ow % sw != 0) continue;
+        v += deltaY[(((size_t)n * OH + oh / sh) * OW + ow / sw) * OC + oc] *
+             W[(((size_t)oc * FH + (FH - 1 - fh)) * FW + (FW - 1 - fw)) * IC + ic];
+      }
+      deltaX[(((size_t)n * IH + ih) * IW + iw) * IC + ic] = v;
+    }
+}
+
+/* Any stride with an FP64 accumulator: every deltaY pixel scatters into the input positions it was computed from. */
+void oracle_deconv3D_deltaX_f64(const float* deltaY, int OH, int OW, const float* W, int FH, int FW, double* deltaX,
+                                int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  for (size_t i = 0; i < (size_t)N * IH * IW * IC; i++) deltaX[i] = 0.0;
+  for (int n = 0; n < N; n++)
+    for (int oh = 0; oh < OH; oh++)
+      for (int ow = 0; ow < OW; ow++) {
+        const float* dy = deltaY + (((size_t)n * OH + oh) * OW + ow) * OC;
+        for (int fh = 0; fh < FH; fh++) {
+          const int ih = oh * sh - ph + fh;
+          if (ih < 0 || ih >= IH) continue;
+          for (int fw = 0; fw < FW; fw++) {
+            const int iw = ow * sw - pw + fw;
+            if (iw < 0 || iw >= IW) continue;
+            double* out = deltaX + (((size_t)n * IH + ih) * IW + iw) * IC;
+            for (int oc = 0; oc < OC; oc++) {
+              const float* w = W + (((size_t)oc * FH + fh) * FW + fw) * IC;
+              const double d = dy[oc];
+              for (int ic = 0; ic < IC; ic++) out[ic] += d * (double)w[ic];
+            }
+          }
+        }
+      }
+}
+
+/* Filter workspace of the strided data gradient.  v2 != 0: CW[y][x][fhr][fwr][oc][ic]; v2 == 0: CW[y][x][oc][fhr][fwr][ic];
+ * tap (fhr, fwr) of phase (y, x) is W[oc][y + (CFH_y-1-fhr)*sh][x + (CFW_x-1-fwr)*sw][ic]; each phase starts at a slot
+ * of OC*mCFH*mCFW*IC floats and fills only its own OC*CFH_y*CFW_x*IC; the rest of CW is left as it was. */
+void oracle_ks_remode(int v2, const float* W, int FH, int FW, float* CW, int mCFH, int mCFW, int OC, int IC, int sh,
+                      int sw) {
+  for (int by = 0; by < sh * sw; by++) {
+    float* cw = CW + (size_t)by * OC * mCFH * mCFW * IC;
+    const int y = by / sw, x = by - y * sw;
+    const int CFH = (FH - y + sh - 1) / sh, CFW = (FW - x + sw - 1) / sw;
+    if (CFH <= 0 || CFW <= 0) continue;
+    for (int oc = 0; oc < OC; oc++)
+      for (int fhr = 0; fhr < CFH; fhr++)
+        for (int fwr = 0; fwr < CFW; fwr++)
+          for (int ic = 0; ic < IC; ic++) {
+            const int fh = y + (CFH - 1 - fhr) * sh, fw = x + (CFW - 1 - fwr) * sw;
+            const float w = (fh < FH && fw < FW) ? W[(((size_t)oc * FH + fh) * FW + fw) * IC + ic] : 0.0f;
+            const size_t idx = v2 ? ((((size_t)fhr * CFW + fwr) * OC + oc) * IC + ic)
+                                  : ((((size_t)oc * CFH + fhr) * CFW + fwr) * IC + ic);
+            cw[idx] = w;
+          }
+  }
 }
 
 /* The same gradient with an FP64 accumulator (accuracy oracle). */

@@ -156,6 +156,27 @@ class ref_loops:
         return dX
 
     @staticmethod
+    def deconv3D_deltaX_img2col(deltaY, W, IH, IW, sh, sw, ph, pw):
+        """Any stride: the reference's float-accumulator check loop (Cuda_dconv3D_deltaX/test.cuh:109-152)."""
+        deltaY, W = _c32(deltaY), _c32(W)
+        N, OH, OW, OC = deltaY.shape
+        _, FH, FW, IC = W.shape
+        dX = np.zeros((N, IH, IW, IC), np.float32)
+        lib().oracle_deconv3D_deltaX_img2col(_f(deltaY), OH, OW, _f(W), FH, FW, _f(dX), IH, IW, N, IC, OC, sh, sw, ph, pw)
+        return dX
+
+    @staticmethod
+    def ks_remode(W, sh, sw, v2=True, fill=np.nan):
+        """W [OC, FH, FW, IC] -> the kernel-split workspace as a flat array of sh*sw*OC*mCFH*mCFW*IC floats
+        (dconv3D_dX_kernelSplit_remode_v1.cuh:28-66 / _v2.cuh:31-66); untouched elements keep `fill`."""
+        W = _c32(W)
+        OC, FH, FW, IC = W.shape
+        mCFH, mCFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+        CW = np.full(sh * sw * OC * mCFH * mCFW * IC, fill, np.float32)
+        lib().oracle_ks_remode(1 if v2 else 0, _f(W), FH, FW, _f(CW), mCFH, mCFW, OC, IC, sh, sw)
+        return CW
+
+    @staticmethod
     def linear_dual2D_row(X1, X2, alpha, beta, gamma, width):
         """X1 [height, stride] (stride = padded row length), X2 [stride]: Y = alpha*X1 + beta*X2 + gamma per
         row, columns >= width zeroed (Cuda_function/type1_linear_dual2D_row.cuh:41-70)."""
@@ -257,6 +278,19 @@ def f64_deconv3D_deltaX_s1(deltaY, W, IH, IW, ph, pw):
 
 
 f64.deconv3D_deltaX_s1 = staticmethod(f64_deconv3D_deltaX_s1)
+
+
+def f64_deconv3D_deltaX(deltaY, W, IH, IW, sh, sw, ph, pw):
+    """FP64 data gradient of the convolution for any stride."""
+    deltaY, W = _c32(deltaY), _c32(W)
+    N, OH, OW, OC = deltaY.shape
+    _, FH, FW, IC = W.shape
+    dX = np.zeros((N, IH, IW, IC), np.float64)
+    lib().oracle_deconv3D_deltaX_f64(_f(deltaY), OH, OW, _f(W), FH, FW, _d(dX), IH, IW, N, IC, OC, sh, sw, ph, pw)
+    return dX
+
+
+f64.deconv3D_deltaX = staticmethod(f64_deconv3D_deltaX)
 
 
 def frob_rel(C, C64) -> float:

@@ -249,20 +249,308 @@ def test_conv_layer_forward_and_data_gradient_through_the_engine_mirror(pkg, O, 
         return t.data_ptr(), t
     eng = pkg.engine.Cu32Engine(148, malloc, [G.stream()])
     rng = np.random.default_rng(66)
-    for (N, IH, IW, IC, OC, F, p) in [(4, 14, 14, 32, 64, 3, 1), (4, 10, 10, 16, 24, 1, 0)]:
-        OH, OW = IH + 2 * p - F + 1, IW + 2 * p - F + 1
+    for (N, IH, IW, IC, OC, F, p, st) in [(4, 14, 14, 32, 64, 3, 1, 1), (4, 10, 10, 16, 24, 1, 0, 1),
+                                          (4, 14, 14, 32, 64, 3, 1, 2), (2, 15, 15, 16, 24, 5, 2, 3)]:
+        OH, OW = (IH + 2 * p - F) // st + 1, (IW + 2 * p - F) // st + 1
         X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
         W = (rng.standard_normal((OC, F, F, IC)) * 0.1).astype(np.float32)
         dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
         dX_, dW_, ddY = G.dev(X), G.dev(W), G.dev(dY)
         Y = G.Out(N * OH * OW * OC)
-        eng.conv3D(Y.ptr, OH, OW, dX_.data_ptr(), IH, IW, dW_.data_ptr(), F, F, N, IC, OC, 1, 1, p, p)
+        eng.conv3D(Y.ptr, OH, OW, dX_.data_ptr(), IH, IW, dW_.data_ptr(), F, F, N, IC, OC, st, st, p, p)
         gX = G.Out(N * IH * IW * IC)
-        eng.conv3D_deltaX(gX.ptr, IH, IW, ddY.data_ptr(), OH, OW, dW_.data_ptr(), F, F, N, IC, OC, 1, 1, p, p)
+        eng.conv3D_deltaX(gX.ptr, IH, IW, ddY.data_ptr(), OH, OW, dW_.data_ptr(), F, F, N, IC, OC, st, st, p, p)
         G.check_status(pkg)
-        for name, got, want in (("forward", Y.host((N, OH, OW, OC)), O.f64.conv3D(X, W, OH, OW, 1, 1, p, p)),
-                                ("deltaX", gX.host((N, IH, IW, IC)), O.f64.deconv3D_deltaX_s1(dY, W, IH, IW, p, p))):
+        for name, got, want in (("forward", Y.host((N, OH, OW, OC)), O.f64.conv3D(X, W, OH, OW, st, st, p, p)),
+                                ("deltaX", gX.host((N, IH, IW, IC)), O.f64.deconv3D_deltaX(dY, W, IH, IW, st, st, p, p))):
             rep = O.report(got, want)
-            assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (name, F, rep)
-    with pytest.raises(NotImplementedError):
-        eng.conv3D_deltaX(0, 8, 8, 0, 4, 4, 0, 3, 3, 1, 4, 4, 2, 2, 1, 1)
+            assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (name, F, st, rep)
+
+
+# ================================================================== any stride
+# The reference computes the data gradient of a strided convolution either by scatter-add from the forward
+# filter (crossAdd) or by "kernel split": sh*sw stride-1 sub-problems over a rearranged copy CW of the filter
+# that ks_remodev2 writes.  Oracle: the reference's any-stride CPU check loop (Cuda_dconv3D_deltaX/test.cuh:109-152),
+# an FP64 version of it, and a restatement of the two rearrangement kernels.
+def _sdims(N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw):
+    return (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+
+
+SDX_SMALL = [
+    # N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw
+    (2, 8, 8, 4, 8, 3, 3, 2, 2, 1, 1),
+    (1, 11, 10, 4, 4, 5, 3, 2, 2, 2, 1),
+    (2, 9, 7, 8, 4, 3, 3, 3, 3, 1, 1),
+    (1, 12, 12, 4, 4, 1, 1, 2, 2, 0, 0),      # filter smaller than the stride: most pixels get no tap
+    (2, 10, 13, 4, 8, 4, 4, 2, 1, 1, 2),      # stride in one direction only
+    (1, 10, 10, 4, 4, 3, 3, 4, 4, 1, 1),
+]
+
+
+def test_strided_oracle_known_answer_and_stride_one(O):
+    # 1x1 filter, stride 2: each deltaY pixel lands on the even input pixel, the others stay zero
+    dY = np.arange(1, 5, dtype=np.float32).reshape(1, 2, 2, 1)
+    W = np.full((1, 1, 1, 1), 3.0, np.float32)
+    dX = O.ref_loops.deconv3D_deltaX_img2col(dY, W, 4, 4, 2, 2, 0, 0)
+    want = np.zeros((4, 4), np.float32); want[0::2, 0::2] = 3.0 * dY[0, :, :, 0]
+    assert np.array_equal(dX[0, :, :, 0], want)
+    # with sh = sw = 1 the any-stride loop is the stride-1 loop, bit for bit
+    rng = np.random.default_rng(8)
+    for case in [(2, 6, 5, 4, 8, 3, 3, 1, 1), (1, 7, 7, 8, 4, 5, 3, 2, 0)]:
+        N, IH, IW, IC, OC, FH, FW, ph, pw = case
+        OH, OW = _dims(*case)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = rng.standard_normal((OC, FH, FW, IC)).astype(np.float32)
+        assert np.array_equal(O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, 1, 1, ph, pw),
+                              O.ref_loops.deconv3D_deltaX_img2col_s1(dY, W, IH, IW, ph, pw))
+
+
+@pytest.mark.parametrize("case", SDX_SMALL)
+def test_strided_oracle_is_the_adjoint_of_the_forward_oracle(O, case):
+    """<conv(X, W), dY> == <X, deltaX(dY, W)> for every X: checked in FP64 with the pinned forward oracle."""
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+    OH, OW = _sdims(*case)
+    rng = np.random.default_rng(9)
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    W = rng.standard_normal((OC, FH, FW, IC)).astype(np.float32)
+    Y64 = O.f64.conv3D(X, W, OH, OW, sh, sw, ph, pw)
+    dX64 = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)
+    lhs, rhs = float((Y64 * dY).sum()), float((X.astype(np.float64) * dX64).sum())
+    assert abs(lhs - rhs) <= 1e-10 * max(1.0, abs(lhs))
+    # and column by column: deltaX of a one-hot deltaY is the filter laid at the strided position
+    got32 = O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw)
+    assert O.frob_rel(got32, dX64) <= 2e-6
+
+
+def _cw_phase(CW, W, sh, sw, y, x, v2):
+    """The part of workspace CW that belongs to phase (y, x), as [CFH][CFW][OC][IC] with taps in filter order."""
+    OC, FH, FW, IC = W.shape
+    mCFH, mCFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+    CFH, CFW = (FH - y + sh - 1) // sh, (FW - x + sw - 1) // sw
+    slot = CW[(y * sw + x) * OC * mCFH * mCFW * IC:][:OC * CFH * CFW * IC]
+    if v2:
+        return slot.reshape(CFH, CFW, OC, IC)[::-1, ::-1]
+    return slot.reshape(OC, CFH, CFW, IC).transpose(1, 2, 0, 3)[::-1, ::-1]
+
+
+@pytest.mark.parametrize("geom", [(3, 3, 2, 2), (5, 3, 2, 2), (7, 7, 2, 2), (3, 3, 3, 3), (4, 4, 2, 1), (1, 1, 2, 2),
+                                  (2, 5, 3, 2)])
+@pytest.mark.parametrize("v2", [True, False])
+def test_ks_remode_oracle_holds_each_phase_sub_filter(O, geom, v2):
+    FH, FW, sh, sw = geom
+    OC, IC = 6, 4
+    W = np.random.default_rng(10).standard_normal((OC, FH, FW, IC)).astype(np.float32)
+    CW = O.ref_loops.ks_remode(W, sh, sw, v2=v2)
+    mCFH, mCFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+    touched = 0
+    for y in range(sh):
+        for x in range(sw):
+            if y >= FH or x >= FW:
+                continue
+            sub = W[:, y::sh, x::sw, :].transpose(1, 2, 0, 3)          # [CFH][CFW][OC][IC], filter order
+            assert np.array_equal(_cw_phase(CW, W, sh, sw, y, x, v2), sub), (y, x)
+            touched += sub.size
+    # every filter element appears exactly once; the rest of each slot is untouched
+    assert touched == W.size and np.count_nonzero(~np.isnan(CW)) == W.size
+    assert CW.size == sh * sw * OC * mCFH * mCFW * IC
+
+
+def test_strided_oracle_against_reference_routine_when_built(O):
+    ref = O.ref_native("deltax")
+    if ref is None or not hasattr(ref, "ref_cpu_deconv3D_deltaX_img2col"):
+        pytest.skip("oracle/_ref/libref_deltax.so not built with the any-stride routines (python oracle/build_ref.py --deltax)")
+    rng = np.random.default_rng(11)
+    fp = ctypes.POINTER(ctypes.c_float)
+    for case in SDX_SMALL:
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+        OH, OW = _sdims(*case)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = rng.standard_normal((OC, FH, FW, IC)).astype(np.float32)
+        out = np.zeros((N, IH, IW, IC), np.float32)
+        ref.ref_cpu_deconv3D_deltaX_img2col(dY.ctypes.data_as(fp), OH, OW, W.ctypes.data_as(fp), FH, FW,
+                                            out.ctypes.data_as(fp), IH, IW, N, IC, OC, sh, sw, ph, pw)
+        assert np.array_equal(out, O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw)), case
+
+
+def test_strided_argument_errors_without_gpu(pkg):
+    lib = pkg.cu32.load()
+    s = (ctypes.c_int64 * 1)(0)
+    P = lambda a: ctypes.cast(a, ctypes.POINTER(ctypes.c_float))
+    ok = 0x10000
+    f = lib.cu32_dconv3D_deltaX_crossAdd
+    #           dY  OH OW  W  FH FW  dX  IH IW  N  IC OC sh sw ph pw
+    assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 9, 8, 2, 8, 8, 2, 2, 1, 1) == -2   # OH inconsistent with IH
+    assert f(s, 1, None, 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 2, 2, 1, 1) == -1
+    assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 6, 8, 2, 2, 1, 1) == -4   # IC % 4
+    assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 0, 2, 1, 1) == -2   # stride 0
+    assert f(s, 1, P(ok), 2, 2, P(ok), 3, 3, P(ok), 20, 20, 2, 8, 8, 17, 17, 0, 0) == -5  # stride beyond 16
+    assert lib.cu32_dconv3D_deltaX_crossAdd_SGM(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 2, 2, 1, 1, 0) == -8
+    assert lib.cu32_dconv3D_deltaX_ksIms2R(s, 0, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 1, 1) == -3   # no stream
+    r = lib.cu32_ks_remodev2
+    assert r(0, None, 3, 3, P(ok), 2, 2, 8, 8, 2, 2) == -1
+    assert r(0, P(ok), 3, 3, P(ok), 3, 2, 8, 8, 2, 2) == -2        # CFH must be ceil(FH / sh)
+    assert lib.cu32_ks_remode(0, P(ok), 3, 3, P(ok), 2, 2, 8, 8, 0, 2) == -2
+
+
+# ------------------------------------------------------------------ GPU, any stride
+def _remode_dev(pkg, W, sh, sw, v2=True, fill=float("nan")):
+    """ks_remode / ks_remodev2 through the mirror; returns the device workspace (prefilled with `fill`)."""
+    import gpu_util as G
+    import torch
+    OC, FH, FW, IC = W.shape
+    CFH, CFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+    dW = G.dev(W)
+    dCW = torch.full((sh * sw * OC * CFH * CFW * IC,), fill, device="cuda", dtype=torch.float32)
+    fn = pkg.cu32.Cuda_dconv3D_deltaX.ks_remodev2 if v2 else pkg.cu32.Cuda_dconv3D_deltaX.ks_remode
+    fn(G.stream(), dW.data_ptr(), FH, FW, dCW.data_ptr(), CFH, CFW, OC, IC, sh, sw)
+    torch.cuda.synchronize()
+    return dCW
+
+
+def _run_strided(pkg, entry, dY, W, IH, IW, sh, sw, ph, pw, GM_slice=64):
+    import gpu_util as G
+    dx = pkg.cu32.Cuda_dconv3D_deltaX
+    N, OH, OW, OC = dY.shape
+    _, FH, FW, IC = W.shape
+    ddY = G.dev(dY)
+    filt = G.dev(W) if entry.startswith("crossAdd") else _remode_dev(pkg, W, sh, sw)
+    out = G.Out(N * IH * IW * IC)
+    base = [[G.stream()], 1, ddY.data_ptr(), OH, OW, filt.data_ptr(), FH, FW, out.ptr, IH, IW, N, IC, OC]
+    tail = [ph, pw] if "Ims2R" in entry else [sh, sw, ph, pw]
+    if entry.endswith("SGM"):
+        tail.append(GM_slice)
+    if entry == "ksV2_Ims2R":
+        dx.dconv3D_deltaX_ksV2_Ims2R(True, *base, *tail)
+    else:
+        getattr(dx, "dconv3D_deltaX_" + entry)(*base, *tail)
+    X = out.host((N, IH, IW, IC))
+    G.check_status(pkg)
+    return X
+
+
+SDX_CASES = SDX_SMALL + [
+    (4, 16, 16, 32, 64, 3, 3, 2, 2, 1, 1),
+    (4, 32, 32, 16, 32, 7, 7, 2, 2, 3, 3),        # the 7x7 stride-2 stem of a residual network
+    (4, 8, 8, 256, 64, 2, 2, 2, 2, 0, 0),         # non-overlapping 2x2 (a learned down-sampling)
+    (2, 15, 17, 36, 40, 3, 3, 3, 3, 1, 1),        # ragged channels, extents not multiples of the stride
+    (2, 14, 13, 64, 128, 4, 4, 2, 1, 1, 2),
+    (8, 56, 56, 64, 128, 3, 3, 2, 2, 1, 1),       # a residual network's down-sampling 3x3
+    (2, 9, 9, 132, 260, 3, 3, 2, 2, 1, 1),        # channel tails in both operands
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", SDX_CASES)
+def test_strided_deltax(pkg, O, cuda, case):
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+    OH, OW = _sdims(*case)
+    rng = np.random.default_rng(23)
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+    want = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)
+    got = _run_strided(pkg, "crossAdd", dY, W, IH, IW, sh, sw, ph, pw)
+    assert np.isfinite(got).all()
+    rep = O.report(got, want)
+    assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (case, rep)
+    # pixels that no filter tap reaches are exactly zero
+    assert np.array_equal(got[want == 0], np.zeros_like(got[want == 0]))
+    # the kernel-split native on the rearranged filter gives the same bits
+    ks = _run_strided(pkg, "kernelSplit", dY, W, IH, IW, sh, sw, ph, pw)
+    assert np.array_equal(ks, got)
+    if N * IH * IW * IC * OC * FH * FW <= 4e7:       # the reference's FP32 loop, where it finishes in seconds
+        loop = O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw)
+        assert O.frob_rel(got, loop) <= 2e-6
+
+
+@pytest.mark.gpu
+def test_strided_entry_points_give_the_same_bits(pkg, O, cuda):
+    rng = np.random.default_rng(21)
+    N, IH, IW, IC, OC, FH, FW, ph, pw = 3, 12, 14, 24, 40, 3, 3, 1, 1
+    for (sh, sw, names) in [
+        (2, 2, ["kernelSplit", "kernelSplit_SGM", "ksImsR", "ksImsR_SGM", "ksImsR_texture", "ksImsR_texture_SGM",
+                "ksIms2R", "ksIms2R_SGM", "ksIms2R_texture", "ksIms2R_texture_SGM", "ksV2_Ims2R", "crossAdd_SGM"]),
+        (3, 2, ["kernelSplit", "kernelSplit_SGM", "ksImsR", "ksImsR_SGM", "ksImsR_texture", "ksImsR_texture_SGM",
+                "crossAdd_SGM"]),
+    ]:
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = rng.standard_normal((OC, FH, FW, IC)).astype(np.float32)
+        base = _run_strided(pkg, "crossAdd", dY, W, IH, IW, sh, sw, ph, pw)
+        assert O.frob_rel(base, O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)) <= 1e-6
+        for nm in names:
+            assert np.array_equal(_run_strided(pkg, nm, dY, W, IH, IW, sh, sw, ph, pw), base), (sh, sw, nm)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("geom", [(3, 3, 2, 2), (5, 3, 2, 2), (7, 7, 2, 2), (3, 3, 3, 3), (4, 4, 2, 1), (1, 1, 2, 2),
+                                  (2, 5, 3, 2)])
+def test_ks_remode_kernels_bit_exact(pkg, O, cuda, geom):
+    import gpu_util as G
+    FH, FW, sh, sw = geom
+    OC, IC = 20, 12
+    W = np.random.default_rng(22).standard_normal((OC, FH, FW, IC)).astype(np.float32)
+    ref = O.ref_native("deltax")
+    for v2 in (True, False):
+        got = _remode_dev(pkg, W, sh, sw, v2=v2).cpu().numpy()
+        want = O.ref_loops.ks_remode(W, sh, sw, v2=v2)
+        assert np.array_equal(got, want, equal_nan=True), (geom, v2)
+        if ref is not None and hasattr(ref, "ref_gpu_ks_remodev2") and OC % 4 == 0 and IC % 4 == 0:
+            # the reference's own rearrangement kernels on the same filter
+            dW = G.dev(W)
+            dR = cuda.full((got.size,), float("nan"), device="cuda")
+            fn = ref.ref_gpu_ks_remodev2 if v2 else ref.ref_gpu_ks_remode
+            CFH, CFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+            assert fn(ctypes.c_longlong(G.stream()), ctypes.c_void_p(dW.data_ptr()), FH, FW,
+                      ctypes.c_void_p(dR.data_ptr()), CFH, CFW, OC, IC, sh, sw) == 0
+            cuda.cuda.synchronize()
+            R = dR.cpu().numpy()
+            live = ~np.isnan(want)        # the reference leaves the unused tail of a slot as it found it
+            assert np.array_equal(R[live], got[live]), (geom, v2)
+
+
+@pytest.mark.gpu
+def test_strided_deltax_against_reference_kernels(pkg, O, cuda):
+    """The reference's scatter-add kernels for strides > 1, compiled for this GPU, on the same inputs."""
+    import gpu_util as G
+    torch = cuda
+    ref = O.ref_native("deltax")
+    if ref is None or not hasattr(ref, "ref_gpu_dconv3D_deltaX_crossAdd"):
+        pytest.skip("oracle/_ref/libref_deltax.so not built with the any-stride routines (python oracle/build_ref.py --deltax)")
+    rng = np.random.default_rng(66)
+    for case in [(4, 28, 28, 64, 64, 3, 3, 2, 2, 1, 1), (2, 15, 17, 16, 32, 5, 5, 3, 3, 2, 2)]:
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+        OH, OW = _sdims(*case)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = (rng.standard_normal((OC, FH, FW, IC)) * 0.05).astype(np.float32)
+        ddY, dW = G.dev(dY), G.dev(W)
+        dR = torch.full((N, IH, IW, IC), float("nan"), device="cuda")
+        streams = (ctypes.c_longlong * 10)(*([G.stream()] * 10))
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        assert ref.ref_gpu_dconv3D_deltaX_crossAdd(streams, 10, vp(ddY), OH, OW, vp(dW), FH, FW, vp(dR), IH, IW, N, IC,
+                                                   OC, sh, sw, ph, pw) == 0
+        torch.cuda.synchronize()
+        R = dR.cpu().numpy()
+        got = _run_strided(pkg, "crossAdd", dY, W, IH, IW, sh, sw, ph, pw)
+        want = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)
+        e_ref, e_our = O.frob_rel(R, want), O.frob_rel(got, want)
+        assert e_ref <= 5e-6, (case, e_ref)
+        assert e_our <= 1e-6 and O.frob_rel(got, R) <= 5e-6, (case, e_our, e_ref)
+
+
+@pytest.mark.gpu
+def test_strided_deltax_is_the_gradient_of_the_forward_entry_point(pkg, O, cuda):
+    """<conv3D(X, W), dY> == <X, deltaX(dY, W)> with both sides computed by this library."""
+    import gpu_util as G
+    rng = np.random.default_rng(67)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = 4, 17, 16, 32, 48, 3, 3, 2, 2, 1, 1
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    Y = G.conv(pkg, "conv3D_GemmR", X, W, sh, sw, ph, pw)
+    dX = _run_strided(pkg, "kernelSplit", dY, W, IH, IW, sh, sw, ph, pw)
+    lhs = float((Y.astype(np.float64) * dY).sum())
+    rhs = float((X.astype(np.float64) * dX).sum())
+    scale = float(np.sqrt((Y.astype(np.float64) ** 2).sum() * (dY.astype(np.float64) ** 2).sum()))
+    assert abs(lhs - rhs) <= 2e-6 * scale, (lhs, rhs, scale)

@@ -160,3 +160,43 @@ def test_fuzz_deltax(pkg, O, cuda):
         _acc(O, out.host((N, IH, IW, IC)), O.f64.deconv3D_deltaX_s1(dY, W, IH, IW, ph, pw),
              f"deltaX {(N, IH, IW, IC, OC, FH, FW, ph, pw)}")
     G.check_status(pkg)
+
+
+def test_fuzz_deltax_strided(pkg, O, cuda):
+    """Random geometries with strides up to 4 through the scatter-add-named and the kernel-split natives (which
+    must agree bit for bit), each against the FP64 oracle.  Includes extents the stride does not divide, filters
+    smaller than the stride and paddings up to the filter size."""
+    dx = pkg.cu32.Cuda_dconv3D_deltaX
+    rng = np.random.default_rng(89)
+    s = [G.stream()]
+    done = 0
+    for case in range(60):
+        N = int(rng.integers(1, 5))
+        FH, FW = int(rng.integers(1, 8)), int(rng.integers(1, 8))
+        sh, sw = int(rng.integers(1, 5)), int(rng.integers(1, 5))
+        ph, pw = int(rng.integers(0, FH)), int(rng.integers(0, FW))
+        IH = int(rng.integers(max(1, FH - 2 * ph), 24 + FH))
+        IW = int(rng.integers(max(1, FW - 2 * pw), 24 + FW))
+        if sh == 1 and sw == 1:
+            sh = 2
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        IC, OC = int(rng.integers(1, 40)) * 4, int(rng.integers(1, 40)) * 4
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+        ddY, dW = G.dev(dY), G.dev(W)
+        geo = (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw)
+        out = G.Out(N * IH * IW * IC)
+        dx.dconv3D_deltaX_crossAdd(s, 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), FH, FW, out.ptr, IH, IW, N, IC, OC,
+                                   sh, sw, ph, pw)
+        got = out.host((N, IH, IW, IC))
+        _acc(O, got, O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw), f"strided deltaX {geo}")
+        CFH, CFW = (FH + sh - 1) // sh, (FW + sw - 1) // sw
+        dCW = torch.full((sh * sw * OC * CFH * CFW * IC,), float("nan"), device="cuda")
+        dx.ks_remodev2(s[0], dW.data_ptr(), FH, FW, dCW.data_ptr(), CFH, CFW, OC, IC, sh, sw)
+        out2 = G.Out(N * IH * IW * IC)
+        dx.dconv3D_deltaX_ksImsR(s, 1, ddY.data_ptr(), OH, OW, dCW.data_ptr(), FH, FW, out2.ptr, IH, IW, N, IC, OC,
+                                 sh, sw, ph, pw)
+        assert np.array_equal(out2.host((N, IH, IW, IC)), got), f"kernel split vs in-place filter {geo}"
+        done += 1
+    assert done == 60
+    G.check_status(pkg)

@@ -110,7 +110,7 @@ def _header_symbols():
 def test_library_exports_every_declared_symbol(pkg):
     lib = pkg.cu32.load()
     names = _header_symbols()
-    assert len(names) >= 54
+    assert len(names) >= 69
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/dragon_cu32.h but not exported"
     # the ctypes table covers the same surface
@@ -142,6 +142,13 @@ def test_jni_symbols_exported(pkg):
                "dconv3D_1deltaX_dconv3D_1deltaX_1V2_1s1", "dconv3D_1deltaX_Im2col_1Winograd_1s8_1texture",
                "dconv3D_1deltaX_Im2col_1Winograd_1s8_1texture_1SGM", "dconv3D_1deltaX_Im2col_1Winograd_1s16_1texture",
                "dconv3D_1deltaX_Im2col_1Winograd_1s16_1texture_1SGM"}
+    want_dx |= {"dconv3D_1deltaX_" + n for n in (
+        "ks_1remode", "ks_1remodev2", "dconv3D_1deltaX_1kernelSplit", "dconv3D_1deltaX_1kernelSplit_1SGM",
+        "dconv3D_1deltaX_1ksImsR", "dconv3D_1deltaX_1ksImsR_1SGM", "dconv3D_1deltaX_1ksImsR_1texture",
+        "dconv3D_1deltaX_1ksImsR_1texture_1SGM", "dconv3D_1deltaX_1ksIms2R", "dconv3D_1deltaX_1ksIms2R_1SGM",
+        "dconv3D_1deltaX_1ksIms2R_1texture", "dconv3D_1deltaX_1ksIms2R_1texture_1SGM", "dconv3D_1deltaX_1ksV2_1Ims2R",
+        "dconv3D_1deltaX_1crossAdd", "dconv3D_1deltaX_1crossAdd_1SGM")}   # all 26 natives of the Java class
+    assert len(want_dx) == 26
     missing = (want_matmul | want_bmm | want_conv | want_fused | want_dx) - syms
     assert not missing, missing
 
