@@ -20,7 +20,7 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
-Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx,
+Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2,
 c3_qk, c3_pv, c4, c5.
 """
 from __future__ import annotations
@@ -304,6 +304,33 @@ class Workload:
             self.bytes = w.algorithmic_bytes
             self.desc = f"dconv3D_deltaX_s1 N={d['N']} {d['OH']}x{d['OW']}x{d['OC']} -> {d['IC']}, 3x3 s1 p1"
             self.images = d["N"]
+        elif name == "dx_s2":
+            # data gradient of a residual network's down-sampling convolution, as the engine runs it for strides > 1:
+            # ks_remodev2 (filter -> kernel-split workspace) + the Ims2R native.  Synthetic, seeded.
+            N_, IH, IC, OC, F, sd, pd = images, 56, 128, 256, 3, 2, 1
+            OH = (IH + 2 * pd - F) // sd + 1
+            g = torch.Generator().manual_seed(4005)
+            dYh = torch.randn((N_, OH, OH, OC), generator=g)
+            Wh = torch.randn((OC, F, F, IC), generator=g) * 0.03
+            self.hosts = [dYh.pin_memory(), Wh.pin_memory()]
+            self.dev_in = [h.cuda() for h in self.hosts]
+            self.out = torch.empty((N_, IH, IH, IC), device="cuda")
+            CF = (F + sd - 1) // sd
+            self.cw = torch.zeros(sd * sd * OC * CF * CF * IC, device="cuda")
+            ddY, dW, dDX = self.dev_in[0], self.dev_in[1], self.out
+            dx = pkg.cu32.Cuda_dconv3D_deltaX
+            self.kernels_per_step = 1 + sd * sd
+
+            def launch():
+                s = st()
+                dx.ks_remodev2(s[0], dW.data_ptr(), F, F, self.cw.data_ptr(), CF, CF, OC, IC, sd, sd)
+                dx.dconv3D_deltaX_ksIms2R(s, 1, ddY.data_ptr(), OH, OH, self.cw.data_ptr(), F, F, dDX.data_ptr(), IH, IH,
+                                          N_, IC, OC, pd, pd)
+            self.launch = launch
+            self.flops = 2.0 * N_ * OH * OH * OC * F * F * IC
+            self.bytes = 4.0 * (dYh.numel() + Wh.numel() + self.out.numel())
+            self.desc = f"ks_remodev2 + dconv3D_deltaX_ksIms2R N={N_} {OH}x{OH}x{OC} -> {IH}x{IH}x{IC}, 3x3 s2 p1"
+            self.images = N_
         else:
             raise SystemExit(f"unknown workload {name}")
 

@@ -57,6 +57,14 @@ DELTAX_CASES = {
     "dx_1x1": (4, 6, 6, 16, 20, 1, 1, 0, 0),
     "dx_2x4_p1p3": (2, 7, 9, 12, 4, 2, 4, 1, 3),
 }
+DELTAX_STRIDED_CASES = {
+    # any-stride data gradient: N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw
+    "dxs_3x3_s2_p1": (3, 9, 8, 8, 12, 3, 3, 2, 2, 1, 1),
+    "dxs_5x3_s2_p2p1": (2, 11, 10, 4, 8, 5, 3, 2, 2, 2, 1),
+    "dxs_3x3_s3_p1": (2, 10, 11, 8, 4, 3, 3, 3, 3, 1, 1),
+    "dxs_1x1_s2": (2, 8, 8, 8, 8, 1, 1, 2, 2, 0, 0),
+    "dxs_4x4_s2s1_p1p2": (2, 10, 13, 4, 8, 4, 4, 2, 1, 1, 2),
+}
 
 
 def golden_inputs(name: str, shapes):
@@ -147,6 +155,18 @@ def make_deltax(O):
         out[name] = dX
     np.savez_compressed(HERE / "golden_deltax.npz", **out)
     print("wrote golden_deltax.npz:", len(out), "cases")
+    if not hasattr(dx, "ref_cpu_deconv3D_deltaX_img2col"):
+        print("libref_deltax.so lacks the any-stride routine: rebuild it (python oracle/build_ref.py --deltax --force)")
+        return
+    out = {}
+    for name, (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw) in DELTAX_STRIDED_CASES.items():
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        dY, W = golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        dX = np.zeros((N, IH, IW, IC), np.float32)
+        dx.ref_cpu_deconv3D_deltaX_img2col(_p(dY), OH, OW, _p(W), FH, FW, _p(dX), IH, IW, N, IC, OC, sh, sw, ph, pw)
+        out[name] = dX
+    np.savez_compressed(HERE / "golden_deltax_strided.npz", **out)
+    print("wrote golden_deltax_strided.npz:", len(out), "cases")
 
 
 if __name__ == "__main__":

@@ -554,3 +554,27 @@ def test_strided_deltax_is_the_gradient_of_the_forward_entry_point(pkg, O, cuda)
     rhs = float((X.astype(np.float64) * dX).sum())
     scale = float(np.sqrt((Y.astype(np.float64) ** 2).sum() * (dY.astype(np.float64) ** 2).sum()))
     assert abs(lhs - rhs) <= 2e-6 * scale, (lhs, rhs, scale)
+
+
+def test_strided_oracle_against_golden_fixture(O, golden):
+    """tests/golden/golden_deltax_strided.npz: outputs of the reference's own any-stride check loop on seeded inputs."""
+    data = np.load(golden.HERE / "golden_deltax_strided.npz")
+    assert set(data.files) == set(golden.DELTAX_STRIDED_CASES)
+    for name, case in golden.DELTAX_STRIDED_CASES.items():
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+        OH, OW = _sdims(*case)
+        dY, W = golden.golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        assert np.array_equal(O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw), data[name]), name
+
+
+@pytest.mark.gpu
+def test_strided_deltax_against_golden_fixture(pkg, O, cuda, golden):
+    data = np.load(golden.HERE / "golden_deltax_strided.npz")
+    for name, case in golden.DELTAX_STRIDED_CASES.items():
+        N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = case
+        OH, OW = _sdims(*case)
+        dY, W = golden.golden_inputs(name, [(N, OH, OW, OC), (OC, FH, FW, IC)])
+        for entry in ("crossAdd", "ksImsR"):
+            got = _run_strided(pkg, entry, dY, W, IH, IW, sh, sw, ph, pw)
+            assert O.frob_rel(got, data[name]) <= 2e-6, (name, entry)   # the golden output carries FP32 accumulation error
+            assert O.same_percent(got, data[name], 1e-5) >= 0.999, (name, entry)

@@ -182,3 +182,51 @@ def test_jni_deltax_on_gpu(pkg, O, cuda):
     f(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out.ptr, IH + 1, IW, N, IC, OC, p, p)
     assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
     G.check_status(pkg)
+
+
+@pytest.mark.gpu
+def test_jni_strided_deltax_on_gpu(pkg, O, cuda):
+    """The engine's sequence for strides > 1 under the JNI names: ks_remodev2, then a kernel-split native."""
+    import gpu_util as G
+    import torch
+    lib = pkg.cu32.load()
+    jni = FakeJNI([G.stream()])
+    rng = np.random.default_rng(10)
+    N, IH, IW, IC, OC, F, p, st = 2, 13, 12, 8, 12, 3, 1, 2
+    OH, OW = (IH + 2 * p - F) // st + 1, (IW + 2 * p - F) // st + 1
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    W = rng.standard_normal((OC, F, F, IC)).astype(np.float32) * 0.1
+    ddY, dW = G.dev(dY), G.dev(W)
+    want = O.f64.deconv3D_deltaX(dY, W, IH, IW, st, st, p, p)
+    CF = (F + st - 1) // st
+    dCW = torch.zeros(st * st * OC * CF * CF * IC, device="cuda")
+    pre = "Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaX_"
+    r = getattr(lib, pre + "ks_1remodev2")
+    r.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int64] + [c_int32] * 6
+    r.restype = None
+    r(jni.env, None, G.stream(), dW.data_ptr(), F, F, dCW.data_ptr(), CF, CF, OC, IC, st, st)
+    assert jni.thrown is None
+    head = [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int32, c_int64, c_int32, c_int32, c_int64]
+    results = []
+    for name, lead, tail in (("dconv3D_1deltaX_1kernelSplit", [], [st, st, p, p]),
+                             ("dconv3D_1deltaX_1ksIms2R_1texture", [], [p, p]),
+                             ("dconv3D_1deltaX_1ksImsR_1SGM", [], [st, st, p, p, 64]),
+                             ("dconv3D_1deltaX_1ksV2_1Ims2R", [1], [p, p])):
+        f = getattr(lib, pre + name)
+        f.argtypes = head[:2] + [ctypes.c_uint8] * len(lead) + head[2:] + [c_int32] * (5 + len(tail))
+        f.restype = None
+        out = G.Out(N * IH * IW * IC)
+        f(jni.env, None, *lead, ARRAY_HANDLE, 1, ddY.data_ptr(), OH, OW, dCW.data_ptr(), F, F, out.ptr, IH, IW, N, IC,
+          OC, *tail)
+        assert jni.thrown is None, name
+        results.append(out.host((N, IH, IW, IC)).copy())
+        assert O.report(results[-1], want)["frob"] <= 1e-6, name
+        assert np.array_equal(results[-1], results[0]), name
+    # scatter-add name, forward filter as it lies
+    c = getattr(lib, pre + "dconv3D_1deltaX_1crossAdd")
+    c.argtypes = head + [c_int32] * 9
+    c.restype = None
+    out = G.Out(N * IH * IW * IC)
+    c(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), F, F, out.ptr, IH, IW, N, IC, OC, st, st, p, p)
+    assert jni.thrown is None and np.array_equal(out.host((N, IH, IW, IC)), results[0])
+    G.check_status(pkg)
