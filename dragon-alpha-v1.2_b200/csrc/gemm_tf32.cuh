@@ -711,15 +711,45 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             }
           }
         }
+      } else if (p.os_on) {
+        // Rows are strided pixels (one phase of a strided data gradient), which no tiled tensor map can
+        // describe.  Same staging tile as above, but the warp itself carries each 32x32 piece out: a
+        // lane stages its own row, then eight lanes together write one row's 128 bytes, four rows per
+        // instruction - whole 128-byte segments instead of 32 scattered 16-byte stores.
+        const uint32_t stg = tiles_base + STAGES * Cfg::STAGE_BYTES + (warp - Cfg::DRAIN_WARP0) * 4096;
+        const int row = w.row0 + q * 32 + lane;
+        long long row_off = -1;   // rows >= M have no pixel
+        if (row < p.M) {
+          const int img = row / p.os_uv, r = row - img * p.os_uv;
+          const int u = r / p.os_v, v = r - u * p.os_v;
+          row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
+        }
+        const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll
+        for (int g = 0; g < CW / 32; ++g) {
+          const int c0 = w.col0 + h * CW + g * 32;
+          if (c0 < p.N && w.row0 + q * 32 < p.M) {   // warp-uniform
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              sts128(stg + lane * 128 + ((c ^ (lane & 7)) * 16),
+                     with_bias(g * 32 + c * 4, make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1],
+                                                           acc[g * 32 + c * 4 + 2], acc[g * 32 + c * 4 + 3])));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + sub;
+              const long long off = __shfl_sync(0xffffffffu, row_off, r);
+              const float4 v = lds128(stg + r * 128 + ((chunk ^ (r & 7)) * 16));
+              if (off >= 0 && c0 + chunk * 4 < p.N)   // p.N is a multiple of 4 here: a vector is whole or absent
+                *reinterpret_cast<float4*>(w.out + off + c0 + chunk * 4) = v;
+            }
+            __syncwarp();   // the piece has been read before the next one overwrites it
+          }
+        }
       } else {
         const int row = w.row0 + q * 32 + lane;
         if (row < p.M) {
-          long long row_off = static_cast<long long>(row) * p.ldc;
-          if (p.os_on) {
-            const int img = row / p.os_uv, r = row - img * p.os_uv;
-            const int u = r / p.os_v, v = r - u * p.os_v;
-            row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
-          }
+          const long long row_off = static_cast<long long>(row) * p.ldc;
           float* dst = w.out + row_off + w.col0 + h * CW;
           const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
           if (p.vec4_ok) {
