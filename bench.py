@@ -20,7 +20,7 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
-Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2,
+Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2, c4_dw,
 c3_qk, c3_pv, c4, c5.
 """
 from __future__ import annotations
@@ -331,6 +331,35 @@ class Workload:
             self.bytes = 4.0 * (dYh.numel() + Wh.numel() + self.out.numel())
             self.desc = f"ks_remodev2 + dconv3D_deltaX_ksIms2R N={N_} {OH}x{OH}x{OC} -> {IH}x{IH}x{IC}, 3x3 s2 p1"
             self.images = N_
+        elif name == "c4_dw":
+            # weight gradient of config 4: deltaW[256,3,3,256] from X and deltaY, split over the pixel axis
+            w = W.config4(N=images)
+            d = w.dims
+            g = torch.Generator().manual_seed(4006)
+            dYh = torch.randn((d["N"], d["OH"], d["OW"], d["OC"]), generator=g)
+            self.hosts = [w.X.pin_memory(), dYh.pin_memory()]
+            self.dev_in = [h.cuda() for h in self.hosts]
+            size = d["OC"] * d["FH"] * d["FW"] * d["IC"]
+            self.out = torch.empty((d["OC"], d["FH"], d["FW"], d["IC"]), device="cuda")
+            gz = int(os.environ.get("DRAGON_BENCH_DW_GRIDZ", "16"))
+            self.cbuf = torch.empty(max(gz - 1, 1) * size, device="cuda")
+            dX, ddY, dDW = self.dev_in[0], self.dev_in[1], self.out
+            dwc = pkg.cu32.Cuda_dconv3D_deltaW
+            self.kernels_per_step = 2 if gz > 1 else 1
+
+            def launch():
+                s = st()
+                dwc.dconv3D_deltaW_GemmSK(s, 1, gz, dX.data_ptr(), d["IH"], d["IW"], ddY.data_ptr(), d["OH"], d["OW"],
+                                          dDW.data_ptr(), self.cbuf.data_ptr(), d["FH"], d["FW"], d["N"], d["IC"], d["OC"],
+                                          w.sh, w.sw, w.ph, w.pw)
+                if gz > 1:
+                    dwc.buf_summary(s[0], self.cbuf.data_ptr(), dDW.data_ptr(), gz - 1, size)
+            self.launch = launch
+            self.flops = w.flops
+            self.bytes = 4.0 * (w.X.numel() + dYh.numel() + size)
+            self.desc = (f"dconv3D_deltaW_GemmSK GridZ={gz} + buf_summary N={d['N']} {d['IH']}x{d['IW']}x{d['IC']}, "
+                         f"deltaY {d['OC']} channels, 3x3 s1 p1")
+            self.images = d["N"]
         else:
             raise SystemExit(f"unknown workload {name}")
 

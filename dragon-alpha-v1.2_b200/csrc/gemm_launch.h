@@ -43,6 +43,8 @@ cudaError_t launch_gemm_kk(int tile_cfg, bool x3, bool im2col, const GemmParams&
 cudaError_t launch_gemm_kn(int tile_cfg, bool x3, bool im2col, const GemmParams& p, int grid_z,
                            cudaStream_t stream);
 cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
+//   NN + im2col : A[K][M], B = im2col walk over an NHWC image, K = output pixels (weight gradient; FP32-accurate only)
+cudaError_t launch_gemm_nn_im2col(int tile_cfg, const GemmParams& p, int grid_z, cudaStream_t stream);
 
 // Shared-memory bytes one stage of the given configuration uses (for reporting).
 int gemm_stage_bytes(int tile_cfg, bool x3);

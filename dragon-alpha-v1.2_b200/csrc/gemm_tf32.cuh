@@ -80,6 +80,7 @@ struct GemmParams {
   int bmap_order;       // 0: B map coordinates (n, tap, k) - filter W[k][tap][n];  1: (n, k, tap) - filter CW[tap][k][n]
   // Strided output rows (data gradient for strides > 1): row -> (image, u, v) -> element offset
   // image * os_sn + u * os_su + v * os_sv; stores go straight from registers.
+  int ztaps;            // > 0: weight gradient, the z index is slice * ztaps + filter tap
   int os_on, os_uv, os_v;
   long long os_sn, os_su, os_sv;
 };
@@ -134,7 +135,12 @@ struct GemmCfg {
   static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN");
   static_assert(TMEM_NEED <= 512, "TMEM");
   static_assert(STAGES >= 2, "stages");
-  static_assert(!(IM2COL && A_MN), "im2col A is K-major");
+  // IM2COL with a K-major A: the A tile is an im2col walk over the image (convolution, data gradient).
+  // IM2COL with an MN-major A: the B tile is the walk and the reduction runs over output pixels
+  // (weight gradient: deltaW = deltaY^T * im2col(X), one filter tap per z index).
+  static constexpr bool IM2COL_A = IM2COL && !A_MN;
+  static constexpr bool IM2COL_B = IM2COL && A_MN;
+  static_assert(!IM2COL_B || B_MN, "an im2col B tile is MN-major (channels contiguous)");
   static_assert(!TS || X3, "TS is only built for the FP32-accurate mode");
 };
 
@@ -161,6 +167,7 @@ struct TileWork {
   int nkb;     // number of k-blocks (0 for a split-K slice that got none)
   float* out;  // output base for this batch / slice
   int zc;      // batch / slice coordinate in the output tensor map
+  int tap;     // weight gradient: filter tap this tile belongs to
   bool to_cbuf;  // this tile's output goes to the split-K partial buffers
 };
 
@@ -214,7 +221,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     w.row0 = (tm * CTAS + static_cast<int>(rank)) * Cfg::BM;
     w.col0 = tn * BN;
     w.bcol0 = w.col0 + static_cast<int>(rank) * Cfg::BN_CTA;
-    if (p.gz > 1) {
+    w.tap = 0;
+    if (p.ztaps > 0) {
+      // weight gradient: z = slice * taps + tap; a tap owns p.N (= IC) columns of each output row
+      const int slice = z / p.ztaps;
+      w.tap = z - slice * p.ztaps;
+      w.kb0 = static_cast<int>((static_cast<long long>(slice) * p.nkb_total) / p.gz);
+      w.nkb = static_cast<int>((static_cast<long long>(slice + 1) * p.nkb_total) / p.gz) - w.kb0;
+      w.batch = 0;
+      w.out = ((slice == 0) ? p.C : p.Cbuf + static_cast<long long>(slice - 1) * p.c_stride) +
+              static_cast<long long>(w.tap) * p.N;
+      w.to_cbuf = slice > 0;
+      w.zc = slice > 0 ? slice - 1 : 0;
+    } else if (p.gz > 1) {
       w.kb0 = static_cast<int>((static_cast<long long>(z) * p.nkb_total) / p.gz);
       w.nkb = static_cast<int>((static_cast<long long>(z + 1) * p.nkb_total) / p.gz) - w.kb0;
       w.batch = 0;
@@ -308,7 +327,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
           // rows and images inside the tensor map's traversal box.
           int ic0 = 0, fh = 0, fw = 0, n = 0, oh = 0, ow = 0;
-          if (Cfg::IM2COL) {
+          if (Cfg::IM2COL_A) {
             const int tap = (w.kb0 + i) / p.conv_icb;
             ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
             fh = tap / p.conv_FW;
@@ -320,11 +339,22 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             oh = r / p.conv_OW;
             ow = r - oh * p.conv_OW;
           }
+          if (Cfg::IM2COL_B) {
+            // the k-block is a run of 32 output pixels starting at pixel k0 = (n, oh, ow); runs wrap over
+            // rows and images inside the tensor map's traversal box and read zeros past the last image
+            fh = w.tap / p.conv_FW;
+            fw = w.tap - fh * p.conv_FW;
+            const int ohw = p.conv_OH * p.conv_OW;
+            n = k0 / ohw;
+            const int r = k0 - n * ohw;
+            oh = r / p.conv_OW;
+            ow = r - oh * p.conv_OW;
+          }
           // one single-thread region for all copies of the k-block
           if (elect_one()) {
             TRACE(0, it);
             mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
-            if (Cfg::IM2COL) {
+            if (Cfg::IM2COL_A) {
               tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
                                  oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
                                  static_cast<uint16_t>(fh), pol_a);
@@ -335,7 +365,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             } else {
               tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
             }
-            if (Cfg::B_MN && Cfg::IM2COL) {
+            if (Cfg::IM2COL_B) {
+              // 32 pixels x 32 channels of tap (fh, fw) per slab; slabs that would start past the last
+              // channel re-read the last block instead (their output columns are never stored)
+              const int cmax = ((p.N - 1) >> 5) << 5;
+#pragma unroll
+              for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
+                tma_load_im2col_4d(b_dst + j * 4096, &p.tmB, full, min(w.bcol0 + 32 * j, cmax),
+                                   ow * p.conv_sw - p.conv_pw, oh * p.conv_sh - p.conv_ph, n,
+                                   static_cast<uint16_t>(fw), static_cast<uint16_t>(fh), pol_b);
+            } else if (Cfg::B_MN && Cfg::IM2COL) {
               // data gradient: this k-block is 32 input channels of tap (fh, fw) of the im2col walk;
               // the filter matrix that multiplies it sits at a tap index given by the host
               const int btap = p.tap_base + p.tap_sy * fh + p.tap_sx * fw;

@@ -283,6 +283,69 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksV2_1Ims2R)(JNIEnv* env, jclas
   done(env, cu32_dconv3D_deltaX_ksV2_Ims2R(useTexture ? 1 : 0, DX_PASS, ph, pw));
 }
 
+// ---- Cuda_dconv3D_deltaW (Java declarations: Cuda_dconv3D_deltaW.java:288-640)
+#define JNAME_DW(method) Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_##method
+JNIEXPORT void JNICALL JNAME_DW(dconv3D_1deltaW)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dX, jint IH,
+                                                 jint IW, jlong dDY, jint OH, jint OW, jlong dDW, jint FH, jint FW,
+                                                 jint N, jint IC, jint OC, jint sh, jint sw, jint ph, jint pw) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaW(s.h, s.n, cptr(dX), IH, IW, cptr(dDY), OH, OW, mptr(dDW), FH, FW, N, IC, OC, sh, sw, ph, pw));
+}
+JNIEXPORT void JNICALL JNAME_DW(dconv3D_1deltaW_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dX,
+                                                     jint IH, jint IW, jlong dDY, jlong dDW, jint N, jint IC, jint OC) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaW_W1(s.h, s.n, cptr(dX), IH, IW, cptr(dDY), mptr(dDW), N, IC, OC));
+}
+JNIEXPORT void JNICALL JNAME_DW(buf_1summary)(JNIEnv* env, jclass, jlong stream, jlong dBuf, jlong dDW, jint part,
+                                              jint sizeW) {
+  done(env, cu32_dconv3D_deltaW_buf_summary(stream, cptr(dBuf), mptr(dDW), part, sizeW));
+}
+#define DW_SK(jname, cname)                                                                                       \
+  JNIEXPORT void JNICALL JNAME_DW(jname)(JNIEnv* env, jclass, jlongArray streams, jint length, jint GridZ, jlong dX, \
+                                         jint IH, jint IW, jlong dDY, jint OH, jint OW, jlong dDW, jlong dBuf,      \
+                                         jint FH, jint FW, jint N, jint IC, jint OC, jint sh, jint sw, jint ph,     \
+                                         jint pw) {                                                                 \
+    Streams s(env, streams, length);                                                                                \
+    done(env, cname(s.h, s.n, GridZ, cptr(dX), IH, IW, cptr(dDY), OH, OW, mptr(dDW), mptr(dBuf), FH, FW, N, IC, OC, \
+                    sh, sw, ph, pw));                                                                               \
+  }
+DW_SK(dconv3D_1deltaW_1GemmSK, cu32_dconv3D_deltaW_GemmSK)
+DW_SK(dconv3D_1deltaW_1GemmV2SK, cu32_dconv3D_deltaW_GemmV2SK)
+JNIEXPORT void JNICALL JNAME_DW(dconv3D_1deltaW_1GemmSK_1W1)(JNIEnv* env, jclass, jlongArray streams, jint length,
+                                                             jint GridZ, jlong dX, jint IH, jint IW, jlong dDY,
+                                                             jlong dDW, jlong dBuf, jint N, jint IC, jint OC) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaW_GemmSK_W1(s.h, s.n, GridZ, cptr(dX), IH, IW, cptr(dDY), mptr(dDW), mptr(dBuf), N, IC, OC));
+}
+#define DW_TAIL jlong dX, jint IH, jint IW, jlong dDY, jint OH, jint OW, jlong dDW, jlong dBuf, jint FH, jint FW, jint N, \
+                jint IC, jint OC, jint ph, jint pw, jint n
+#define DW_TAIL_PASS cptr(dX), IH, IW, cptr(dDY), OH, OW, mptr(dDW), mptr(dBuf), FH, FW, N, IC, OC, ph, pw, n
+JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s4_1texture)(JNIEnv* env, jclass, jlongArray streams,
+                                                                          jint length, jint GridZ, jint OH_slice,
+                                                                          jint OW_slice, DW_TAIL) {
+  Streams s(env, streams, length);
+  const int rc = cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s4_texture(s.h, s.n, GridZ, OH_slice, OW_slice, DW_TAIL_PASS);
+  done(env, rc);
+  return rc == 0 ? 1 : 0;
+}
+JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s8_1texture)(JNIEnv* env, jclass, jlongArray streams,
+                                                                          jint length, jint GridZ, jint OH_slice,
+                                                                          jint OW_slice, DW_TAIL) {
+  Streams s(env, streams, length);
+  const int rc = cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s8_texture(s.h, s.n, GridZ, OH_slice, OW_slice, DW_TAIL_PASS);
+  done(env, rc);
+  return rc == 0 ? 1 : 0;
+}
+JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s16_1texture)(JNIEnv* env, jclass, jlongArray streams,
+                                                                           jint length, jint GridZ, jint OH_slice,
+                                                                           jint OW_slice, jint c64, DW_TAIL) {
+  Streams s(env, streams, length);
+  const int rc =
+      cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture(s.h, s.n, GridZ, OH_slice, OW_slice, c64, DW_TAIL_PASS);
+  done(env, rc);
+  return rc == 0 ? 1 : 0;
+}
+
 // Contraction + bias row in one pass.  These natives do not exist in the reference's Java classes; a
 // maintainer who wants the fusion declares them and calls them from
 // CudaFloat32EngineBase.matMul_biased / conv3D_biased instead of the two-kernel sequence.

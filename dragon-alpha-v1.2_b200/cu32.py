@@ -106,6 +106,15 @@ SIGNATURES = {
     "cu32_dconv3D_deltaX_ksV2_Ims2R": [_I, _sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7,
     "cu32_dconv3D_deltaX_crossAdd": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
     "cu32_dconv3D_deltaX_crossAdd_SGM": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 10,
+    "cu32_dconv3D_deltaW": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaW_W1": [_sp, _I, _fp, _I, _I, _fp, _fp, _I, _I, _I],
+    "cu32_dconv3D_deltaW_buf_summary": [c_int64, _fp, _fp, _I, _I],
+    "cu32_dconv3D_deltaW_GemmSK": [_sp, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaW_GemmV2SK": [_sp, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 9,
+    "cu32_dconv3D_deltaW_GemmSK_W1": [_sp, _I, _I, _fp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
+    "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s4_texture": [_sp, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s8_texture": [_sp, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
+    "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture": [_sp, _I, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -602,3 +611,64 @@ def _add_ks_methods():
 
 
 _add_ks_methods()
+
+
+class Cuda_dconv3D_deltaW:
+    """Mirror of z.dragon.engine.cuda.impl.math.Cuda_dconv3D_deltaW (Cuda_dconv3D_deltaW.java:288-640): the weight
+    gradient of the convolution, deltaW[OC, FH, FW, IC] from X[N, IH, IW, IC] and deltaY[N, OH, OW, OC]."""
+
+    @staticmethod
+    def dconv3D_deltaW(streamArray, length, dX, IH, IW, d_deltaY, OH, OW, d_deltaW, FH, FW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaW(s, n, _p(dX), IH, IW, _p(d_deltaY), OH, OW, _p(d_deltaW), FH, FW, N, IC, OC,
+                                          sh, sw, ph, pw), "dconv3D_deltaW")
+
+    @staticmethod
+    def dconv3D_deltaW_W1(streamArray, length, dX, IH, IW, d_deltaY, d_deltaW, N, IC, OC):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaW_W1(s, n, _p(dX), IH, IW, _p(d_deltaY), _p(d_deltaW), N, IC, OC), "dconv3D_deltaW_W1")
+
+    @staticmethod
+    def buf_summary(stream, d_deltaW_buf, d_deltaW, part, sizeW):
+        _check(load().cu32_dconv3D_deltaW_buf_summary(int(stream), _p(d_deltaW_buf), _p(d_deltaW), part, sizeW), "buf_summary")
+
+    @staticmethod
+    def _sk(name, streamArray, length, GridZ, dX, IH, IW, d_deltaY, OH, OW, d_deltaW, d_buf, FH, FW, N, IC, OC, sh, sw, ph, pw):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_dconv3D_deltaW_" + name)(s, n, GridZ, _p(dX), IH, IW, _p(d_deltaY), OH, OW, _p(d_deltaW),
+                                                              _p(d_buf), FH, FW, N, IC, OC, sh, sw, ph, pw), name)
+
+    @staticmethod
+    def dconv3D_deltaW_GemmSK(*a):
+        Cuda_dconv3D_deltaW._sk("GemmSK", *a)
+
+    @staticmethod
+    def dconv3D_deltaW_GemmV2SK(*a):
+        Cuda_dconv3D_deltaW._sk("GemmV2SK", *a)
+
+    @staticmethod
+    def dconv3D_deltaW_GemmSK_W1(streamArray, length, GridZ, dX, IH, IW, d_deltaY, d_deltaW, d_buf, N, IC, OC):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaW_GemmSK_W1(s, n, GridZ, _p(dX), IH, IW, _p(d_deltaY), _p(d_deltaW), _p(d_buf),
+                                                    N, IC, OC), "dconv3D_deltaW_GemmSK_W1")
+
+    @staticmethod
+    def _wino(name, lead, streamArray, length, GridZ, OH_slice, OW_slice, dX, IH, IW, d_deltaY, OH, OW, d_deltaW, d_buf,
+              FH, FW, N, IC, OC, ph, pw, n_):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_" + name)(
+            s, n, GridZ, OH_slice, OW_slice, *lead, _p(dX), IH, IW, _p(d_deltaY), OH, OW, _p(d_deltaW), _p(d_buf), FH, FW,
+            N, IC, OC, ph, pw, n_), name)
+        return True
+
+    @staticmethod
+    def Im2col_WinogradV2_SHW_s4_texture(streamArray, length, GridZ, OH_slice, OW_slice, *a):
+        return Cuda_dconv3D_deltaW._wino("s4_texture", (), streamArray, length, GridZ, OH_slice, OW_slice, *a)
+
+    @staticmethod
+    def Im2col_WinogradV2_SHW_s8_texture(streamArray, length, GridZ, OH_slice, OW_slice, *a):
+        return Cuda_dconv3D_deltaW._wino("s8_texture", (), streamArray, length, GridZ, OH_slice, OW_slice, *a)
+
+    @staticmethod
+    def Im2col_WinogradV2_SHW_s16_texture(streamArray, length, GridZ, OH_slice, OW_slice, c64, *a):
+        return Cuda_dconv3D_deltaW._wino("s16_texture", (c64,), streamArray, length, GridZ, OH_slice, OW_slice, *a)

@@ -218,6 +218,35 @@ class Cu32Engine:
         else:
             dx.dconv3D_deltaX_s1(sa, 1, deltaY, OH, OW, W, FH, FW, deltaX, IH, IW, N, IC, OC, ph, pw)
 
+    def conv3D_deltaW(self, deltaW, FH, FW, X, IH, IW, deltaY, OH, OW, N, IC, OC, sh, sw, ph, pw, GridZ=None):
+        """Weight gradient the way the Java engine runs its split-K branch (CudaFloat32EngineBase.java:3541-3640):
+        partial buffers for GridZ - 1 slices from the pool, the GemmSK native (W1 form for 1x1 filters), then
+        buf_summary on streams[0].  GridZ: the caller's, else enough slices of the pixel axis to give every SM a
+        tile (the Java rule, :3166-3187, counts thread blocks of the reference's own kernels and is not mirrored)."""
+        from .cu32 import Cuda_dconv3D_deltaW as dw
+        sa = self.streams[:1]
+        if GridZ is None:
+            tiles = ((OC + 255) // 256) * ((IC + 255) // 256) * FH * FW
+            GK = N * OH * OW
+            GridZ = max(1, min(self.sm_count // max(tiles, 1), GK // 512, 64))
+        size = OC * FH * FW * IC
+        buf = 0
+        if GridZ > 1:
+            buf, keep = self.malloc((GridZ - 1) * size)
+            self._keep.append(keep)
+        if FH == 1 and FW == 1 and sh == 1 and sw == 1 and ph == 0 and pw == 0:
+            if GridZ > 1:
+                dw.dconv3D_deltaW_GemmSK_W1(sa, 1, GridZ, X, IH, IW, deltaY, deltaW, buf, N, IC, OC)
+            else:
+                dw.dconv3D_deltaW_W1(sa, 1, X, IH, IW, deltaY, deltaW, N, IC, OC)
+        elif GridZ > 1:
+            dw.dconv3D_deltaW_GemmSK(sa, 1, GridZ, X, IH, IW, deltaY, OH, OW, deltaW, buf, FH, FW, N, IC, OC, sh, sw, ph, pw)
+        else:
+            dw.dconv3D_deltaW(sa, 1, X, IH, IW, deltaY, OH, OW, deltaW, FH, FW, N, IC, OC, sh, sw, ph, pw)
+        if GridZ > 1:
+            dw.buf_summary(self.streams[0], buf, deltaW, GridZ - 1, size)
+        return GridZ
+
     def release(self):
         """Drop the workspaces (the Java Syncer frees them after the streams complete)."""
         self._keep.clear()

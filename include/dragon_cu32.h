@@ -273,6 +273,43 @@ CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM(int useTexture,
                            const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
                            float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
 
+/* ------------------------------------------------------------------ Cuda_dconv3D_deltaW
+ * deltaW[oc,fh,fw,ic] = sum over (n,oh,ow) of deltaY[n,oh,ow,oc] * X[n, oh*sh-ph+fh, ow*sw-pw+fw, ic] (zero outside
+ * the image); X [N,IH,IW,IC], deltaY [N,OH,OW,OC], deltaW [OC,FH,FW,IC], IC and OC multiples of 4.  These replace the
+ * natives of the Java class z/dragon/engine/cuda/impl/math/Cuda_dconv3D_deltaW.java (:288 dconv3D_deltaW, :342 _W1,
+ * :352 buf_summary, :404 _GemmSK, :473 _GemmV2SK, :518 _GemmSK_W1, :557/:595/:634 Im2col_WinogradV2_SHW_s4/s8/s16);
+ * the reference's CUDA source for them is not published, so argument order and the split-K protocol follow the Java
+ * declarations and their caller (CudaFloat32EngineBase.java:3520-3640): slice 0 of the reduction over pixels goes to
+ * deltaW, slice s = 1..GridZ-1 to d_deltaW_buf + (s-1)*OC*FH*FW*IC, and buf_summary adds the partials into deltaW.
+ * The Winograd natives return through the JNI layer as "handled"; OH_slice, OW_slice, c64 and n are ignored. */
+CU32_API int cu32_dconv3D_deltaW(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                           const float* d_deltaY, int OH, int OW, float* d_deltaW, int FH, int FW, int N, int IC,
+                           int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaW_W1(const int64_t* streams, int length, const float* dX, int IH, int IW,
+                           const float* d_deltaY, float* d_deltaW, int N, int IC, int OC);
+CU32_API int cu32_dconv3D_deltaW_buf_summary(int64_t stream, const float* d_deltaW_buf, float* d_deltaW, int part,
+                           int sizeW);
+CU32_API int cu32_dconv3D_deltaW_GemmSK(const int64_t* streams, int length, int GridZ, const float* dX, int IH, int IW,
+                           const float* d_deltaY, int OH, int OW, float* d_deltaW, float* d_deltaW_buf, int FH, int FW,
+                           int N, int IC, int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaW_GemmV2SK(const int64_t* streams, int length, int GridZ, const float* dX, int IH,
+                           int IW, const float* d_deltaY, int OH, int OW, float* d_deltaW, float* d_deltaW_buf, int FH,
+                           int FW, int N, int IC, int OC, int sh, int sw, int ph, int pw);
+CU32_API int cu32_dconv3D_deltaW_GemmSK_W1(const int64_t* streams, int length, int GridZ, const float* dX, int IH,
+                           int IW, const float* d_deltaY, float* d_deltaW, float* d_deltaW_buf, int N, int IC, int OC);
+CU32_API int cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s4_texture(const int64_t* streams, int length, int GridZ,
+                           int OH_slice, int OW_slice, const float* dX, int IH, int IW, const float* d_deltaY, int OH,
+                           int OW, float* d_deltaW, float* d_deltaW_buf, int FH, int FW, int N, int IC, int OC, int ph,
+                           int pw, int n);
+CU32_API int cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s8_texture(const int64_t* streams, int length, int GridZ,
+                           int OH_slice, int OW_slice, const float* dX, int IH, int IW, const float* d_deltaY, int OH,
+                           int OW, float* d_deltaW, float* d_deltaW_buf, int FH, int FW, int N, int IC, int OC, int ph,
+                           int pw, int n);
+CU32_API int cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture(const int64_t* streams, int length, int GridZ,
+                           int OH_slice, int OW_slice, int c64, const float* dX, int IH, int IW, const float* d_deltaY,
+                           int OH, int OW, float* d_deltaW, float* d_deltaW_buf, int FH, int FW, int N, int IC, int OC,
+                           int ph, int pw, int n);
+
 /* ------------------------------------------------------------------ Cuda_dconv3D_deltaX, any stride
  * deltaX[n,ih,iw,ic] = sum over (oh,ow,fh,fw,oc) with oh*sh - ph + fh == ih and ow*sw - pw + fw == iw of
  * deltaY[n,oh,ow,oc] * W[oc,fh,fw,ic];  OH = (IH + 2*ph - FH) / sh + 1 (likewise OW).  Computed as sh*sw stride-1

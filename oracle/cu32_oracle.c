@@ -369,3 +369,59 @@ void oracle_conv3D_f64(const float* X, int IH, int IW, const float* W, int FH, i
           Y[(((size_t)n * OH + oh) * OW + ow) * OC + oc] = v;
         }
 }
+
+/* ------------------------------------------------------------------ weight gradient of the convolution
+ * The reference's CUDA source for Cuda_dconv3D_deltaW is not published; its Java test
+ * (test/cuda/conv3D/Cuda_conv3D_dW_test.java:64-98) checks the natives against Tense.deconv3d_deltaW_naive
+ * (ZUTIL-STD-1.2/src/z/util/math/vector/Tense.java:1276-1318), which swaps the N and IC axes of X, spreads deltaY
+ * over a zero-dilated OHp x OWp grid and calls Tense.conv3D_naive (:same file; FP32 products summed in a double,
+ * loops over grid rows, grid columns, then images).  Restated here without the temporaries: the dilated grid's zero
+ * entries add 0.0 to the sum, so only the live positions are visited, in the same order. */
+void oracle_deconv3D_deltaW_naive(const float* X, int IH, int IW, const float* deltaY, int OH, int OW, float* deltaW,
+                                  int FH, int FW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  for (int ic = 0; ic < IC; ic++)
+    for (int oc = 0; oc < OC; oc++)
+      for (int fh = 0; fh < FH; fh++)
+        for (int fw = 0; fw < FW; fw++) {
+          double v = 0;
+          for (int oh = 0; oh < OH; oh++) {
+            const int ih = fh - ph + oh * sh;
+            if (ih < 0 || ih >= IH) continue;
+            for (int ow = 0; ow < OW; ow++) {
+              const int iw = fw - pw + ow * sw;
+              if (iw < 0 || iw >= IW) continue;
+              for (int n = 0; n < N; n++) {
+                const float prod = X[(((size_t)n * IH + ih) * IW + iw) * IC + ic] *
+                                   deltaY[(((size_t)n * OH + oh) * OW + ow) * OC + oc];
+                v += prod;
+              }
+            }
+          }
+          deltaW[(((size_t)oc * FH + fh) * FW + fw) * IC + ic] = (float)v;
+        }
+}
+
+/* FP64 throughout (exact products of FP32 inputs, double accumulator). */
+void oracle_deconv3D_deltaW_f64(const float* X, int IH, int IW, const float* deltaY, int OH, int OW, double* deltaW,
+                                int FH, int FW, int N, int IC, int OC, int sh, int sw, int ph, int pw) {
+  for (size_t i = 0; i < (size_t)OC * FH * FW * IC; i++) deltaW[i] = 0.0;
+  for (int n = 0; n < N; n++)
+    for (int oh = 0; oh < OH; oh++)
+      for (int ow = 0; ow < OW; ow++) {
+        const float* dy = deltaY + (((size_t)n * OH + oh) * OW + ow) * OC;
+        for (int fh = 0; fh < FH; fh++) {
+          const int ih = oh * sh - ph + fh;
+          if (ih < 0 || ih >= IH) continue;
+          for (int fw = 0; fw < FW; fw++) {
+            const int iw = ow * sw - pw + fw;
+            if (iw < 0 || iw >= IW) continue;
+            const float* x = X + (((size_t)n * IH + ih) * IW + iw) * IC;
+            for (int oc = 0; oc < OC; oc++) {
+              double* out = deltaW + (((size_t)oc * FH + fh) * FW + fw) * IC;
+              const double d = dy[oc];
+              for (int ic = 0; ic < IC; ic++) out[ic] += d * (double)x[ic];
+            }
+          }
+        }
+      }
+}

@@ -166,6 +166,17 @@ class ref_loops:
         return dX
 
     @staticmethod
+    def deconv3D_deltaW_naive(X, deltaY, FH, FW, sh, sw, ph, pw):
+        """X [N, IH, IW, IC], deltaY [N, OH, OW, OC] -> deltaW [OC, FH, FW, IC]: the Java check loop the reference's
+        own weight-gradient test uses (ZUTIL-STD-1.2 Tense.java:1276-1318: float products, double accumulator)."""
+        X, deltaY = _c32(X), _c32(deltaY)
+        N, IH, IW, IC = X.shape
+        _, OH, OW, OC = deltaY.shape
+        dW = np.zeros((OC, FH, FW, IC), np.float32)
+        lib().oracle_deconv3D_deltaW_naive(_f(X), IH, IW, _f(deltaY), OH, OW, _f(dW), FH, FW, N, IC, OC, sh, sw, ph, pw)
+        return dW
+
+    @staticmethod
     def ks_remode(W, sh, sw, v2=True, fill=np.nan):
         """W [OC, FH, FW, IC] -> the kernel-split workspace as a flat array of sh*sw*OC*mCFH*mCFW*IC floats
         (dconv3D_dX_kernelSplit_remode_v1.cuh:28-66 / _v2.cuh:31-66); untouched elements keep `fill`."""
@@ -330,3 +341,16 @@ def ref_native(name: str):
     if hasattr(l, "ref_cpu_samePercent"):
         l.ref_cpu_samePercent.restype = c_float
     return l
+
+
+def f64_deconv3D_deltaW(X, deltaY, FH, FW, sh, sw, ph, pw):
+    """Weight gradient in FP64: deltaW [OC, FH, FW, IC] (float64)."""
+    X, deltaY = _c32(X), _c32(deltaY)
+    N, IH, IW, IC = X.shape
+    _, OH, OW, OC = deltaY.shape
+    dW = np.zeros((OC, FH, FW, IC), np.float64)
+    lib().oracle_deconv3D_deltaW_f64(_f(X), IH, IW, _f(deltaY), OH, OW, _d(dW), FH, FW, N, IC, OC, sh, sw, ph, pw)
+    return dW
+
+
+f64.deconv3D_deltaW = staticmethod(f64_deconv3D_deltaW)

@@ -110,7 +110,7 @@ def _header_symbols():
 def test_library_exports_every_declared_symbol(pkg):
     lib = pkg.cu32.load()
     names = _header_symbols()
-    assert len(names) >= 69
+    assert len(names) >= 78
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/dragon_cu32.h but not exported"
     # the ctypes table covers the same surface
@@ -149,6 +149,11 @@ def test_jni_symbols_exported(pkg):
         "dconv3D_1deltaX_1ksIms2R_1texture", "dconv3D_1deltaX_1ksIms2R_1texture_1SGM", "dconv3D_1deltaX_1ksV2_1Ims2R",
         "dconv3D_1deltaX_1crossAdd", "dconv3D_1deltaX_1crossAdd_1SGM")}   # all 26 natives of the Java class
     assert len(want_dx) == 26
+    want_dw = {"dconv3D_1deltaW_" + n for n in (
+        "dconv3D_1deltaW", "dconv3D_1deltaW_1W1", "buf_1summary", "dconv3D_1deltaW_1GemmSK", "dconv3D_1deltaW_1GemmV2SK",
+        "dconv3D_1deltaW_1GemmSK_1W1", "Im2col_1WinogradV2_1SHW_1s4_1texture", "Im2col_1WinogradV2_1SHW_1s8_1texture",
+        "Im2col_1WinogradV2_1SHW_1s16_1texture")}   # all 9 natives of the Java class
+    want_dx |= want_dw
     missing = (want_matmul | want_bmm | want_conv | want_fused | want_dx) - syms
     assert not missing, missing
 
