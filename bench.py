@@ -341,7 +341,7 @@ class Workload:
             self.dev_in = [h.cuda() for h in self.hosts]
             size = d["OC"] * d["FH"] * d["FW"] * d["IC"]
             self.out = torch.empty((d["OC"], d["FH"], d["FW"], d["IC"]), device="cuda")
-            gz = int(os.environ.get("DRAGON_BENCH_DW_GRIDZ", "16"))
+            gz = int(os.environ.get("DRAGON_BENCH_DW_GRIDZ", "8"))
             self.cbuf = torch.empty(max(gz - 1, 1) * size, device="cuda")
             dX, ddY, dDW = self.dev_in[0], self.dev_in[1], self.out
             dwc = pkg.cu32.Cuda_dconv3D_deltaW
