@@ -200,3 +200,34 @@ def test_fuzz_deltax_strided(pkg, O, cuda):
         done += 1
     assert done == 60
     G.check_status(pkg)
+
+
+def test_fuzz_deltaw(pkg, O, cuda):
+    """Random geometries (strides up to 3, any padding below the filter size, channel tails, pixel counts that are
+    not multiples of the 32-pixel k-block, more split-K slices than k-blocks) through the weight-gradient natives."""
+    dw = pkg.cu32.Cuda_dconv3D_deltaW
+    rng = np.random.default_rng(90)
+    s = [G.stream()]
+    for case in range(40):
+        N = int(rng.integers(1, 6))
+        FH, FW = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        sh, sw = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        ph, pw = int(rng.integers(0, FH)), int(rng.integers(0, FW))
+        IH = int(rng.integers(max(1, FH - 2 * ph), 18 + FH))
+        IW = int(rng.integers(max(1, FW - 2 * pw), 18 + FW))
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        IC, OC = int(rng.integers(1, 40)) * 4, int(rng.integers(1, 40)) * 4
+        GZ = int(rng.choice([1, 2, 3, 7, 16]))
+        X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        dX_, ddY = G.dev(X), G.dev(dY)
+        size = OC * FH * FW * IC
+        out = G.Out(size)
+        buf = torch.full((max(GZ - 1, 1) * size,), float("nan"), device="cuda")
+        dw.dconv3D_deltaW_GemmSK(s, 1, GZ, dX_.data_ptr(), IH, IW, ddY.data_ptr(), OH, OW, out.ptr, buf.data_ptr(), FH, FW,
+                                 N, IC, OC, sh, sw, ph, pw)
+        if GZ > 1:
+            dw.buf_summary(s[0], buf.data_ptr(), out.ptr, GZ - 1, size)
+        _acc(O, out.host((OC, FH, FW, IC)), O.f64.deconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw),
+             f"deltaW {(N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, GZ)}")
+    G.check_status(pkg)

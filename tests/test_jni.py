@@ -230,3 +230,49 @@ def test_jni_strided_deltax_on_gpu(pkg, O, cuda):
     c(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), F, F, out.ptr, IH, IW, N, IC, OC, st, st, p, p)
     assert jni.thrown is None and np.array_equal(out.host((N, IH, IW, IC)), results[0])
     G.check_status(pkg)
+
+
+@pytest.mark.gpu
+def test_jni_deltaw_on_gpu(pkg, O, cuda):
+    """The engine's split-K sequence for the weight gradient under the JNI names of class Cuda_dconv3D_deltaW."""
+    import gpu_util as G
+    import torch
+    lib = pkg.cu32.load()
+    jni = FakeJNI([G.stream()])
+    rng = np.random.default_rng(11)
+    N, IH, IW, IC, OC, F, p, GZ = 3, 9, 8, 8, 12, 3, 1, 3
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    dY = rng.standard_normal((N, IH, IW, OC)).astype(np.float32)
+    dX_, ddY = G.dev(X), G.dev(dY)
+    want = O.f64.deconv3D_deltaW(X, dY, F, F, 1, 1, p, p)
+    size = OC * F * F * IC
+    buf = torch.full(((GZ - 1) * size,), float("nan"), device="cuda")
+    pre = "Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_"
+    f = getattr(lib, pre + "dconv3D_1deltaW_1GemmSK")
+    f.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_int32, c_int64, c_int32, c_int32,
+                  c_int64, c_int64] + [c_int32] * 9
+    f.restype = None
+    sm = getattr(lib, pre + "buf_1summary")
+    sm.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_int32]
+    sm.restype = None
+    out = G.Out(size)
+    f(jni.env, None, ARRAY_HANDLE, 1, GZ, dX_.data_ptr(), IH, IW, ddY.data_ptr(), IH, IW, out.ptr, buf.data_ptr(), F, F,
+      N, IC, OC, 1, 1, p, p)
+    sm(jni.env, None, G.stream(), buf.data_ptr(), out.ptr, GZ - 1, size)
+    assert jni.thrown is None
+    base = out.host((OC, F, F, IC)).copy()
+    assert O.report(base, want)["frob"] <= 1e-6
+    w = getattr(lib, pre + "Im2col_1WinogradV2_1SHW_1s8_1texture")
+    w.argtypes = [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int64, c_int32, c_int32, c_int64,
+                  c_int32, c_int32, c_int64, c_int64] + [c_int32] * 8
+    w.restype = ctypes.c_uint8
+    out2 = G.Out(size)
+    assert w(jni.env, None, ARRAY_HANDLE, 1, GZ, IH, IW, dX_.data_ptr(), IH, IW, ddY.data_ptr(), IH, IW, out2.ptr,
+             buf.data_ptr(), F, F, N, IC, OC, p, p, 6) == 1
+    sm(jni.env, None, G.stream(), buf.data_ptr(), out2.ptr, GZ - 1, size)
+    assert np.array_equal(out2.host((OC, F, F, IC)), base)
+    # inconsistent geometry becomes a CudaException(-2)
+    f(jni.env, None, ARRAY_HANDLE, 1, GZ, dX_.data_ptr(), IH, IW, ddY.data_ptr(), IH + 1, IW, out.ptr, buf.data_ptr(), F, F,
+      N, IC, OC, 1, 1, p, p)
+    assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
+    G.check_status(pkg)
