@@ -106,6 +106,30 @@ def conv_out_dim(I: int, F: int, s: int, p: int) -> int:
     return (I + 2 * p - F) // s + 1
 
 
+CONV3D_DW_SK = SplitKConfig(512, 16, 1.5, 4.0)
+
+
+def conv3D_deltaW_gridZ(OH: int, OW: int, IH: int, IW: int, FH: int, FW: int, N: int, IC: int, OC: int, sm_count: int,
+                        cfg: SplitKConfig = CONV3D_DW_SK) -> int:
+    """GridZ of the convolution's weight gradient (CudaFloat32EngineBase.java:3519-3522 threshold, :3166-3187 rule):
+    no split below `threshold` output pixels or when the [OC x FH*FW*IC] output alone gives every SM enough thread
+    blocks; else the ratio of the forward and data-gradient block counts to the weight gradient's, capped by 256
+    pixels per slice, by maxBlock_perSM and by maxPart, and rounded up to a multiple of 4."""
+    GK = N * OH * OW
+    if GK < cfg.threshold:
+        return 1
+    expect = cfg.minBlock_perSM * (GK / (GK + 1024.0))
+    b2 = Cuda_matMul.blockNum(OC, FH * FW * IC)         # Cuda_dconv3D_deltaW.GEMM_nblock
+    if b2 >= sm_count * expect:
+        return 1
+    b0 = Cuda_matMul.blockNum(OC, N * OH * OW)          # Cuda_conv3D.GEMM_nblock
+    b1 = Cuda_matMul.blockNum(IC, N * IH * IW)          # Cuda_dconv3D_deltaX.GEMM_nblock
+    GZ = (b0 + b1) // (b2 << 1)
+    GZ = min(GZ, GK >> 8, int(sm_count * cfg.maxBlock_perSM / b2))
+    GZ = 2 if GZ < 2 else (GZ + 3) >> 2 << 2
+    return min(GZ, cfg.maxPart)
+
+
 class Cu32Engine:
     """The hot-path methods of CudaFloat32EngineBase on raw device addresses.
 
@@ -221,14 +245,11 @@ class Cu32Engine:
     def conv3D_deltaW(self, deltaW, FH, FW, X, IH, IW, deltaY, OH, OW, N, IC, OC, sh, sw, ph, pw, GridZ=None):
         """Weight gradient the way the Java engine runs its split-K branch (CudaFloat32EngineBase.java:3541-3640):
         partial buffers for GridZ - 1 slices from the pool, the GemmSK native (W1 form for 1x1 filters), then
-        buf_summary on streams[0].  GridZ: the caller's, else enough slices of the pixel axis to give every SM a
-        tile (the Java rule, :3166-3187, counts thread blocks of the reference's own kernels and is not mirrored)."""
+        buf_summary on streams[0].  GridZ: the caller's, else the Java engine's own rule (conv3D_deltaW_gridZ)."""
         from .cu32 import Cuda_dconv3D_deltaW as dw
         sa = self.streams[:1]
         if GridZ is None:
-            tiles = ((OC + 255) // 256) * ((IC + 255) // 256) * FH * FW
-            GK = N * OH * OW
-            GridZ = max(1, min(self.sm_count // max(tiles, 1), GK // 512, 64))
+            GridZ = conv3D_deltaW_gridZ(OH, OW, IH, IW, FH, FW, N, IC, OC, self.sm_count)
         size = OC * FH * FW * IC
         buf = 0
         if GridZ > 1:

@@ -205,3 +205,17 @@ def test_missing_library_fails_loudly(pkg, tmp_path, monkeypatch):
 def test_status_decoding(pkg):
     assert pkg.cu32.decode_status(0) == "ok"
     assert "drainer" in pkg.cu32.decode_status((5 << 24) | (1 << 16) | 7)
+
+
+def test_conv3D_deltaW_gridZ_rule(pkg):
+    """The Java engine's split decision for the weight gradient, on hand-computed cases."""
+    gz = pkg.engine.conv3D_deltaW_gridZ
+    # config 4: b2 = blockNum(256, 2304) = 2*18 = 36 < 148*1.5; (3136 + 3136) / 72 = 87, capped by 148*4/36 = 16
+    assert gz(28, 28, 28, 28, 3, 3, 256, 256, 256, 148) == 16
+    # fewer than 512 output pixels: never split
+    assert gz(7, 7, 7, 7, 3, 3, 4, 512, 512, 148) == 1
+    # the output alone fills the SMs: blockNum(1024, 9*1024) = 8*72 = 576 >= 148 * 1.5 * GK/(GK+1024)
+    assert gz(14, 14, 14, 14, 3, 3, 64, 1024, 1024, 148) == 1
+    # small layer, 784 pixels: b2 = blockNum(64, 288) = 1*3; b0 = blockNum(64, 784) = 7, b1 = blockNum(32, 784) = 7;
+    # 14 / 6 = 2, below the caps 784 >> 8 = 3 and 148*4/3; rounded up to a multiple of 4
+    assert gz(14, 14, 14, 14, 3, 3, 4, 32, 64, 148) == 4
