@@ -201,3 +201,24 @@ def test_conv_layer_weight_gradient_through_the_engine_mirror(pkg, O, cuda):
         G.check_status(pkg)
         rep = O.report(gW.host((OC, F, F, IC)), O.f64.deconv3D_deltaW(X, dY, F, F, st, st, p, p))
         assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (F, st, gz, rep)
+
+
+@pytest.mark.gpu
+def test_deltaw_repeats_bit_for_bit_on_every_tile(pkg, O, cuda):
+    """Same reduction order on every tile shape and in every run: an unfenced hand-over between the im2col loads,
+    the split and the tensor core would show up as a few differing elements in one run of many."""
+    rng = np.random.default_rng(36)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = 8, 28, 28, 64, 96, 3, 3, 1, 1, 1, 1
+    X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+    dY = rng.standard_normal((N, IH, IW, OC)).astype(np.float32)
+    try:
+        pkg.cu32.tune("tile", 4)
+        base = _run(pkg, "dconv3D_deltaW_GemmSK", X, dY, FH, FW, sh, sw, ph, pw, GZ=4)
+        assert O.frob_rel(base, O.f64.deconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw)) <= 1e-6
+        for tile in (0, 1, 2, 3, 4, 8):
+            pkg.cu32.tune("tile", tile)
+            for rep in range(6):
+                R = _run(pkg, "dconv3D_deltaW_GemmSK", X, dY, FH, FW, sh, sw, ph, pw, GZ=4)
+                assert np.array_equal(R, base), (tile, rep, int((R != base).sum()))
+    finally:
+        pkg.cu32.tune("tile", -1)

@@ -578,3 +578,23 @@ def test_strided_deltax_against_golden_fixture(pkg, O, cuda, golden):
             got = _run_strided(pkg, entry, dY, W, IH, IW, sh, sw, ph, pw)
             assert O.frob_rel(got, data[name]) <= 2e-6, (name, entry)   # the golden output carries FP32 accumulation error
             assert O.same_percent(got, data[name], 1e-5) >= 0.999, (name, entry)
+
+
+@pytest.mark.gpu
+def test_strided_deltax_repeats_bit_for_bit_on_every_tile(pkg, O, cuda):
+    rng = np.random.default_rng(68)
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw = 8, 28, 28, 96, 64, 3, 3, 2, 2, 1, 1
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+    try:
+        pkg.cu32.tune("tile", 4)
+        base = _run_strided(pkg, "ksIms2R", dY, W, IH, IW, sh, sw, ph, pw)
+        assert O.frob_rel(base, O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)) <= 1e-6
+        for tile in (0, 1, 2, 3, 4, 8):
+            pkg.cu32.tune("tile", tile)
+            for rep in range(6):
+                R = _run_strided(pkg, "crossAdd" if rep & 1 else "ksIms2R", dY, W, IH, IW, sh, sw, ph, pw)
+                assert np.array_equal(R, base), (tile, rep, int((R != base).sum()))
+    finally:
+        pkg.cu32.tune("tile", -1)
