@@ -5,8 +5,11 @@
 // One kernel template covers every entry point of the Cu32 matMul / batchMatMul /
 // implicit-GEMM convolution family: the operand "major-ness" (which axis is
 // contiguous in memory) is a template flag per operand, the batch index or the
-// split-K slice rides on blockIdx.z, and the A operand can be gathered from an
-// NHWC feature map by an im2col-mode tensor map.
+// split-K slice rides on the tile index, and one operand can be gathered from an
+// NHWC feature map by an im2col-mode tensor map: the A operand for the convolution and
+// its data gradient (rows = output pixels, K = filter taps x channels), the B operand
+// for its weight gradient (K = output pixels, one filter tap per z index).  Output rows
+// may be strided pixels of an image (one phase of a strided data gradient).
 //
 // Arithmetic.  Each FP32 input x is used as
 //     hi = tf32_trunc(x)          lo = tf32_round(x - hi)
