@@ -20,7 +20,7 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
-Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2, c4_dw,
+Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2, c4_dw, c3_qk_scaled,
 c3_qk, c3_pv, c4, c5.
 """
 from __future__ import annotations
@@ -246,15 +246,20 @@ class Workload:
             self.desc = f"matMul {w.form} N={w.N} M={w.M} K={w.K}"
             self.cpu_case = (w.form, w.N, w.M, w.K, w.A, w.B)
             self.units = None
-        elif name in ("c3_qk", "c3_pv"):
+        elif name in ("c3_qk", "c3_qk_scaled", "c3_pv"):
             w = W.config3(Batch=batch)
-            if name == "c3_qk":
+            if name in ("c3_qk", "c3_qk_scaled"):
                 self.hosts = [w.Q.pin_memory(), w.K.pin_memory()]
                 self.dev_in = [h.cuda() for h in self.hosts]
                 self.out = torch.empty((w.Batch, w.L, w.L), device="cuda")
                 dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
                 self.launch = lambda: bm.batchMatMulT2(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.Batch, w.L, w.L, w.L, w.D)
                 self.desc = f"batchMatMulT2 Q*K^T Batch={w.Batch} {w.L}x{w.L}x{w.D}"
+                if name == "c3_qk_scaled":   # the attention block's 1/sqrt(d) scale fused into the store
+                    alpha = 1.0 / (w.D ** 0.5)
+                    self.launch = lambda: bm.batchMatMulT2_scaled(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                                                                  w.Batch, w.L, w.L, w.L, w.D, alpha)
+                    self.desc = f"batchMatMulT2_scaled Q*K^T/sqrt(d) Batch={w.Batch} {w.L}x{w.L}x{w.D}"
             else:
                 g = torch.Generator().manual_seed(3003)
                 P = torch.softmax(torch.randn((w.Batch, w.L, w.L), generator=g), dim=-1)

@@ -124,6 +124,8 @@ struct GemmCall {
   cudaStream_t stream;
   const float* bias;        // optional row vector (n_store floats) added in the epilogue; needs gz == 1, batch == 1
   int bias_width;           // true width of the rows: columns beyond it are stored as zeros
+  bool scale_on = false;   // store alpha * result (one rounding), vector store paths only
+  float alpha = 1.0f;
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -163,6 +165,7 @@ static int run_gemm(const GemmCall& c) {
     if (c.bias_width <= 0 || c.bias_width > c.n_store) return CU32_E_DIM;
     if (!aligned16(c.bias) || (c.n_store & 3)) return CU32_E_ALIGN;
   }
+  if (c.scale_on && (c.gz != 1 || c.bias)) return CU32_E_ARG;
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
@@ -198,6 +201,8 @@ static int run_gemm(const GemmCall& c) {
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;   // the bias is applied on the vector store paths only
+  if (c.scale_on && !p.vec4_ok) return CU32_E_ALIGN;
+  p.scale_on = c.scale_on ? 1 : 0; p.alpha = c.alpha;
   if (p.vec4_ok) {
     // Output maps for the TMA-store epilogue: (columns, rows, batch) with the caller's pitch.
     const uint64_t zs_c = c.gz > 1 ? 1 : nb;
@@ -854,13 +859,14 @@ int cu32_SKbuf_summary_biased(int64_t stream, const float* dCbuf, float* dC, con
 
 // ---- batched
 static int bmm_any(int form, bool x3, const int64_t* s, int n, const float* A, const float* B, float* C,
-                   int Batch, int d0, int d1, int d2, int d3) {
+                   int Batch, int d0, int d1, int d2, int d3, bool scaled = false, float alpha = 1.0f) {
   cudaStream_t st;
   if (int rc = check_streams(s, n, &st)) return rc;
   if (Batch <= 0 || d0 <= 0 || d1 <= 0 || d2 <= 0 || d3 <= 0) return CU32_E_DIM;
   GemmCall c{};
   c.A = A; c.B = B; c.C = C; c.Cbuf = nullptr;
   c.batch = Batch; c.gz = 1; c.x3 = x3; c.stream = st;
+  c.scale_on = scaled; c.alpha = alpha;
   if (form == FORM_AB) {            // (Batch, N, M, BK, AK)
     const int N = d0, M = d1, BK = d2, AK = d3;
     if (AK < BK) return CU32_E_DIM;
@@ -884,6 +890,22 @@ static int bmm_any(int form, bool x3, const int64_t* s, int n, const float* A, c
     c.ldc = CM; c.sC = static_cast<long long>(N) * CM;
   }
   return run_gemm(c);
+}
+
+// ---- batched contraction + scalar scale in one pass (no counterpart among the reference's natives: its
+// attention block runs sdiv = linear2D(1/sqrt(d), X, 0) as a second kernel over the scores,
+// nn/unit/complex/block/ImageMHA.java:67-68, Engine.java:4002, Cuda_function/type1_linear2D.cuh:40-58)
+int cu32_batchMatMul_scaled(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int N, int M,
+                            int BK, int AK, float alpha) {
+  return bmm_any(FORM_AB, true, s, n, A, B, C, Batch, N, M, BK, AK, true, alpha);
+}
+int cu32_batchMatMulT1_scaled(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int CN,
+                              int AN, int M, int K, float alpha) {
+  return bmm_any(FORM_T1, true, s, n, A, B, C, Batch, CN, AN, M, K, true, alpha);
+}
+int cu32_batchMatMulT2_scaled(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int N,
+                              int CM, int BM, int K, float alpha) {
+  return bmm_any(FORM_T2, true, s, n, A, B, C, Batch, N, CM, BM, K, true, alpha);
 }
 
 int cu32_batchMatMul(const int64_t* s, int n, const float* A, const float* B, float* C, int Batch, int N,

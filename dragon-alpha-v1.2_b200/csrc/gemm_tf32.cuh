@@ -83,6 +83,8 @@ struct GemmParams {
   int bmap_order;       // 0: B map coordinates (n, tap, k) - filter W[k][tap][n];  1: (n, k, tap) - filter CW[tap][k][n]
   // Strided output rows (data gradient for strides > 1): row -> (image, u, v) -> element offset
   // image * os_sn + u * os_su + v * os_sv; stores go straight from registers.
+  int scale_on;         // multiply every output element by alpha on its way out (one FP32 rounding)
+  float alpha;
   int ztaps;            // > 0: weight gradient, the z index is slice * ztaps + filter tap
   int os_on, os_uv, os_v;
   long long os_sn, os_su, os_sv;
@@ -714,6 +716,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       // after the product - one FP32 add per element, padding columns forced to zero.  Applied to
       // each 4-column vector on its way out, so that no more than a few bias values are live.
       auto with_bias = [&](int j, float4 v) -> float4 {
+        if (p.scale_on) {   // what a separate y = alpha*x + 0 kernel would store: one fused multiply-add per element
+          v.x = fmaf(v.x, p.alpha, 0.0f); v.y = fmaf(v.y, p.alpha, 0.0f);
+          v.z = fmaf(v.z, p.alpha, 0.0f); v.w = fmaf(v.w, p.alpha, 0.0f);
+        }
         if (p.bias == nullptr) return v;
         const int c = w.col0 + h * CW + j;   // a multiple of 4, like p.N: all four columns exist or none
         if (c >= p.N) return v;

@@ -283,6 +283,20 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksV2_1Ims2R)(JNIEnv* env, jclas
   done(env, cu32_dconv3D_deltaX_ksV2_Ims2R(useTexture ? 1 : 0, DX_PASS, ph, pw));
 }
 
+// Batched contraction + scale in one pass; a Java class would declare them as
+//   public static native void batchMatMul[T1|T2]_scaled(long[] streamArray, int length, long dA, long dB, long dC,
+//                                                       int Batch, int d0, int d1, int d2, int d3, float alpha);
+#define BMM_SCALED(jname, cname)                                                                                   \
+  JNIEXPORT void JNICALL JNAME(batchMatMul, jname)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dA,  \
+                                                   jlong dB, jlong dC, jint Batch, jint d0, jint d1, jint d2,       \
+                                                   jint d3, jfloat alpha) {                                        \
+    Streams s(env, streams, length);                                                                               \
+    done(env, cname(s.h, s.n, cptr(dA), cptr(dB), mptr(dC), Batch, d0, d1, d2, d3, alpha));                        \
+  }
+BMM_SCALED(batchMatMul_1scaled, cu32_batchMatMul_scaled)
+BMM_SCALED(batchMatMulT1_1scaled, cu32_batchMatMulT1_scaled)
+BMM_SCALED(batchMatMulT2_1scaled, cu32_batchMatMulT2_scaled)
+
 // ---- Cuda_dconv3D_deltaW (Java declarations: Cuda_dconv3D_deltaW.java:288-640)
 #define JNAME_DW(method) Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_##method
 JNIEXPORT void JNICALL JNAME_DW(dconv3D_1deltaW)(JNIEnv* env, jclass, jlongArray streams, jint length, jlong dX, jint IH,

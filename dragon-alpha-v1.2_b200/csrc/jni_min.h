@@ -12,6 +12,7 @@
 extern "C" {
 
 typedef int32_t jint;
+typedef float jfloat;
 typedef int64_t jlong;
 typedef uint8_t jboolean;
 typedef void* jobject;

@@ -115,6 +115,9 @@ SIGNATURES = {
     "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s4_texture": [_sp, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
     "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s8_texture": [_sp, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
     "cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture": [_sp, _I, _I, _I, _I, _I, _fp, _I, _I, _fp, _I, _I, _fp, _fp] + [_I] * 8,
+    "cu32_batchMatMul_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
+    "cu32_batchMatMulT1_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
+    "cu32_batchMatMulT2_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -672,3 +675,17 @@ class Cuda_dconv3D_deltaW:
     @staticmethod
     def Im2col_WinogradV2_SHW_s16_texture(streamArray, length, GridZ, OH_slice, OW_slice, c64, *a):
         return Cuda_dconv3D_deltaW._wino("s16_texture", (c64,), streamArray, length, GridZ, OH_slice, OW_slice, *a)
+
+
+def _add_scaled_methods():
+    """batchMatMul*_scaled: the batched natives with the attention block's 1/sqrt(d) scale fused into the store."""
+    def make(name):
+        def f(streamArray, length, dA, dB, dC, Batch, d0, d1, d2, d3, alpha):
+            s, n = _streams(streamArray, length)
+            _check(getattr(load(), "cu32_" + name)(s, n, _p(dA), _p(dB), _p(dC), Batch, d0, d1, d2, d3, float(alpha)), name)
+        return staticmethod(f)
+    for nm in ("batchMatMul_scaled", "batchMatMulT1_scaled", "batchMatMulT2_scaled"):
+        setattr(Cuda_batchMatMul, nm, make(nm))
+
+
+_add_scaled_methods()

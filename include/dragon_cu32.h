@@ -273,6 +273,20 @@ CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM(int useTexture,
                            const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
                            float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
 
+/* ------------------------------------------------------------------ batched contraction + scale (optional)
+ * C = alpha * (A x B) with the product rounded to FP32 first and the scale applied as one fused multiply-add with a
+ * zero addend - the bits of the reference's two-kernel sequence batchMatMul* followed by sdiv(sqrt(d), C) =
+ * linear2D(1/sqrt(d), C, 0) (nn/unit/complex/block/ImageMHA.java:67-68, Engine.java:4002,
+ * Cuda_function/type1_linear2D.cuh:40-58, micro.cuh:54-58) - without the second pass over C.  No counterpart among the
+ * reference's natives; arguments as the unscaled entry points plus alpha.  C must be 16-byte aligned with a pitch that
+ * is a multiple of 4 floats (CU32_E_ALIGN otherwise). */
+CU32_API int cu32_batchMatMul_scaled(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                           int Batch, int N, int M, int BK, int AK, float alpha);
+CU32_API int cu32_batchMatMulT1_scaled(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                           int Batch, int CN, int AN, int M, int K, float alpha);
+CU32_API int cu32_batchMatMulT2_scaled(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                           int Batch, int N, int CM, int BM, int K, float alpha);
+
 /* ------------------------------------------------------------------ Cuda_dconv3D_deltaW
  * deltaW[oc,fh,fw,ic] = sum over (n,oh,ow) of deltaY[n,oh,ow,oc] * X[n, oh*sh-ph+fh, ow*sw-pw+fw, ic] (zero outside
  * the image); X [N,IH,IW,IC], deltaY [N,OH,OW,OC], deltaW [OC,FH,FW,IC], IC and OC multiples of 4.  These replace the

@@ -7,7 +7,7 @@ where they lie; nothing is copied into this repository):
   libref_bmm.so      Cuda_batchMatMul: same
   libref_conv.so     Cuda_conv3D:      same (about 25 minutes; only with --conv)
   libref_deltax.so   Cuda_dconv3D_deltaX: CPU check loop + stride-1 dispatcher (long build; only with --deltax)
-  libref_function.so Cuda_function:    only linear_dual2D_row, the bias-row add that follows the
+  libref_function.so Cuda_function:    linear_dual2D_row, the bias-row add that follows the
                                        contractions in matMul_biased / conv3D_biased (seconds)
 
 The CPU loops pin oracle/cu32_oracle.c (tests/test_oracle.py compares them bit for bit) and

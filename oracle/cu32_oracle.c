@@ -425,3 +425,9 @@ void oracle_deconv3D_deltaW_f64(const float* X, int IH, int IW, const float* del
         }
       }
 }
+
+/* Y = alpha * X + beta, element by element: the reference's linear2D kernel (Cuda_function/type1_linear2D.cuh:40-58
+ * with simdLinear4, micro.cuh:54-58: x * alpha + beta, which nvcc contracts to one fused multiply-add). */
+void oracle_linear2D(float alpha, const float* X, float beta, float* Y, long long length) {
+  for (long long i = 0; i < length; i++) Y[i] = fmaf(X[i], alpha, beta);
+}

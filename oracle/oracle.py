@@ -177,6 +177,14 @@ class ref_loops:
         return dW
 
     @staticmethod
+    def linear2D(alpha, X, beta):
+        """Y = alpha * X + beta as the reference's linear2D kernel computes it (type1_linear2D.cuh:40-58): one FMA."""
+        X = _c32(X)
+        Y = np.empty_like(X)
+        lib().oracle_linear2D(c_float(alpha), _f(X), c_float(beta), _f(Y), ctypes.c_longlong(X.size))
+        return Y
+
+    @staticmethod
     def ks_remode(W, sh, sw, v2=True, fill=np.nan):
         """W [OC, FH, FW, IC] -> the kernel-split workspace as a flat array of sh*sw*OC*mCFH*mCFW*IC floats
         (dconv3D_dX_kernelSplit_remode_v1.cuh:28-66 / _v2.cuh:31-66); untouched elements keep `fill`."""
