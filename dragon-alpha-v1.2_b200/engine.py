@@ -205,6 +205,20 @@ class Cu32Engine:
         sa, n = self._stream_array(N, CM)
         Cuda_batchMatMul.batchMatMulT2_texture(sa, n, A, B, C, Batch, N, CM, BM, K)
 
+    def batchMatMulT1_sdiv(self, C, A, B, Batch, CN, AN, M, K, divisor):
+        """sdiv(divisor, batchMatMulT1(A, B)) - the attention block's scaled scores (ImageMHA.java:67-68) - in one
+        kernel; alpha is formed as the Java engine forms it, 1.0f / divisor in FP32 (Engine.java:4002)."""
+        import numpy as np
+        sa, n = self._stream_array(CN, M)
+        alpha = float(np.float32(1.0) / np.float32(divisor))
+        Cuda_batchMatMul.batchMatMulT1_scaled(sa, n, A, B, C, Batch, CN, AN, M, K, alpha)
+
+    def batchMatMulT2_sdiv(self, C, A, B, Batch, N, CM, BM, K, divisor):
+        import numpy as np
+        sa, n = self._stream_array(N, CM)
+        alpha = float(np.float32(1.0) / np.float32(divisor))
+        Cuda_batchMatMul.batchMatMulT2_scaled(sa, n, A, B, C, Batch, N, CM, BM, K, alpha)
+
     def conv3D(self, Y, OH, OW, X, IH, IW, W, FH, FW, N, IC, OC, sh, sw, ph, pw):
         """Forward convolution the way the Java engine runs its GEMMR branch: remode the
         filter on streams[0], then the implicit GEMM (CudaFloat32EngineBase.java:2268-2332)."""

@@ -87,3 +87,24 @@ def test_scaled_is_the_product_followed_by_the_scale_kernel(pkg, O, cuda, form, 
                                     ctypes.c_float(0.0), ctypes.c_void_p(t.data_ptr()), n, cols, cols) == 0
         cuda.cuda.synchronize()
         assert np.array_equal(t.cpu().numpy(), fused)
+
+
+@pytest.mark.gpu
+def test_attention_scores_through_the_engine_mirror(pkg, O, cuda):
+    """Q [Batch, d, L] and K [Batch, d, L] as the reference's attention block lays them out: scores = Q^T K / sqrt(d)."""
+    import gpu_util as G
+    torch = cuda
+    eng = pkg.engine.Cu32Engine(148, lambda n: (0, None), [G.stream()])
+    rng = np.random.default_rng(42)
+    Batch, d, L = 8, 32, 96
+    Q = rng.standard_normal((Batch, d, L)).astype(np.float32)
+    K = rng.standard_normal((Batch, d, L)).astype(np.float32)
+    dQ, dK = G.dev(Q), G.dev(K)
+    out = G.Out(Batch * L * L)
+    eng.batchMatMulT1_sdiv(out.ptr, dQ.data_ptr(), dK.data_ptr(), Batch, L, L, L, d, float(np.sqrt(d)))
+    G.check_status(pkg)
+    S = out.host((Batch, L, L))
+    alpha = np.float32(1.0) / np.float32(np.sqrt(d))
+    want = np.einsum("bkn,bkm->bnm", Q.astype(np.float64), K.astype(np.float64)) * np.float64(alpha)
+    rep = O.report(S, want)
+    assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, rep
