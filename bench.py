@@ -545,11 +545,13 @@ def main():
     if world > 1:
         # The only collective of the path: putting the shards' outputs back together (all-gather
         # over NVLink), or for the K-sharded long-K shape summing the partial products.
-        if a.workload == "c5":
+        if a.workload in ("c5", "c4_dw"):
+            # K-sharded shapes: each rank reduces over its own rows (c5) or its own images (the convolution's
+            # weight gradient, the data-parallel training pattern) and the partial outputs are summed
             def step_collective():
                 wl.launch()
                 dist.all_reduce(wl.out)
-            kind = "all-reduce of the [N,M] partial products"
+            kind = "all-reduce of the partial products"
         else:
             gathered = torch.empty((world,) + tuple(wl.out.shape), device="cuda")
 
