@@ -62,11 +62,24 @@ def _worker(rank, world, port, results):
         ok_k = True
         if rank == 0:
             ok_k = torch.allclose(part, At.T @ Bt, rtol=0, atol=1e-10)
+        # --- convolution weight gradient: images sharded, each rank's partial deltaW summed (data-parallel training)
+        Xi = torch.rand((Nimg, 5, 5, 4), generator=g, dtype=torch.float64)
+        dYi = torch.rand((Nimg, 5, 5, 4), generator=g, dtype=torch.float64)
+
+        def dw(X, dY):   # 3x3, stride 1, pad 1: deltaW[oc, fh, fw, ic]
+            Xp = torch.nn.functional.pad(X, (0, 0, 1, 1, 1, 1))
+            return torch.stack([torch.stack([torch.einsum("nhwo,nhwi->oi", dY, Xp[:, fh:fh + 5, fw:fw + 5, :])
+                                             for fw in range(3)], 1) for fh in range(3)], 1)
+        part_w = dw(Xi[i0:i1], dYi[i0:i1]).contiguous()
+        sh.reduce_partials(dist, part_w, dst=0)
+        ok_dw = True
+        if rank == 0:
+            ok_dw = torch.allclose(part_w, dw(Xi, dYi), rtol=0, atol=1e-10)
         # --- max-over-ranks timing reduction used by the benchmark
         t = torch.tensor([float(rank + 1)])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ok_t = t.item() == float(world)
-        results[rank] = bool(ok_mm and ok_bmm and ok_img and ok_k and ok_t)
+        results[rank] = bool(ok_mm and ok_bmm and ok_img and ok_k and ok_dw and ok_t)
     finally:
         dist.destroy_process_group()
 
