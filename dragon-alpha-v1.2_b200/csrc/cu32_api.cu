@@ -458,7 +458,8 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
 // 180 degrees and read "transposed" in place.  The filter rotation is a reversal of the tap index in
 // the TMA producer; nothing is re-laid-out or copied.
 static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, int OH, int OW, const float* dW,
-                         int FH, int FW, float* dDX, int IH, int IW, int N, int IC, int OC, int ph, int pw) {
+                         int FH, int FW, float* dDX, int IH, int IW, int N, int IC, int OC, int ph, int pw,
+                         const float* dBias = nullptr, int width = 0) {
   if (!dDY || !dW || !dDX) return CU32_E_NULL;
   if (FH <= 0 || FW <= 0 || ph < 0 || pw < 0 || IC <= 0 || OC <= 0) return CU32_E_DIM;
   if ((IC & 3) || (OC & 3)) return CU32_E_ALIGN;
@@ -466,7 +467,7 @@ static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, i
   if (IH != OH - 1 + FH - 2 * ph || IW != OW - 1 + FW - 2 * pw) return CU32_E_DIM;
   if (FH > 16 || FW > 16) return CU32_E_GEOMETRY;           // the tap index travels in the batch coordinate
   return conv_any(true, streams, length, dDY, OH, OW, dW, FH, FW, dDX, IH, IW, N, /*in*/ OC, /*out*/ IC, 1, 1,
-                  FH - 1 - ph, FW - 1 - pw, nullptr, 0, true);
+                  FH - 1 - ph, FW - 1 - pw, dBias, width, true);
 }
 
 // ------------------------------------------------------------------ kernel-split filter workspace
@@ -530,7 +531,8 @@ static int ceil_div(int a, int b) { return a >= 0 ? (a + b - 1) / b : -((-a) / b
 
 static int deconv_strided_any(const int64_t* streams, int length, const float* dDY, int OH, int OW,
                               const float* filt, bool filt_is_cw, int FH, int FW, float* dDX, int IH, int IW, int N,
-                              int IC, int OC, int sh, int sw, int ph, int pw) {
+                              int IC, int OC, int sh, int sw, int ph, int pw, const float* dBias = nullptr,
+                              int width = 0) {
   load_env_once();
   cudaStream_t st;
   if (int rc = check_streams(streams, length, &st)) return rc;
@@ -544,6 +546,11 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
   if (static_cast<long long>(N) * IH * IW * IC >= (1LL << 31) || static_cast<long long>(N) * OH * OW * OC >= (1LL << 31))
     return CU32_E_DIM;
   if (sh > 16 || sw > 16 || FH > 256 || FW > 256) return CU32_E_GEOMETRY;
+  if (dBias) {
+    if (width <= 0 || width > IC) return CU32_E_DIM;
+    if (!aligned16(dBias)) return CU32_E_ALIGN;
+    if (FH < sh || FW < sw) return CU32_E_GEOMETRY;   // pixels no tap reaches would need the bias alone
+  }
   if (!load_driver_entry_points() || !g_encode_im2col) return CU32_E_DRIVER;
   const int mCFH = (FH + sh - 1) / sh, mCFW = (FW + sw - 1) / sw;
   cudaError_t e;
@@ -612,6 +619,7 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
         p.tap_sy = -sh * FW;
         p.tap_sx = -sw;
       }
+      p.bias = dBias; p.bias_width = width;
       p.C = dDX + (static_cast<long long>(u0 * sh + y - ph) * IW + (v0 * sw + x - pw)) * IC;
       p.Cbuf = nullptr; p.ldc = IC; p.c_stride = 0;
       p.os_on = 1; p.os_uv = U * V; p.os_v = V;
@@ -890,6 +898,22 @@ static int bmm_any(int form, bool x3, const int64_t* s, int n, const float* A, c
     c.ldc = CM; c.sC = static_cast<long long>(N) * CM;
   }
   return run_gemm(c);
+}
+
+// ---- data gradient / transposed convolution + bias row in one pass (no counterpart among the reference's natives:
+// the Java engine's deconv3D_biased runs Cuda_function.linear_dual2D_row(Y, bias, 1, 1, 0) as a second kernel,
+// CudaFloat32EngineBase.java:2620-2650).  Bias has IC entries (the channels of the output), width <= IC are real.
+int cu32_dconv3D_deltaX_s1_biased(const int64_t* s, int n, const float* dY, int OH, int OW, const float* W, int FH,
+                                  int FW, float* dX, int IH, int IW, int N, int IC, int OC, int ph, int pw,
+                                  const float* Bias, int width) {
+  if (!Bias) return CU32_E_NULL;
+  return deconv_s1_any(s, n, dY, OH, OW, W, FH, FW, dX, IH, IW, N, IC, OC, ph, pw, Bias, width);
+}
+int cu32_dconv3D_deltaX_ksImsR_biased(const int64_t* s, int n, const float* dY, int OH, int OW, const float* CW, int FH,
+                                      int FW, float* dX, int IH, int IW, int N, int IC, int OC, int sh, int sw, int ph,
+                                      int pw, const float* Bias, int width) {
+  if (!Bias) return CU32_E_NULL;
+  return deconv_strided_any(s, n, dY, OH, OW, CW, true, FH, FW, dX, IH, IW, N, IC, OC, sh, sw, ph, pw, Bias, width);
 }
 
 // ---- batched contraction + scalar scale in one pass (no counterpart among the reference's natives: its

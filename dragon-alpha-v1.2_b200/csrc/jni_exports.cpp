@@ -283,6 +283,19 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksV2_1Ims2R)(JNIEnv* env, jclas
   done(env, cu32_dconv3D_deltaX_ksV2_Ims2R(useTexture ? 1 : 0, DX_PASS, ph, pw));
 }
 
+// Data gradient / transposed convolution + bias row in one pass (arguments of the unbiased native, then the bias
+// address and the true row width).
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1s1_1biased)(JNIEnv* env, jclass, DX_HEAD, jint ph, jint pw,
+                                                             jlong dBias, jint width) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_s1_biased(DX_PASS, ph, pw, cptr(dBias), width));
+}
+JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksImsR_1biased)(JNIEnv* env, jclass, DX_HEAD, jint sh, jint sw, jint ph,
+                                                                 jint pw, jlong dBias, jint width) {
+  Streams s(env, streams, length);
+  done(env, cu32_dconv3D_deltaX_ksImsR_biased(DX_PASS, sh, sw, ph, pw, cptr(dBias), width));
+}
+
 // Batched contraction + scale in one pass; a Java class would declare them as
 //   public static native void batchMatMul[T1|T2]_scaled(long[] streamArray, int length, long dA, long dB, long dC,
 //                                                       int Batch, int d0, int d1, int d2, int d3, float alpha);

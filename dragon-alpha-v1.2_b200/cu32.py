@@ -118,6 +118,8 @@ SIGNATURES = {
     "cu32_batchMatMul_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_batchMatMulT1_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_batchMatMulT2_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
+    "cu32_dconv3D_deltaX_s1_biased": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7 + [_fp, _I],
+    "cu32_dconv3D_deltaX_ksImsR_biased": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9 + [_fp, _I],
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_matMul_mma_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
     "cu32_SKbuf_summary_biased": [c_int64, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -689,3 +691,20 @@ def _add_scaled_methods():
 
 
 _add_scaled_methods()
+
+
+def _add_dx_biased_methods():
+    def s1(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, dBias, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_s1_biased(s, n, _p(d_deltaY), OH, OW, _p(dW), FH, FW, _p(d_deltaX), IH, IW, N, IC,
+                                                    OC, ph, pw, _p(dBias), width), "dconv3D_deltaX_s1_biased")
+
+    def ks(streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw, dBias, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_ksImsR_biased(s, n, _p(d_deltaY), OH, OW, _p(dCW), FH, FW, _p(d_deltaX), IH, IW, N,
+                                                        IC, OC, sh, sw, ph, pw, _p(dBias), width), "dconv3D_deltaX_ksImsR_biased")
+    Cuda_dconv3D_deltaX.dconv3D_deltaX_s1_biased = staticmethod(s1)
+    Cuda_dconv3D_deltaX.dconv3D_deltaX_ksImsR_biased = staticmethod(ks)
+
+
+_add_dx_biased_methods()

@@ -273,6 +273,19 @@ CU32_API int cu32_dconv3D_deltaX_Im2col_Winograd_s16_texture_SGM(int useTexture,
                            const float* d_deltaY, int OH, int OW, const float* dW, int FH, int FW,
                            float* d_deltaX, int IH, int IW, int N, int IC, int OC, int ph, int pw, int GM_slice);
 
+/* ------------------------------------------------------------------ data gradient + bias row (optional)
+ * The Java engine's transposed convolution (deconv3D_biased, CudaFloat32EngineBase.java:2590-2740) runs a deltaX native
+ * and then Cuda_function.linear_dual2D_row(Y, Bias, 1, 1, 0, Y, lengthv, width, stride) as a second kernel; these two
+ * add the bias row (IC floats; columns >= width come out 0) in the epilogue with the bits of that sequence.  _s1: the
+ * forward filter as it lies; _ksImsR: the ks_remodev2 workspace, any stride (FH >= sh and FW >= sw required here).
+ * No counterpart among the reference's natives. */
+CU32_API int cu32_dconv3D_deltaX_s1_biased(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC, int OC,
+                           int ph, int pw, const float* dBias, int width);
+CU32_API int cu32_dconv3D_deltaX_ksImsR_biased(const int64_t* streams, int length, const float* d_deltaY, int OH, int OW,
+                           const float* dCW, int FH, int FW, float* d_deltaX, int IH, int IW, int N, int IC, int OC,
+                           int sh, int sw, int ph, int pw, const float* dBias, int width);
+
 /* ------------------------------------------------------------------ batched contraction + scale (optional)
  * C = alpha * (A x B) with the product rounded to FP32 first and the scale applied as one fused multiply-add with a
  * zero addend - the bits of the reference's two-kernel sequence batchMatMul* followed by sdiv(sqrt(d), C) =

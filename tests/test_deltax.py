@@ -598,3 +598,45 @@ def test_strided_deltax_repeats_bit_for_bit_on_every_tile(pkg, O, cuda):
                 assert np.array_equal(R, base), (tile, rep, int((R != base).sum()))
     finally:
         pkg.cu32.tune("tile", -1)
+
+
+# ------------------------------------------------------------------ bias row fused into the data gradient
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [
+    # N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, width
+    (4, 12, 12, 32, 48, 3, 3, 1, 1, 1, 1, 32),
+    (2, 9, 10, 132, 64, 3, 3, 1, 1, 1, 1, 130),      # padded channels: columns >= width come out 0
+    (3, 8, 8, 24, 16, 1, 1, 1, 1, 0, 0, 24),         # 1x1: the plain contraction
+    (4, 16, 16, 32, 64, 3, 3, 2, 2, 1, 1, 32),       # stride 2 through the kernel-split workspace
+    (2, 15, 17, 36, 40, 3, 3, 3, 3, 1, 1, 34),
+    (2, 14, 13, 64, 128, 4, 4, 2, 1, 1, 2, 64),
+])
+def test_deltax_biased_is_the_unbiased_native_followed_by_the_bias_kernel(pkg, O, cuda, case):
+    """The transposed convolution's forward pass with bias: the fused entry points must store the bits of the
+    data-gradient native followed by linear_dual2D_row(Y, bias, 1, 1, 0)."""
+    import gpu_util as G
+    N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw, width = case
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    rng = np.random.default_rng(69)
+    dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+    W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+    bias = rng.standard_normal(IC).astype(np.float32)
+    dx = pkg.cu32.Cuda_dconv3D_deltaX
+    ddY, dB = G.dev(dY), G.dev(bias)
+    out = G.Out(N * IH * IW * IC)
+    if sh == 1 and sw == 1:
+        plain = _run(pkg, "dconv3D_deltaX_W1" if (FH, FW, ph, pw) == (1, 1, 0, 0) else "dconv3D_deltaX_s1", dY, W, IH, IW, ph, pw)
+        dW = G.dev(W)
+        dx.dconv3D_deltaX_s1_biased([G.stream()], 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), FH, FW, out.ptr, IH, IW, N, IC, OC,
+                                    ph, pw, dB.data_ptr(), width)
+    else:
+        plain = _run_strided(pkg, "ksImsR", dY, W, IH, IW, sh, sw, ph, pw)
+        dCW = _remode_dev(pkg, W, sh, sw)
+        dx.dconv3D_deltaX_ksImsR_biased([G.stream()], 1, ddY.data_ptr(), OH, OW, dCW.data_ptr(), FH, FW, out.ptr, IH, IW, N, IC,
+                                        OC, sh, sw, ph, pw, dB.data_ptr(), width)
+    fused = out.host((N, IH, IW, IC))
+    G.check_status(pkg)
+    want = O.ref_loops.linear_dual2D_row(plain.reshape(-1, IC), bias, 1.0, 1.0, 0.0, width).reshape(fused.shape)
+    assert np.array_equal(fused, want)
+    if width < IC:
+        assert not fused[..., width:].any()

@@ -110,7 +110,7 @@ def _header_symbols():
 def test_library_exports_every_declared_symbol(pkg):
     lib = pkg.cu32.load()
     names = _header_symbols()
-    assert len(names) >= 81
+    assert len(names) >= 83
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/dragon_cu32.h but not exported"
     # the ctypes table covers the same surface
@@ -136,7 +136,8 @@ def test_jni_symbols_exported(pkg):
                  "conv3D_conv3D_1Im2col_1WinogradR_1s16_1texture_1SGM"}
     want_fused = {"matMul_matMul_1biased", "matMul_matMul_1mma_1biased", "matMul_SKbuf_1summary_1biased",
                   "conv3D_conv3D_1GemmR_1biased", "batchMatMul_batchMatMul_1scaled", "batchMatMul_batchMatMulT1_1scaled",
-                  "batchMatMul_batchMatMulT2_1scaled"}   # no counterpart in the reference's Java classes
+                  "batchMatMul_batchMatMulT2_1scaled", "dconv3D_1deltaX_dconv3D_1deltaX_1s1_1biased",
+                  "dconv3D_1deltaX_dconv3D_1deltaX_1ksImsR_1biased"}   # no counterpart in the reference's Java classes
     want_dx = {"dconv3D_1deltaX_dconv3D_1deltaX_1s1", "dconv3D_1deltaX_dconv3D_1deltaX_1s1_1SGM",
                "dconv3D_1deltaX_dconv3D_1deltaX_1s1_1texture", "dconv3D_1deltaX_dconv3D_1deltaX_1s1_1texture_1SGM",
                "dconv3D_1deltaX_dconv3D_1deltaX_1W1", "dconv3D_1deltaX_dconv3D_1deltaX_1W1_1SGM",
