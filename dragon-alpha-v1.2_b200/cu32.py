@@ -353,6 +353,24 @@ class Cuda_batchMatMul:
         _check(load().cu32_batchMatMulT2_mma(int(bool(useTexture)), s, n, _p(dA), _p(dB), _p(dC), Batch, N, CM, BM, K),
                "batchMatMulT2_mma")
 
+    # scale fused into the store (no counterpart in the Java class): arguments of the unscaled native, then alpha
+    @staticmethod
+    def _scaled(name, streamArray, length, dA, dB, dC, Batch, d0, d1, d2, d3, alpha):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_" + name)(s, n, _p(dA), _p(dB), _p(dC), Batch, d0, d1, d2, d3, float(alpha)), name)
+
+    @staticmethod
+    def batchMatMul_scaled(streamArray, length, dA, dB, dC, Batch, N, M, BK, AK, alpha):
+        Cuda_batchMatMul._scaled("batchMatMul_scaled", streamArray, length, dA, dB, dC, Batch, N, M, BK, AK, alpha)
+
+    @staticmethod
+    def batchMatMulT1_scaled(streamArray, length, dA, dB, dC, Batch, CN, AN, M, K, alpha):
+        Cuda_batchMatMul._scaled("batchMatMulT1_scaled", streamArray, length, dA, dB, dC, Batch, CN, AN, M, K, alpha)
+
+    @staticmethod
+    def batchMatMulT2_scaled(streamArray, length, dA, dB, dC, Batch, N, CM, BM, K, alpha):
+        Cuda_batchMatMul._scaled("batchMatMulT2_scaled", streamArray, length, dA, dB, dC, Batch, N, CM, BM, K, alpha)
+
 
 class Cuda_conv3D:
     """Mirror of the GEMM / GEMMR natives of z.dragon.engine.cuda.impl.math.Cuda_conv3D."""
@@ -495,6 +513,17 @@ class Cuda_conv3D:
         return Cuda_conv3D.grid_slice << (7 if flag else 6)
 
 
+def _dx_native(name):
+    """A strided data-gradient native of Cuda_dconv3D_deltaX: every one takes the same leading arguments, followed by
+    its own tail of geometry integers, and forwards them unchanged."""
+    def f(streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC, OC, *tail):
+        s, n = _streams(streamArray, length)
+        _check(getattr(load(), "cu32_dconv3D_deltaX_" + name)(s, n, _p(d_deltaY), OH, OW, _p(dF), FH, FW, _p(d_deltaX),
+                                                              IH, IW, N, IC, OC, *tail), name)
+    f.__name__ = "dconv3D_deltaX_" + name
+    return staticmethod(f)
+
+
 class Cuda_dconv3D_deltaX:
     """Mirror of the stride-1 natives of z.dragon.engine.cuda.impl.math.Cuda_dconv3D_deltaX (the data gradient
     of the forward convolution; reference: Cuda_dconv3D_deltaX/A.cu:21-277, :837-1040) and, further down, of the
@@ -591,31 +620,40 @@ class Cuda_dconv3D_deltaX:
                                                               _p(d_deltaX), IH, IW, N, IC, OC, *tail), name)
 
 
-def _add_ks_methods():
-    def strided(name):
-        def f(streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw, *gm):
-            Cuda_dconv3D_deltaX._ks(name, (), streamArray, length, d_deltaY, OH, OW, dF, FH, FW, d_deltaX, IH, IW, N, IC,
-                                    OC, sh, sw, ph, pw, *gm)
-        return staticmethod(f)
-
-    def stride2(name):
-        def f(streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, *gm):
-            Cuda_dconv3D_deltaX._ks(name, (), streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC,
-                                    OC, ph, pw, *gm)
-        return staticmethod(f)
-    for nm in ("kernelSplit", "kernelSplit_SGM", "ksImsR", "ksImsR_SGM", "ksImsR_texture", "ksImsR_texture_SGM", "crossAdd",
-               "crossAdd_SGM"):
-        setattr(Cuda_dconv3D_deltaX, "dconv3D_deltaX_" + nm, strided(nm))
-    for nm in ("ksIms2R", "ksIms2R_SGM", "ksIms2R_texture", "ksIms2R_texture_SGM"):
-        setattr(Cuda_dconv3D_deltaX, "dconv3D_deltaX_" + nm, stride2(nm))
-
-    def ksv2(useTexture, streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw):
+    @staticmethod
+    def dconv3D_deltaX_ksV2_Ims2R(useTexture, streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC,
+                                  OC, ph, pw):
         Cuda_dconv3D_deltaX._ks("ksV2_Ims2R", (int(bool(useTexture)),), streamArray, length, d_deltaY, OH, OW, dCW, FH, FW,
                                 d_deltaX, IH, IW, N, IC, OC, ph, pw)
-    Cuda_dconv3D_deltaX.dconv3D_deltaX_ksV2_Ims2R = staticmethod(ksv2)
 
+    # (…, sh, sw, ph, pw[, GM_slice]) for any stride; (…, ph, pw[, GM_slice]) for the stride-2 "Ims2" natives
+    dconv3D_deltaX_kernelSplit = _dx_native("kernelSplit")
+    dconv3D_deltaX_kernelSplit_SGM = _dx_native("kernelSplit_SGM")
+    dconv3D_deltaX_ksImsR = _dx_native("ksImsR")
+    dconv3D_deltaX_ksImsR_SGM = _dx_native("ksImsR_SGM")
+    dconv3D_deltaX_ksImsR_texture = _dx_native("ksImsR_texture")
+    dconv3D_deltaX_ksImsR_texture_SGM = _dx_native("ksImsR_texture_SGM")
+    dconv3D_deltaX_ksIms2R = _dx_native("ksIms2R")
+    dconv3D_deltaX_ksIms2R_SGM = _dx_native("ksIms2R_SGM")
+    dconv3D_deltaX_ksIms2R_texture = _dx_native("ksIms2R_texture")
+    dconv3D_deltaX_ksIms2R_texture_SGM = _dx_native("ksIms2R_texture_SGM")
+    dconv3D_deltaX_crossAdd = _dx_native("crossAdd")
+    dconv3D_deltaX_crossAdd_SGM = _dx_native("crossAdd_SGM")
 
-_add_ks_methods()
+    # bias row fused (no counterpart in the Java class): (…unbiased arguments…, dBias, width)
+    @staticmethod
+    def dconv3D_deltaX_s1_biased(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw,
+                                 dBias, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_s1_biased(s, n, _p(d_deltaY), OH, OW, _p(dW), FH, FW, _p(d_deltaX), IH, IW, N, IC,
+                                                    OC, ph, pw, _p(dBias), width), "dconv3D_deltaX_s1_biased")
+
+    @staticmethod
+    def dconv3D_deltaX_ksImsR_biased(streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, sh, sw,
+                                     ph, pw, dBias, width):
+        s, n = _streams(streamArray, length)
+        _check(load().cu32_dconv3D_deltaX_ksImsR_biased(s, n, _p(d_deltaY), OH, OW, _p(dCW), FH, FW, _p(d_deltaX), IH, IW, N,
+                                                        IC, OC, sh, sw, ph, pw, _p(dBias), width), "dconv3D_deltaX_ksImsR_biased")
 
 
 class Cuda_dconv3D_deltaW:
@@ -677,34 +715,3 @@ class Cuda_dconv3D_deltaW:
     @staticmethod
     def Im2col_WinogradV2_SHW_s16_texture(streamArray, length, GridZ, OH_slice, OW_slice, c64, *a):
         return Cuda_dconv3D_deltaW._wino("s16_texture", (c64,), streamArray, length, GridZ, OH_slice, OW_slice, *a)
-
-
-def _add_scaled_methods():
-    """batchMatMul*_scaled: the batched natives with the attention block's 1/sqrt(d) scale fused into the store."""
-    def make(name):
-        def f(streamArray, length, dA, dB, dC, Batch, d0, d1, d2, d3, alpha):
-            s, n = _streams(streamArray, length)
-            _check(getattr(load(), "cu32_" + name)(s, n, _p(dA), _p(dB), _p(dC), Batch, d0, d1, d2, d3, float(alpha)), name)
-        return staticmethod(f)
-    for nm in ("batchMatMul_scaled", "batchMatMulT1_scaled", "batchMatMulT2_scaled"):
-        setattr(Cuda_batchMatMul, nm, make(nm))
-
-
-_add_scaled_methods()
-
-
-def _add_dx_biased_methods():
-    def s1(streamArray, length, d_deltaY, OH, OW, dW, FH, FW, d_deltaX, IH, IW, N, IC, OC, ph, pw, dBias, width):
-        s, n = _streams(streamArray, length)
-        _check(load().cu32_dconv3D_deltaX_s1_biased(s, n, _p(d_deltaY), OH, OW, _p(dW), FH, FW, _p(d_deltaX), IH, IW, N, IC,
-                                                    OC, ph, pw, _p(dBias), width), "dconv3D_deltaX_s1_biased")
-
-    def ks(streamArray, length, d_deltaY, OH, OW, dCW, FH, FW, d_deltaX, IH, IW, N, IC, OC, sh, sw, ph, pw, dBias, width):
-        s, n = _streams(streamArray, length)
-        _check(load().cu32_dconv3D_deltaX_ksImsR_biased(s, n, _p(d_deltaY), OH, OW, _p(dCW), FH, FW, _p(d_deltaX), IH, IW, N,
-                                                        IC, OC, sh, sw, ph, pw, _p(dBias), width), "dconv3D_deltaX_ksImsR_biased")
-    Cuda_dconv3D_deltaX.dconv3D_deltaX_s1_biased = staticmethod(s1)
-    Cuda_dconv3D_deltaX.dconv3D_deltaX_ksImsR_biased = staticmethod(ks)
-
-
-_add_dx_biased_methods()
