@@ -16,6 +16,9 @@
  *   deconv3D_deltaX_img2col (any stride)             same file, :109-152
  *   ks_remode / ks_remodev2 (filter workspace of the strided data gradient; GPU kernels, restated element by
  *   element)                                         dconv3D_dX_kernelSplit_remode_v1.cuh:28-66, _v2.cuh:31-66
+ *   linear2D (y = alpha*x + beta, the attention block's scale; a GPU kernel)   Cuda_function/type1_linear2D.cuh:40-58
+ *   deconv3d_deltaW_naive (the Java check loop of the weight gradient; PARITY UNPINNED, see below)
+ *                                                    ZUTIL-STD-1.2/src/z/util/math/vector/Tense.java:1276-1318
  *   linear_dual2D_row (the bias-row add the engine applies right after matMul / conv3D;
  *   a GPU kernel, restated element by element)        Cuda_function/Cuda_function/type1_linear_dual2D_row.cuh:41-70
  * Loop order and accumulation type follow the reference exactly (k outermost, FP32 "+=" into
@@ -28,6 +31,9 @@
  *
  * Pinning status: pinned against the reference's own routines compiled here (see above) and
  * against hand-computed known answers in tests/golden/; the reference ships no golden vectors.
+ * Exception - parity unpinned: the weight-gradient loop.  The reference publishes no CUDA source for
+ * Cuda_dconv3D_deltaW and its only CPU statement of it is Java, which cannot be run here; the restatement is checked
+ * against the FP64 version, and that against the pinned forward-convolution oracle (tests/test_deltaw.py).
  */
 #include <math.h>
 #include <stddef.h>
