@@ -23,6 +23,10 @@ static std::atomic<int> g_kc{2};
 static std::atomic<int> g_kc_fast{4};
 static std::atomic<int> g_tile{-1};
 static std::atomic<int> g_l2hint{0};
+static std::atomic<int> g_ring_raw{0};        // 0 = chosen per call (see choose_rings)
+static std::atomic<int> g_ring_lo{0};
+static std::atomic<int> g_store_bufs{0};
+static std::atomic<int> g_arrive_release{0};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -31,6 +35,9 @@ static void load_env_once() {
     if (const char* s = std::getenv("DRAGON_CU32_KC_FAST")) { int v = std::atoi(s); if (v >= 1) g_kc_fast = v; }
     if (const char* s = std::getenv("DRAGON_CU32_L2HINT")) { int v = std::atoi(s); if (v >= 0 && v <= 2) g_l2hint = v; }
     if (const char* s = std::getenv("DRAGON_CU32_TILE")) { int v = std::atoi(s); if (v >= -1 && v < TILE_COUNT) g_tile = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_RING_RAW")) { int v = std::atoi(s); if (v >= 0 && v <= 8) g_ring_raw = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_RING_LO")) { int v = std::atoi(s); if (v >= 0 && v <= 8) g_ring_lo = v; }
+    if (const char* s = std::getenv("DRAGON_CU32_STORE_BUFS")) { int v = std::atoi(s); if (v >= 0 && v <= 2) g_store_bufs = v; }
   });
 }
 
@@ -99,18 +106,6 @@ static int make_map3(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1
   return r == CUDA_SUCCESS ? CU32_OK : CU32_E_TENSORMAP;
 }
 
-#ifdef DRAGON_TRACE
-static long long* g_trace_buf = nullptr;
-extern "C" __attribute__((visibility("default"))) int cu32_trace_enable(void) {
-  if (!g_trace_buf && cudaMalloc(&g_trace_buf, sizeof(long long) * 24 * 256) != cudaSuccess) return -1;
-  return static_cast<int>(cudaMemset(g_trace_buf, 0, sizeof(long long) * 24 * 256));
-}
-extern "C" __attribute__((visibility("default"))) int cu32_trace_read(long long* out) {
-  cudaDeviceSynchronize();
-  return static_cast<int>(cudaMemcpy(out, g_trace_buf, sizeof(long long) * 24 * 256, cudaMemcpyDeviceToHost));
-}
-#endif
-
 // One contraction, BLAS letters: C[M,N] = A * B over K.
 struct GemmCall {
   const float* A; const float* B; float* C; float* Cbuf;
@@ -130,27 +125,37 @@ struct GemmCall {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Tile choice: estimated time = waves over the 148 SMs x work per CTA / measured per-CTA
+// Tile choice: estimated time = waves over the SMs x work per CTA / measured per-CTA
 // rate.  The rates are FP32-accurate TFLOP/s measured at 8192^3 on a B200 with every SM
 // busy; padded rows and columns count as work, so narrow outputs pick narrow tiles and
 // small problems pick small tiles.
 static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
   if (forced >= 0) return forced;
-  // the TMEM-operand tiles (last three) are not chosen automatically yet
   // measured matMul 8192^3 rates per tile shape, TFLOP/s (order of the TileCfg enum)
-  static const double rate[TILE_COUNT] = {123.0, 180.0, 200.0, 228.0, 278.0, 0.0, 0.0, 0.0, 140.0};
+  static const double rate[TILE_COUNT] = {123.0, 180.0, 200.0, 228.0, 278.0, 140.0};
+  const double sms = static_cast<double>(device_sm_count());
   int best = TILE_1x128;
   double best_t = 1e300;
   for (int t = 0; t < TILE_COUNT; ++t) {
-    if (rate[t] <= 0.0) continue;
     const int ctas = tile_ctas(t), bn = tile_bn(t);
     const double n_cta = static_cast<double>((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn) * ctas * z;
-    const double waves = static_cast<double>(static_cast<long long>((n_cta + 147.0) / 148.0));
+    const double waves = static_cast<double>(static_cast<long long>((n_cta + sms - 1.0) / sms));
     const double time = waves * (128.0 * bn) / rate[t];
     if (time < best_t) { best_t = time; best = t; }
   }
   return best;
+}
+
+// Ring lengths for a launch (see GemmParams): explicit tuning values win, otherwise 0 = the kernel
+// configuration's balanced default.
+static void choose_rings(GemmParams* p) {
+  p->ring_raw = g_ring_raw.load();
+  p->ring_lo = g_ring_lo.load();
+  p->store_bufs = g_store_bufs.load();
+  if (p->ring_raw > 0 && p->ring_lo == 0) p->ring_lo = p->ring_raw;
+  if (p->ring_raw == 0) p->ring_lo = 0;
+  p->arrive_release = g_arrive_release.load();
 }
 
 static int run_gemm(const GemmCall& c) {
@@ -169,7 +174,6 @@ static int run_gemm(const GemmCall& c) {
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
-  if (!c.x3 && tile_is_ts(tile)) tile = TILE_1x256;   // the TMEM-operand tiles are FP32-accurate only
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -198,6 +202,7 @@ static int run_gemm(const GemmCall& c) {
   p.tiles_n = (c.n_store + bn - 1) / bn;
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
+  choose_rings(&p);
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;   // the bias is applied on the vector store paths only
@@ -216,9 +221,6 @@ static int run_gemm(const GemmCall& c) {
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
 
-#ifdef DRAGON_TRACE
-  p.trace = g_trace_buf;
-#endif
   // Batches (or split-K slices) are folded into the kernel's tile index.
   const int zs = c.gz > 1 ? c.gz : c.batch;
   if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
@@ -344,6 +346,11 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
       sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
     return CU32_E_DIM;
   if ((IC & 3) || !aligned16(dX) || !aligned16(dW)) return CU32_E_ALIGN;
+  // forward entry points: the output extents must be the ones the geometry gives (the data-gradient callers
+  // have derived their padding from the extents already)
+  if (!flip && (IH + 2 * ph < FH || IW + 2 * pw < FW || OH != (IH + 2 * ph - FH) / sh + 1 ||
+                OW != (IW + 2 * pw - FW) / sw + 1))
+    return CU32_E_DIM;
   if (dBias) {
     if (width <= 0 || width > OC) return CU32_E_DIM;
     if (!aligned16(dBias) || (OC & 3)) return CU32_E_ALIGN;
@@ -378,7 +385,6 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
     return CU32_E_GEOMETRY;
 
   int tile = pick_tile(GM, OC, 1);
-  if (!x3 && tile_is_ts(tile)) tile = TILE_1x256;
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -435,6 +441,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   p.tiles_n = (OC + bn - 1) / bn;
   p.gz = 1;
   p.kc = x3 ? g_kc.load() : g_kc_fast.load();
+  choose_rings(&p);
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(dY) && !(OC & 3)) ? 1 : 0;
   if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;
@@ -512,7 +519,7 @@ static int ks_remode_any(bool v2, int64_t stream, const float* dW, int FH, int F
   cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
   const long long n = static_cast<long long>(OC) * CFH * CFW * IC;
   long long bx = (n + 255) / 256;
-  if (bx > 148 * 8) bx = 148 * 8;
+  if (bx > device_sm_count() * 8) bx = device_sm_count() * 8;
   const dim3 grid(static_cast<unsigned>(bx), static_cast<unsigned>(sh * sw));
   if (v2) ks_remode_kernel<true><<<grid, 256, 0, st>>>(dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
   else    ks_remode_kernel<false><<<grid, 256, 0, st>>>(dW, FH, FW, dCW, CFH, CFW, OC, IC, sh, sw);
@@ -576,7 +583,6 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
         return CU32_E_GEOMETRY;
       const long long GM = static_cast<long long>(N) * U * V;
       int tile = pick_tile(GM, IC, 1);
-      if (tile_is_ts(tile)) tile = TILE_1x256;
       const int ctas = tile_ctas(tile), bn = tile_bn(tile);
       GemmParams p;
       std::memset(&p, 0, sizeof(p));
@@ -633,6 +639,7 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       p.tiles_n = (IC + bn - 1) / bn;
       p.gz = 1;
       p.kc = g_kc.load();
+      choose_rings(&p);
       p.vec4_ok = 1;
       p.tma_store = 0;
       p.conv_OW = V; p.conv_OH = U; p.conv_FW = CFW; p.conv_IC = OC;
@@ -695,7 +702,6 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
 
   const int zs = static_cast<int>(taps) * GridZ;
   int tile = pick_tile(OC, IC, zs);
-  if (tile_is_ts(tile)) tile = TILE_1x256;
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
@@ -729,6 +735,7 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
   p.gz = GridZ;
   p.ztaps = static_cast<int>(taps);
   p.kc = g_kc.load();
+  choose_rings(&p);
   p.vec4_ok = 1;
   p.tma_store = 0;   // a tap's columns end inside the row: register stores clip there
   p.conv_OW = OW; p.conv_OH = OH; p.conv_FW = FW; p.conv_IC = IC;
@@ -793,7 +800,7 @@ static int summary_any(int64_t stream, const float* dCbuf, float* dC, int part, 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream));
   const int threads = 256;
   long long blocks = (static_cast<long long>(sizeC) / 4 + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
   if (blocks < 1) blocks = 1;
   if (dBias)
     skbuf_summary_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, st>>>(dCbuf, dC, part, sizeC, dBias,
@@ -1208,6 +1215,9 @@ int cu32_matMulT1SK_noalloc(const int64_t* s, int n, int GZ, const float* A, con
   if (GZ < 1) return CU32_E_ARG;
   const long long need = static_cast<long long>(GZ - 1) * N * M;
   if (need > CU32_NOALLOC_SCRATCH_FLOATS) return CU32_E_SCRATCH;
+  // everything the two launches would refuse is refused before the first one writes into C
+  if (!A || !B || !C) return CU32_E_NULL;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || (N & 3) || (M & 3)) return CU32_E_ALIGN;
   cudaError_t e;
   float* scratch = splitk_scratch_ptr(&e);
   if (!scratch) return static_cast<int>(e);
@@ -1218,6 +1228,35 @@ int cu32_matMulT1SK_noalloc(const int64_t* s, int n, int GZ, const float* A, con
   return cu32_SKbuf_summary(s[0], scratch, C, GZ - 1, N * M);
 }
 
+// ---- self-test of the bounded waits
+}  // extern "C"
+namespace dragon {
+// One warp waits on an mbarrier that nobody ever arrives at, with a short limit; the wait runs out, the
+// kernel records its give-up code in the status word exactly as the contraction kernel's roles do, and
+// returns normally.
+__global__ void selftest_wait_kernel(int* status, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ volatile int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool done = ptx::mbar_wait(ptx::smem_u32(&bar), 0u, &abort_flag, limit_cycles);
+  if (!done && threadIdx.x == 0) atomicCAS(status, 0, (ROLE_SELFTEST << 24) | (1 << 16) | 42);
+}
+}  // namespace dragon
+extern "C" {
+int cu32_selftest_wait_giveup(int64_t stream, long long limit_cycles) {
+  if (limit_cycles < 1 || limit_cycles > 100000000LL) return CU32_E_ARG;   // at most ~50 ms
+  cudaError_t e;
+  int* status = status_word_ptr(&e);
+  if (!status) return static_cast<int>(e);
+  selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(static_cast<intptr_t>(stream))>>>(status, limit_cycles);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
 // ---- library control
 int cu32_tune(const char* key, int value) {
   load_env_once();
@@ -1226,6 +1265,10 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "kc_fast")) { if (value < 1) return CU32_E_ARG; g_kc_fast = value; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { if (value < -1 || value >= TILE_COUNT) return CU32_E_ARG; g_tile = value; return CU32_OK; }
   if (!std::strcmp(key, "l2hint")) { if (value < 0 || value > 2) return CU32_E_ARG; g_l2hint = value; return CU32_OK; }
+  if (!std::strcmp(key, "ring_raw")) { if (value < 0 || value > 8) return CU32_E_ARG; g_ring_raw = value; return CU32_OK; }
+  if (!std::strcmp(key, "ring_lo")) { if (value < 0 || value > 8) return CU32_E_ARG; g_ring_lo = value; return CU32_OK; }
+  if (!std::strcmp(key, "store_bufs")) { if (value < 0 || value > 2) return CU32_E_ARG; g_store_bufs = value; return CU32_OK; }
+  if (!std::strcmp(key, "arrive_release")) { g_arrive_release = value ? 1 : 0; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {
@@ -1235,6 +1278,10 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "kc_fast")) { *value = g_kc_fast; return CU32_OK; }
   if (!std::strcmp(key, "tile")) { *value = g_tile; return CU32_OK; }
   if (!std::strcmp(key, "l2hint")) { *value = g_l2hint; return CU32_OK; }
+  if (!std::strcmp(key, "ring_raw")) { *value = g_ring_raw; return CU32_OK; }
+  if (!std::strcmp(key, "ring_lo")) { *value = g_ring_lo; return CU32_OK; }
+  if (!std::strcmp(key, "store_bufs")) { *value = g_store_bufs; return CU32_OK; }
+  if (!std::strcmp(key, "arrive_release")) { *value = g_arrive_release; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_read_status(int* status) {

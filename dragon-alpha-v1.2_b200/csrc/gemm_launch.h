@@ -14,23 +14,31 @@ enum TileCfg : int {
   TILE_1x256 = 2,  // 128 x 256, one CTA
   TILE_2x128 = 3,  // 256 x 128, CTA pair
   TILE_2x256 = 4,  // 256 x 256, CTA pair
-  // "T" tiles feed the A operand to the tensor core through TMEM (FP32-accurate mode only)
-  TILE_2x192T = 5, // 256 x 192, CTA pair
-  TILE_1x64T = 6,  // 128 x 64, one CTA
-  TILE_1x128T = 7, // 128 x 128, one CTA
-  TILE_2x64 = 8,   // 256 x 64, CTA pair (narrow outputs: halves the MMA instructions per row)
-  TILE_COUNT = 9
+  TILE_2x64 = 5,   // 256 x 64, CTA pair (narrow outputs: halves the MMA instructions per row)
+  TILE_COUNT = 6
 };
 
-inline int tile_ctas(int cfg) { return (cfg == TILE_2x128 || cfg == TILE_2x256 || cfg == TILE_2x192T || cfg == TILE_2x64) ? 2 : 1; }
-inline bool tile_is_ts(int cfg) { return cfg >= TILE_2x192T && cfg <= TILE_1x128T; }
+inline int tile_ctas(int cfg) { return (cfg == TILE_2x128 || cfg == TILE_2x256 || cfg == TILE_2x64) ? 2 : 1; }
 inline int tile_bn(int cfg) {
   switch (cfg) {
-    case TILE_1x64: case TILE_1x64T: case TILE_2x64: return 64;
-    case TILE_1x128: case TILE_2x128: case TILE_1x128T: return 128;
-    case TILE_2x192T: return 192;
+    case TILE_1x64: case TILE_2x64: return 64;
+    case TILE_1x128: case TILE_2x128: return 128;
     default: return 256;
   }
+}
+// Bytes one k-block of the tile brings into a CTA (one slot of the raw ring, and of the lo ring).
+inline int tile_slot_bytes(int cfg) { return (128 + tile_bn(cfg) / tile_ctas(cfg)) * 32 * 4; }
+
+// Streaming multiprocessors of the current device (cached per device ordinal).
+inline int device_sm_count() {
+  static int cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+  int n = __atomic_load_n(&cache[dev & 63], __ATOMIC_ACQUIRE);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 1;
+  __atomic_store_n(&cache[dev & 63], n, __ATOMIC_RELEASE);
+  return n;
 }
 
 // Operand layouts.  "K" = the reduction axis is contiguous in memory, "N" = the
@@ -46,10 +54,6 @@ cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_
 //   NN + im2col : A[K][M], B = im2col walk over an NHWC image, K = output pixels (weight gradient; FP32-accurate only)
 cudaError_t launch_gemm_nn_im2col(int tile_cfg, const GemmParams& p, int grid_z, cudaStream_t stream);
 
-// Shared-memory bytes one stage of the given configuration uses (for reporting).
-int gemm_stage_bytes(int tile_cfg, bool x3);
-int gemm_stages(int tile_cfg, bool x3);
-
 template <class Cfg>
 cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   auto kernel = gemm_tf32_kernel<Cfg>;
@@ -62,13 +66,14 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   int units = __atomic_load_n(&resident_units[dev & 63], __ATOMIC_ACQUIRE);
   if (units == 0) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::MAX_DYN_SMEM);
     if (e != cudaSuccess) return e;
+    const int sms = device_sm_count();
     if (Cfg::CTAS == 2) {
       cudaLaunchConfig_t q = {};
-      q.gridDim = dim3(2 * 148, 1, 1);
+      q.gridDim = dim3(2 * sms, 1, 1);
       q.blockDim = dim3(Cfg::THREADS, 1, 1);
-      q.dynamicSmemBytes = Cfg::DYN_SMEM;
+      q.dynamicSmemBytes = Cfg::MAX_DYN_SMEM;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
       qa[0].val.clusterDim.x = 2;
@@ -79,10 +84,8 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
       e = cudaOccupancyMaxActiveClusters(&units, kernel, &q);
       if (e != cudaSuccess) return e;
     } else {
-      int sms = 0, per_sm = 0;
-      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      if (e != cudaSuccess) return e;
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Cfg::THREADS, Cfg::DYN_SMEM);
+      int per_sm = 0;
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, Cfg::THREADS, Cfg::MAX_DYN_SMEM);
       if (e != cudaSuccess) return e;
       units = sms * per_sm;
     }
@@ -93,10 +96,17 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   const long long grid_units = total_tiles < units ? total_tiles : units;
   GemmParams q = p;
   q.zcount = grid_z;
+  // Rings: 0 = the balanced default (as many raw + lo pairs as fit beside one staging tile per drain warp).
+  if (q.ring_raw == 0) { q.ring_raw = Cfg::STAGES; q.ring_lo = Cfg::STAGES; }
+  if (q.store_bufs == 0) q.store_bufs = 1;
+  if (!Cfg::X3) q.ring_lo = q.ring_raw;
+  if (q.ring_raw < 2 || q.ring_raw > Cfg::MAX_RING || q.ring_lo < 1 || q.ring_lo > q.ring_raw ||
+      q.store_bufs < 1 || q.store_bufs > 2 || Cfg::dyn_smem(q.ring_raw, q.ring_lo, q.store_bufs) > Cfg::MAX_DYN_SMEM)
+    return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid_units) * Cfg::CTAS, 1, 1);
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
+  cfg.dynamicSmemBytes = Cfg::dyn_smem(q.ring_raw, q.ring_lo, q.store_bufs);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   cfg.numAttrs = 0;
@@ -119,9 +129,6 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
     case TILE_1x256: return launch_one<GemmCfg<256, 1, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
     case TILE_2x128: return launch_one<GemmCfg<128, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
     case TILE_2x256: return launch_one<GemmCfg<256, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream); \
-    case TILE_2x192T: return launch_one<GemmCfg<192, 2, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
-    case TILE_1x64T:  return launch_one<GemmCfg<64, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream);  \
-    case TILE_1x128T: return launch_one<GemmCfg<128, 1, A_MN, B_MN, true, IM2COL, true>>(p, grid_z, stream); \
     case TILE_2x64:  return launch_one<GemmCfg<64, 2, A_MN, B_MN, X3, IM2COL>>(p, grid_z, stream);  \
     default: return cudaErrorInvalidValue;                                                     \
   }

@@ -69,9 +69,14 @@ struct GemmParams {
   int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
   int l2_hints;         // load A with evict-last and B with evict-first L2 priority
   int* status;          // device word, 0 = ok; first give-up code otherwise
-#ifdef DRAGON_TRACE
-  long long* trace;     // 2 CTAs x 12 events x 256 timestamps (tracing builds only)
-#endif
+  // Shared-memory rings (sized by the host within the 227 KB a CTA may use).  A k-block's raw tiles
+  // occupy a slot of the raw ring from the TMA issue until its MMAs have completed; its lo tiles
+  // occupy a slot of the (shorter or equal) lo ring only from the split until then.  Memory-bound
+  // shapes trade lo slots for raw slots: more loads in flight against the HBM latency.
+  int ring_raw;         // raw slots, 2..8
+  int ring_lo;          // lo slots, 1..ring_raw (FP32-accurate mode only)
+  int store_bufs;       // 4 KB store-staging tiles per drain warp, 1 or 2
+  int arrive_release;   // debugging aid: remote mbarrier arrives carry a cluster-scope release
   // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
   // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
@@ -90,54 +95,39 @@ struct GemmParams {
   long long os_sn, os_su, os_sv;
 };
 
-#ifdef DRAGON_TRACE
-// Timeline instrumentation for pipeline studies: CTA 0 records clock64() at the hand-over
-// points of its first 256 k-blocks into GemmParams::trace.  Not compiled into the product.
-#define TRACE(ev, idx) do { if (p.trace && blockIdx.x < 2 && (idx) < 256u) p.trace[(blockIdx.x * 12 + (ev)) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(ev, idx) do { } while (0)
-#endif
+enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5, ROLE_SELFTEST = 7 };
 
-enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5 };
-
-template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false, bool TS_ = false>
+template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false>
 struct GemmCfg {
   static constexpr int BN = BN_, CTAS = CTAS_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, X3 = X3_, IM2COL = IM2COL_;
-  // TS: the A operand reaches the tensor core through TMEM instead of shared memory.
-  // The raw A tile is split by four warps straight into TMEM (hi and lo, 32 columns
-  // each per k-block, two slots), which removes A's hi/lo tiles and all of A's
-  // operand fetches from shared memory - the bandwidth that otherwise bounds the kernel.
-  static constexpr bool TS = TS_;
   static constexpr int BM = 128;            // rows of A (and TMEM lanes) per CTA
   static constexpr int BK = 32;             // one 128-byte swizzle row of FP32
   static constexpr int BN_CTA = BN / CTAS;  // B columns staged per CTA
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN_CTA * BK * 4;
-  static constexpr int HI_BYTES = A_BYTES + B_BYTES;   // bytes one k-block brings in by TMA
-  // stage layout   !TS: [A_hi][B_hi][A_lo][B_lo]      TS: [A_raw][B_hi][B_lo]
-  static constexpr int STAGE_BYTES = TS ? (A_BYTES + B_BYTES * (X3 ? 2 : 1)) : HI_BYTES * (X3 ? 2 : 1);
-  static constexpr int B_LO_OFFSET = TS ? B_BYTES : HI_BYTES;  // from B_hi to B_lo
-  static constexpr int SMEM_BUDGET = 192 * 1024;   // pipeline stages
-  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int STORE_STAGING = 8 * 4096;  // one 32x32 FP32 staging tile per drain warp
-  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + STORE_STAGING + 1024;  // +1024: manual alignment
-  static constexpr int A_TMEM_COL0 = 2 * BN;                    // TS: A slots follow the two chunk buffers
-  static constexpr int A_SLOT_COLS = 2 * BK;                    // hi (32 columns) + lo (32 columns)
-  static constexpr int TMEM_NEED = 2 * BN + (TS ? 2 * A_SLOT_COLS : 0);
+  static constexpr int HI_BYTES = A_BYTES + B_BYTES;   // bytes one k-block brings in by TMA: a raw slot [A][B]
+  // Shared memory: [raw ring][lo ring (FP32-accurate mode)][store staging]; the ring lengths are launch
+  // parameters.  MAX_DYN_SMEM leaves room for the static barriers inside the 227 KB a CTA may use.
+  static constexpr int MAX_DYN_SMEM = 226 * 1024;
+  static constexpr int MAX_RING = 8;
+  static constexpr int STAGING_TILE = 4096;   // one 32x32 FP32 piece
+  // the default, balanced rings: as many (raw + lo) pairs as fit beside one staging tile per drain warp
+  static constexpr int PAIR_BYTES = HI_BYTES * (X3 ? 2 : 1);
+  static constexpr int STAGES_RAW = (MAX_DYN_SMEM - 1024 - 8 * STAGING_TILE) / PAIR_BYTES;
+  static constexpr int STAGES = STAGES_RAW > MAX_RING ? MAX_RING : STAGES_RAW;
+  static constexpr int TMEM_NEED = 2 * BN;
   static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
                                    : TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int THREADS = 512;
-  static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;      // TS: warps 2,3 split B, warps 4..7 split A
+  static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;
   static constexpr int DRAIN_WARP0 = 8, DRAIN_WARPS = 8;
   static constexpr int CW = BN / 2;          // columns per drain warp
   static constexpr bool REALLOC = CW > 64;   // drainers need > 128 registers
-  // register budgets after reallocation (256 threads each side, 64 K registers per SM):
-  // the TMEM-writing splitters hold 64 split values, so they keep more than the plain ones
-  static constexpr int REGS_MOVERS = TS ? 96 : 72;
-  static constexpr int REGS_DRAINERS = TS ? 160 : 184;
-  static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "BN");
+  // register budgets after reallocation (256 threads each side, 64 K registers per SM)
+  static constexpr int REGS_MOVERS = 72;
+  static constexpr int REGS_DRAINERS = 184;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "BN");
   static_assert(TMEM_NEED <= 512, "TMEM");
   static_assert(STAGES >= 2, "stages");
   // IM2COL with a K-major A: the A tile is an im2col walk over the image (convolution, data gradient).
@@ -146,7 +136,11 @@ struct GemmCfg {
   static constexpr bool IM2COL_A = IM2COL && !A_MN;
   static constexpr bool IM2COL_B = IM2COL && A_MN;
   static_assert(!IM2COL_B || B_MN, "an im2col B tile is MN-major (channels contiguous)");
-  static_assert(!TS || X3, "TS is only built for the FP32-accurate mode");
+
+  // Dynamic shared memory a launch with the given rings needs (1024: manual alignment of the tiles).
+  static constexpr int dyn_smem(int ring_raw, int ring_lo, int store_bufs) {
+    return 1024 + ring_raw * HI_BYTES + (X3 ? ring_lo * HI_BYTES : 0) + 8 * store_bufs * STAGING_TILE;
+  }
 };
 
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
@@ -179,13 +173,9 @@ struct TileWork {
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
   using namespace ptx;
-  constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, STAGES = Cfg::STAGES, CW = Cfg::CW;
+  constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, CW = Cfg::CW;
   constexpr bool X3 = Cfg::X3;
   constexpr bool RELAY = X3 || CTAS == 2;  // MMA waits on the splitters' barrier
-  // Shared-memory split: the tensor core drops the low 13 mantissa bits of an FP32 operand
-  // by itself, so the tile as TMA wrote it already is the "hi" operand (hi = trunc(x)) and
-  // only lo = tf32(x - trunc(x)) has to be written.
-  constexpr bool TRUNC_HI = X3 && !Cfg::TS;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full_tma[8];
@@ -194,7 +184,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   __shared__ __align__(8) uint64_t bar_empty[8];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
-  __shared__ __align__(8) uint64_t bar_a_empty[2];   // TS: the MMAs have read A slot i
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
 
@@ -202,7 +191,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   const int lane = threadIdx.x & 31;
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
 
-  const uint32_t tiles_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  // ring geometry (launch parameters, uniform over the grid)
+  const uint32_t R = static_cast<uint32_t>(p.ring_raw);
+  const uint32_t L = X3 ? static_cast<uint32_t>(p.ring_lo) : R;
+  const uint32_t raw_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t lo_base = raw_base + R * Cfg::HI_BYTES;
+  const uint32_t stg_base = lo_base + (X3 ? L * Cfg::HI_BYTES : 0u);
 
   // ---- persistent tile loop: this CTA (pair) takes tiles first, first + step, ...
   // Tile ids run over (z, m-group, n, m-in-group); concurrently resident tiles are
@@ -273,7 +267,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[b]), Cfg::DRAIN_WARPS * CTAS);
-      mbar_init(smem_u32(&bar_a_empty[b]), 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&p.tmA);
@@ -293,6 +286,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   auto leader_addr = [&](const uint64_t* bar) -> uint32_t {
     return (CTAS == 2) ? mapa(smem_u32(bar), 0u) : smem_u32(bar);
   };
+  auto arrive_remote = [&](uint32_t bar) {
+    if (p.arrive_release) mbar_arrive_cluster_release(bar);
+    else mbar_arrive_cluster(bar);
+  };
 
   // Warps 0..7 (two warpgroups) run the data-movement roles on a small register
   // budget; warps 8..15 hold the FP32 accumulators.  With 256-column tiles the
@@ -308,7 +305,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     {
       const bool leader = lane == 0;
       uint32_t it = 0;  // k-blocks issued so far, over all tiles
-      uint32_t s = 0, ph = 0;  // stage = it % STAGES and its phase parity, carried as counters
+      uint32_t s = 0, ph = 0;  // raw slot = it % R and its phase parity, carried as counters
       bool alive = true;
       // Tiles are walked in groups of 8 row-tiles across all column-tiles, so an A panel is
       // re-used by every column-tile of the sweep while B streams through once per group:
@@ -318,7 +315,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
-        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == STAGES) ? 0u : s + 1, ph ^= (s == 0)) {
+        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == R) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
             if (leader) give_up(ROLE_TMA, s, i);
             alive = false;
@@ -326,7 +323,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           }
           const uint32_t full = smem_u32(&bar_full_tma[s]);
           int k0 = (w.kb0 + i) * Cfg::BK;
-          const uint32_t a_dst = tiles_base + s * Cfg::STAGE_BYTES;
+          const uint32_t a_dst = raw_base + s * Cfg::HI_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           // im2col coordinates: k-block -> (filter tap, block of 32 channels inside the tap);
           // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
@@ -357,7 +354,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           }
           // one single-thread region for all copies of the k-block
           if (elect_one()) {
-            TRACE(0, it);
             mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
             if (Cfg::IM2COL_A) {
               tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
@@ -400,13 +396,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       }
       if (leader && abort_flag) {
         // Let copies already in flight land before shared memory is released:
-        // wait (bounded) for the barrier of every stage still outstanding.
-        const uint32_t lo = it > static_cast<uint32_t>(STAGES) ? it - STAGES : 0u;
-        for (uint32_t i = lo; i < it; ++i) {
-          const int s = i % STAGES;
-          const uint32_t ph = (i / STAGES) & 1;
+        // wait (bounded) for the barrier of every slot still outstanding.
+        const uint32_t first = it > R ? it - R : 0u;
+        for (uint32_t i = first; i < it; ++i) {
+          const uint32_t slot = i % R;
+          const uint32_t par = (i / R) & 1u;
           const long long t0 = clock64();
-          while (!mbar_try_wait(smem_u32(&bar_full_tma[s]), ph) && clock64() - t0 < 20000000LL) {
+          while (!mbar_try_wait(smem_u32(&bar_full_tma[slot]), par) && clock64() - t0 < 20000000LL) {
           }
         }
       }
@@ -419,7 +415,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     // time it waits for operands.
     if (rank == 0) {
       const bool leader = lane == 0;   // the one thread that issues (and whose commits track) the MMAs
-      constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN && !Cfg::TS, Cfg::B_MN);
+      constexpr uint32_t idesc = make_idesc_tf32(Cfg::BM * CTAS, BN, Cfg::A_MN, Cfg::B_MN);
       constexpr uint32_t A_LBO = Cfg::A_MN ? 4096u : 16u;
       constexpr uint32_t B_LBO = Cfg::B_MN ? 4096u : 16u;
       constexpr uint32_t A_SBO = Cfg::A_MN ? 512u : 1024u;
@@ -433,7 +429,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       // being re-derived with divisions every k-block.
       uint32_t it = 0;    // k-blocks consumed so far, over all tiles
       uint32_t ch = 0;    // chunks started so far: TMEM buffer = ch & 1
-      uint32_t s = 0, ph = 0;   // pipeline stage and its phase parity
+      uint32_t s = 0, ph = 0;   // raw slot and its phase parity
+      uint32_t l = 0;     // lo slot = it % L
       uint32_t kk = 0;    // k-blocks already in the current chunk
       bool alive = true;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
@@ -450,13 +447,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             alive = false;
             break;
           }
-          if (leader) TRACE(6, it);
           if (CTAS == 2 && !mbar_wait<true>(smem_u32(&bar_full_split_peer[0]) + s * 8u, ph, &abort_flag)) {
             if (leader) give_up(ROLE_MMA, 50 + s, i);
             alive = false;
             break;
           }
-          if (leader) TRACE(3, it);
           const uint32_t buf = ch & 1u;
           if (chunk_start) {
             // the n-th use of a buffer waits for the (n-1)-th drain; the first use passes
@@ -467,8 +462,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             }
           }
           tc_fence_after();
-          const uint32_t a_hi = tiles_base + s * Cfg::STAGE_BYTES;
+          const uint32_t a_hi = raw_base + s * Cfg::HI_BYTES;
           const uint32_t b_hi = a_hi + Cfg::A_BYTES;
+          const uint32_t a_lo = lo_base + l * Cfg::HI_BYTES;
+          const uint32_t b_lo = a_lo + Cfg::A_BYTES;
           const uint32_t d = tmem_base + buf * BN;
           // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
           // instruction, an error of up to one ulp of the *accumulator*.  Issuing all the
@@ -484,48 +481,30 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             constexpr uint64_t A_STEP = A_KSTEP >> 4, B_STEP = B_KSTEP >> 4;
             const uint64_t db_hi0 = make_smem_desc(b_hi, B_LBO, B_SBO, B_LT);
             const uint32_t first = chunk_start ? 0u : 1u;
-            if (Cfg::TS) {
-              const uint32_t slot = it & 1u;
-              const uint32_t ta_hi = tmem_base + Cfg::A_TMEM_COL0 + slot * Cfg::A_SLOT_COLS;
-              const uint32_t ta_lo = ta_hi + Cfg::BK;
-              const uint64_t db_lo0 = make_smem_desc(b_hi + Cfg::B_LO_OFFSET, B_LBO, B_SBO, B_LT);
+            const uint64_t da_hi0 = make_smem_desc(a_hi, A_LBO, A_SBO, A_LT);
+            if (X3) {
+              const uint64_t da_lo0 = make_smem_desc(a_lo, A_LBO, A_SBO, A_LT);
+              const uint64_t db_lo0 = make_smem_desc(b_lo, B_LBO, B_SBO, B_LT);
 #pragma unroll
               for (int j = 0; j < Cfg::BK / 8; ++j) {
-                umma_tf32_ts<CTAS>(d, ta_lo + j * 8, db_hi0 + j * B_STEP, idesc, j == 0 ? first : 1u);
-                umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_lo0 + j * B_STEP, idesc, 1u);
+                umma_tf32<CTAS>(d, da_lo0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, j == 0 ? first : 1u);
+                umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_lo0 + j * B_STEP, idesc, 1u);
               }
-#pragma unroll
-              for (int j = 0; j < Cfg::BK / 8; ++j)
-                umma_tf32_ts<CTAS>(d, ta_hi + j * 8, db_hi0 + j * B_STEP, idesc, 1u);
-              if (CTAS == 2) umma_commit_pair(smem_u32(&bar_a_empty[slot]));
-              else umma_commit<CTAS>(smem_u32(&bar_a_empty[slot]));
-            } else {
-              const uint64_t da_hi0 = make_smem_desc(a_hi, A_LBO, A_SBO, A_LT);
-              if (X3) {
-                const uint64_t da_lo0 = make_smem_desc(a_hi + Cfg::HI_BYTES, A_LBO, A_SBO, A_LT);
-                const uint64_t db_lo0 = make_smem_desc(b_hi + Cfg::HI_BYTES, B_LBO, B_SBO, B_LT);
-#pragma unroll
-                for (int j = 0; j < Cfg::BK / 8; ++j) {
-                  umma_tf32<CTAS>(d, da_lo0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, j == 0 ? first : 1u);
-                  umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_lo0 + j * B_STEP, idesc, 1u);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < Cfg::BK / 8; ++j)
-                umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, (!X3 && j == 0) ? first : 1u);
             }
-            TRACE(4, it);
-            // The stage may be refilled once these MMAs have read it.
+#pragma unroll
+            for (int j = 0; j < Cfg::BK / 8; ++j)
+              umma_tf32<CTAS>(d, da_hi0 + j * A_STEP, db_hi0 + j * B_STEP, idesc, (!X3 && j == 0) ? first : 1u);
+            // The raw slot (and with it the lo slot) may be refilled once these MMAs have read it.
             if (CTAS == 2) umma_commit_pair(smem_u32(&bar_empty[0]) + s * 8u);
             else umma_commit<CTAS>(smem_u32(&bar_empty[0]) + s * 8u);
             if (chunk_end) {
               if (CTAS == 2) umma_commit_pair(smem_u32(&bar_tmem_full[0]) + buf * 8u);
               else umma_commit<CTAS>(smem_u32(&bar_tmem_full[0]) + buf * 8u);
             }
-            if (!Cfg::TS) TRACE(7, it);
           }
           __syncwarp();
-          if (++s == static_cast<uint32_t>(STAGES)) { s = 0; ph ^= 1u; }
+          if (++s == R) { s = 0; ph ^= 1u; }
+          if (++l == L) l = 0;
           if (chunk_end) ++ch;
         }
       }
@@ -533,74 +512,40 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   } else {
     // ------------------------------------------------------------ splitters
     if (RELAY) {
-      const bool a_splitter = Cfg::TS && warp >= 4;   // TS: warps 4..7 own TMEM lane quarters 0..3
-      // shared-memory split: which 16-byte vectors of the stage this thread handles
-      const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;   // TS: only warps 2,3 (0..63) use it
-      constexpr int NST = Cfg::TS ? 64 : Cfg::SPLIT_WARPS * 32;
-      constexpr int VEC0 = Cfg::TS ? Cfg::A_BYTES / 16 : 0;           // TS: only the B tile
+      // which 16-byte vectors of the slot this thread handles
+      const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;
+      constexpr int NST = Cfg::SPLIT_WARPS * 32;
       constexpr int NVEC = Cfg::HI_BYTES / 16;
-      constexpr int LO_OFF = Cfg::TS ? Cfg::B_LO_OFFSET : Cfg::HI_BYTES;
       uint32_t it = 0;
-      uint32_t s = 0, ph = 0;  // stage = it % STAGES and its phase parity, carried as counters
+      uint32_t s = 0, ph = 0;     // raw slot = it % R and its phase parity, carried as counters
+      uint32_t l = 0;             // lo slot = it % L
+      uint32_t sp = 0, php = 0;   // raw slot and phase parity of k-block it - L, the previous user of lo slot l
       bool alive = true;
       for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
         const TileWork w = decode(t);
-        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == STAGES) ? 0u : s + 1, ph ^= (s == 0)) {
+        for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == R) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
             if (lane == 0) give_up(ROLE_SPLIT, s, i);
             alive = false;
             break;
           }
-          if (!Cfg::TS && warp == 2 && lane == 0) TRACE(1, it);
-          if (Cfg::TS && warp == 4 && lane == 0) TRACE(6, it);
-          const uint32_t hi_base = tiles_base + s * Cfg::STAGE_BYTES;
-          if (a_splitter) {
-            // This thread owns row (quarter*32 + lane) of the A tile = its TMEM lane.
-            const uint32_t slot = it & 1u;
-            if (!mbar_wait(smem_u32(&bar_a_empty[slot]), ((it >> 1) & 1u) ^ 1u, &abort_flag)) {
-              if (lane == 0) give_up(ROLE_SPLIT, 100 + static_cast<int>(slot), i);
+          if (X3 && L != R && it >= L) {
+            // The lo slot is free once the MMAs of k-block it - L have completed, which is what frees
+            // that k-block's raw slot: wait on its "empty" barrier.  (With L == R that is this raw slot's
+            // own previous use, which the producer has waited for already.)  No later phase of that
+            // barrier can complete before this k-block has been split, so the parity is unambiguous.
+            if (!mbar_wait(smem_u32(&bar_empty[sp]), php, &abort_flag)) {
+              if (lane == 0) give_up(ROLE_SPLIT, 100 + sp, i);
               alive = false;
               break;
             }
-            tc_fence_after();
-            const int qd = warp & 3;
-            float hi[32], lo[32];
-            if (Cfg::A_MN) {
-              // A tile = 4 slabs of [32 k][32 m] floats, 32-byte-unit swizzle; this lane reads
-              // its column m = lane of slab qd, one element per k-row.
-              const uint32_t slab = hi_base + qd * 4096;
-#pragma unroll
-              for (int k = 0; k < 32; ++k) {
-                float x;
-                const uint32_t addr = slab + k * 128 + ((((lane >> 3) ^ (k & 3)) << 5) | ((lane & 7) << 2));
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(addr));
-                hi[k] = rn_tf32(x);
-                lo[k] = rn_tf32(x - hi[k]);
-              }
-            } else {
-              // A tile = [128 rows][32 k] floats, 16-byte-unit swizzle: chunk c of row r sits
-              // at r*128 + ((c ^ (r & 7)) * 16).
-              const int r = qd * 32 + lane;
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const float4 x = lds128(hi_base + r * 128 + ((c ^ (r & 7)) * 16));
-                hi[c * 4 + 0] = rn_tf32(x.x); lo[c * 4 + 0] = rn_tf32(x.x - hi[c * 4 + 0]);
-                hi[c * 4 + 1] = rn_tf32(x.y); lo[c * 4 + 1] = rn_tf32(x.y - hi[c * 4 + 1]);
-                hi[c * 4 + 2] = rn_tf32(x.z); lo[c * 4 + 2] = rn_tf32(x.z - hi[c * 4 + 2]);
-                hi[c * 4 + 3] = rn_tf32(x.w); lo[c * 4 + 3] = rn_tf32(x.w - hi[c * 4 + 3]);
-              }
-            }
-            const uint32_t ta = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + Cfg::A_TMEM_COL0 +
-                                slot * Cfg::A_SLOT_COLS;
-            if (warp == 4 && lane == 0) TRACE(1, it);
-            tmem_st_32x32(ta, hi);
-            tmem_st_32x32(ta + Cfg::BK, lo);
-            tmem_wait_st();
-            if (warp == 4 && lane == 0) TRACE(2, it);
-            tc_fence_before();
-          } else if (TRUNC_HI) {
-            // lo = tf32(x - trunc(x)); x itself stays where TMA put it.  The loads of the
-            // next group of four vectors are in flight while this group is converted and stored.
+          }
+          const uint32_t hi_base = raw_base + s * Cfg::HI_BYTES;
+          const uint32_t lo_slot = lo_base + l * Cfg::HI_BYTES;
+          if (X3) {
+            // lo = tf32(x - trunc(x)); x itself stays where TMA put it (the tensor core drops the low
+            // 13 mantissa bits of an FP32 operand by itself, so the raw tile already is the hi operand).
+            // The loads of the next group of vectors are in flight while this group is converted and stored.
             constexpr int PER = (NVEC + NST - 1) / NST;
             constexpr int G = 3;
             float4 x[2][G];
@@ -622,39 +567,27 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
                 const int v = st + (b + u) * NST;
                 if (b + u < PER && v < NVEC) {
                   const float4 xv = x[cur][u];
-                  float4 l;
-                  l.x = rn_tf32(xv.x - trunc_tf32(xv.x)); l.y = rn_tf32(xv.y - trunc_tf32(xv.y));
-                  l.z = rn_tf32(xv.z - trunc_tf32(xv.z)); l.w = rn_tf32(xv.w - trunc_tf32(xv.w));
-                  sts128(hi_base + v * 16 + LO_OFF, l);
+                  float4 lv;
+                  lv.x = rn_tf32(xv.x - trunc_tf32(xv.x)); lv.y = rn_tf32(xv.y - trunc_tf32(xv.y));
+                  lv.z = rn_tf32(xv.z - trunc_tf32(xv.z)); lv.w = rn_tf32(xv.w - trunc_tf32(xv.w));
+                  sts128(lo_slot + v * 16, lv);
                 }
               }
             }
             // the tensor core reads these tiles through the async proxy: without this fence a
             // store can still be in flight when the MMA that the arrive below releases reads it
             fence_proxy_async_smem();
-          } else if (X3) {
-#pragma unroll 4
-            for (int v = VEC0 + st; v < NVEC; v += NST) {
-              const uint32_t addr = hi_base + v * 16;
-              const float4 x = lds128(addr);
-              float4 h, l;
-              h.x = rn_tf32(x.x); h.y = rn_tf32(x.y); h.z = rn_tf32(x.z); h.w = rn_tf32(x.w);
-              l.x = rn_tf32(x.x - h.x); l.y = rn_tf32(x.y - h.y);
-              l.z = rn_tf32(x.z - h.z); l.w = rn_tf32(x.w - h.w);
-              sts128(addr, h);
-              sts128(addr + LO_OFF, l);
-            }
-            fence_proxy_async_smem();
           }
           __syncwarp();
-          if (!Cfg::TS && warp == 2 && lane == 0) TRACE(2, it);
-          if (Cfg::TS && warp == 4 && lane == 0) TRACE(7, it);
           if (lane == 0) {
             if (CTAS == 2 && rank != 0)
-              mbar_arrive_cluster(leader_addr(&bar_full_split_peer[s]));
+              arrive_remote(leader_addr(&bar_full_split_peer[s]));
             else
               mbar_arrive(smem_u32(&bar_full_split[s]));
           }
+          if (++l == L) l = 0;
+          // (sp, php) follow k-block (it + 1) - L: it sits at raw slot 0, phase 0 when it + 1 == L
+          if (it + 1 > L && ++sp == R) { sp = 0; php ^= 1u; }
         }
       }
     }
@@ -665,6 +598,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     const int q = warp & 3;                              // TMEM lane quarter this warp may read
     const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
     uint32_t ch = 0;                                     // chunks drained so far, over all tiles
+    uint32_t pc = 0;                                     // 32x32 pieces this warp has sent through TMA stores
+    const uint32_t sbufs = static_cast<uint32_t>(p.store_bufs);
+    const uint32_t stg0 = stg_base + (warp - Cfg::DRAIN_WARP0) * sbufs * Cfg::STAGING_TILE;
     bool alive = true;
     for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
       const TileWork w = decode(t);
@@ -681,7 +617,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           break;
         }
         tc_fence_after();
-        if (warp == 8 && lane == 0) TRACE(5, ch);
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                             static_cast<uint32_t>(buf * BN + h * CW);
         // 16-column pieces, the load of piece g+1 in flight while piece g is added; the
@@ -701,11 +636,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             __syncwarp();
             if (lane == 0) {
               if (CTAS == 2 && rank != 0)
-                mbar_arrive_cluster(leader_addr(&bar_tmem_empty[buf]));
+                arrive_remote(leader_addr(&bar_tmem_empty[buf]));
               else
                 mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
             }
-            if (warp == 8 && lane == 0) TRACE(8, ch);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc[g * 16 + j] += cur[j];
@@ -736,15 +670,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         // Each drain warp owns a 32-row x CW-column block.  32x32 pieces go through a
         // swizzled 4 KB staging tile (row r, 16-byte chunk c at r*128 + ((c ^ (r & 7)) * 16):
         // conflict-free for the row-per-lane writes) and leave as one TMA store each, which
-        // writes whole 128-byte row segments and clips rows >= M and columns >= N.
-        const uint32_t stg = tiles_base + STAGES * Cfg::STAGE_BYTES + (warp - Cfg::DRAIN_WARP0) * 4096;
+        // writes whole 128-byte row segments and clips rows >= M and columns >= N.  With two
+        // staging tiles per warp a piece is staged while the previous one is still being read.
         const CUtensorMap* cmap = w.to_cbuf ? &p.tmCbuf : &p.tmC;
 #pragma unroll
         for (int g = 0; g < CW / 32; ++g) {
           const int c0 = w.col0 + h * CW + g * 32;
           const int r0 = w.row0 + q * 32;
           if (c0 < p.N && r0 < p.M) {   // warp-uniform
-            if (lane == 0) tma_store_wait_read();   // the previous piece has left the staging tile
+            const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
+            if (lane == 0) {   // the store that last used this staging tile has read it
+              if (sbufs == 2u) tma_store_wait_read_1(); else tma_store_wait_read();
+            }
             __syncwarp();
 #pragma unroll
             for (int c = 0; c < 8; ++c)
@@ -757,6 +694,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               tma_store_3d(cmap, stg, c0, r0, w.zc);
               tma_store_commit();
             }
+            ++pc;
           }
         }
       } else if (p.os_on) {
@@ -764,7 +702,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         // describe.  Same staging tile as above, but the warp itself carries each 32x32 piece out: a
         // lane stages its own row, then eight lanes together write one row's 128 bytes, four rows per
         // instruction - whole 128-byte segments instead of 32 scattered 16-byte stores.
-        const uint32_t stg = tiles_base + STAGES * Cfg::STAGE_BYTES + (warp - Cfg::DRAIN_WARP0) * 4096;
+        const uint32_t stg = stg0;
         const int row = w.row0 + q * 32 + lane;
         long long row_off = -1;   // rows >= M have no pixel
         if (row < p.M) {
@@ -818,7 +756,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           }
         }
       }
-      if (warp == 8 && lane == 0) TRACE(9, ch - 1);
     }
     // stores still in flight read this CTA's shared memory: let them finish before exit
     if (lane == 0) tma_store_wait_all();

@@ -48,6 +48,14 @@ struct Streams {
 inline const float* cptr(jlong a) { return reinterpret_cast<const float*>(static_cast<intptr_t>(a)); }
 inline float* mptr(jlong a) { return reinterpret_cast<float*>(static_cast<intptr_t>(a)); }
 inline void done(JNIEnv* env, int rc) { if (rc != 0) throw_cuda_exception(env, rc); }
+// The boolean natives tell Java whether they handled the shape: the engine tries them in an else-if chain
+// (`algo == X && native(...)`) and falls through to the general native on false.  A refused shape or argument
+// (negative code) is therefore a plain false with no exception pending, as in the reference; only a CUDA
+// runtime error (positive code) is thrown.
+inline jboolean handled(JNIEnv* env, int rc) {
+  if (rc > 0) throw_cuda_exception(env, rc);
+  return rc == 0 ? 1 : 0;
+}
 
 }  // namespace
 
@@ -82,6 +90,17 @@ MATMUL_PLAIN(matMulT2_1mma, cu32_matMulT2_mma)
 MATMUL_SK(matMulSK, cu32_matMulSK)
 MATMUL_SK(matMulT1SK, cu32_matMulT1SK)
 MATMUL_SK(matMulT2SK, cu32_matMulT2SK)
+
+// Reads and clears the device status word (0 = every bounded wait of the kernels completed; otherwise the
+// first give-up record, see cu32_read_status).  Not in the reference's Java class: a maintainer declares
+// `public static native int kernelStatus();` in Cuda_matMul and calls it where the engine already
+// synchronises (its Syncer), so that a protocol time-out surfaces as an error instead of a wrong tensor.
+JNIEXPORT jint JNICALL JNAME(matMul, kernelStatus)(JNIEnv* env, jclass) {
+  int status = 0;
+  const int rc = cu32_read_status(&status);
+  if (rc != 0) { throw_cuda_exception(env, rc); return -1; }
+  return status;
+}
 
 // ---------------------------------------------------------------- Cuda_batchMatMul
 #define BMM_PLAIN(jname, cname)                                                                          \
@@ -213,8 +232,8 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1W1_1SGM)(JNIEnv* env, jclass, j
     Streams s(env, streams, length);                                                                       \
     const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, \
                          IW, N, IC, OC, ph, pw);                                                           \
-    done(env, rc);                                                                                         \
-    return rc == 0 ? 1 : 0;                                                                                \
+    return handled(env, rc);                                                                                         \
+                                                                                    \
   }
 #define DX_WINOGRAD_SGM(jname, cname)                                                                      \
   JNIEXPORT jboolean JNICALL JNAME_DX(jname)(JNIEnv* env, jclass, jboolean useTexture, jlongArray streams, \
@@ -224,8 +243,8 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1W1_1SGM)(JNIEnv* env, jclass, j
     Streams s(env, streams, length);                                                                       \
     const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dDY), OH, OW, cptr(dW), FH, FW, mptr(dDX), IH, \
                          IW, N, IC, OC, ph, pw, GM_slice);                                                 \
-    done(env, rc);                                                                                         \
-    return rc == 0 ? 1 : 0;                                                                                \
+    return handled(env, rc);                                                                                         \
+                                                                                    \
   }
 DX_WINOGRAD(Im2col_1Winograd_1s8_1texture, cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture)
 DX_WINOGRAD_SGM(Im2col_1Winograd_1s8_1texture_1SGM, cu32_dconv3D_deltaX_Im2col_Winograd_s8_texture_SGM)
@@ -352,16 +371,16 @@ JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s4_1texture)(JNIEnv
                                                                           jint OW_slice, DW_TAIL) {
   Streams s(env, streams, length);
   const int rc = cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s4_texture(s.h, s.n, GridZ, OH_slice, OW_slice, DW_TAIL_PASS);
-  done(env, rc);
-  return rc == 0 ? 1 : 0;
+  return handled(env, rc);
+  
 }
 JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s8_1texture)(JNIEnv* env, jclass, jlongArray streams,
                                                                           jint length, jint GridZ, jint OH_slice,
                                                                           jint OW_slice, DW_TAIL) {
   Streams s(env, streams, length);
   const int rc = cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s8_texture(s.h, s.n, GridZ, OH_slice, OW_slice, DW_TAIL_PASS);
-  done(env, rc);
-  return rc == 0 ? 1 : 0;
+  return handled(env, rc);
+  
 }
 JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s16_1texture)(JNIEnv* env, jclass, jlongArray streams,
                                                                            jint length, jint GridZ, jint OH_slice,
@@ -369,12 +388,12 @@ JNIEXPORT jboolean JNICALL JNAME_DW(Im2col_1WinogradV2_1SHW_1s16_1texture)(JNIEn
   Streams s(env, streams, length);
   const int rc =
       cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture(s.h, s.n, GridZ, OH_slice, OW_slice, c64, DW_TAIL_PASS);
-  done(env, rc);
-  return rc == 0 ? 1 : 0;
+  return handled(env, rc);
+  
 }
 
 // Contraction + bias row in one pass.  These natives do not exist in the reference's Java classes; a
-// maintainer who wants the fusion declares them and calls them from
+// maintainer who wants the fusion declares them in the Java class and calls them from
 // CudaFloat32EngineBase.matMul_biased / conv3D_biased instead of the two-kernel sequence.
 JNIEXPORT void JNICALL JNAME(matMul, matMul_1biased)(JNIEnv* env, jclass, jlongArray streams, jint length,
                                                      jlong dA, jlong dB, jlong dC, jlong dBias, jint N, jint M,
@@ -430,8 +449,8 @@ JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmV2R)(JNIEnv* env, jclass, jbool
     Streams s(env, streams, length);                                                                       \
     const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW,      \
                          mptr(dY), OH, OW, N, IC, OC, ph, pw);                                             \
-    done(env, rc);                                                                                         \
-    return rc == 0 ? 1 : 0;                                                                                \
+    return handled(env, rc);                                                                                         \
+                                                                                    \
   }
 #define CONV_WINOGRAD_SGM(jname, cname)                                                                    \
   JNIEXPORT jboolean JNICALL JNAME(conv3D, jname)(JNIEnv* env, jclass, jboolean useTexture,                \
@@ -442,8 +461,8 @@ JNIEXPORT void JNICALL JNAME(conv3D, conv3D_1GemmV2R)(JNIEnv* env, jclass, jbool
     Streams s(env, streams, length);                                                                       \
     const int rc = cname(useTexture ? 1 : 0, s.h, s.n, cptr(dX), IH, IW, cptr(dW), cptr(dCW), FH, FW,      \
                          mptr(dY), OH, OW, N, IC, OC, ph, pw, GM_slice);                                   \
-    done(env, rc);                                                                                         \
-    return rc == 0 ? 1 : 0;                                                                                \
+    return handled(env, rc);                                                                                         \
+                                                                                    \
   }
 CONV_WINOGRAD(conv3D_1Im2col_1Winograd_1s8_1R_1texture, cu32_conv3D_Im2col_Winograd_s8_R_texture)
 CONV_WINOGRAD_SGM(conv3D_1Im2col_1WinogradR_1s8_1texture_1SGM, cu32_conv3D_Im2col_WinogradR_s8_texture_SGM)

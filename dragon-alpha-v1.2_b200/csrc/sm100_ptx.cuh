@@ -39,6 +39,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// The same arrive with a cluster-scope release (debugging aid, selected by a tuning key: if a result
+// ever changes with it, a hand-over relied on ordering the default form does not give).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
@@ -72,7 +77,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // given up; seeing it set makes this wait give up too.  Returns false on give-up.
 template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag, long long limit_cycles = WAIT_LIMIT_CYCLES) {
 #pragma unroll 1
   for (int i = 0; i < 128; ++i) {
     if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
@@ -85,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
       if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_flag != 0) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
 }
 
@@ -158,6 +163,10 @@ __device__ __forceinline__ void tma_store_commit() {
 // All of this thread's committed stores have finished READING shared memory.
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// All but the most recent of this thread's committed stores have finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 // All of this thread's committed stores are complete.
 __device__ __forceinline__ void tma_store_wait_all() {
@@ -238,23 +247,6 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with the A operand read from TMEM (128 lanes = rows, one 32-bit column per k).
-template <int CTAS>
-__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  if (CTAS == 1)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Arrive (count 1) on `bar` once every tcgen05 operation this thread issued so

@@ -137,6 +137,7 @@ SIGNATURES = {
     "cu32_tune": [c_char_p, _I],
     "cu32_get_tune": [c_char_p, POINTER(c_int)],
     "cu32_read_status": [POINTER(c_int)],
+    "cu32_selftest_wait_giveup": [c_int64, ctypes.c_longlong],
 }
 
 
@@ -192,8 +193,14 @@ def read_status() -> int:
 def decode_status(word: int) -> str:
     if word == 0:
         return "ok"
-    roles = {1: "tma-producer", 2: "splitter", 3: "mma(operands)", 4: "mma(tmem-buffer)", 5: "drainer"}
+    roles = {1: "tma-producer", 2: "splitter", 3: "mma(operands)", 4: "mma(tmem-buffer)", 5: "drainer",
+             7: "self-test"}
     return f"{roles.get(word >> 24, word >> 24)} gave up at stage/buffer {(word >> 16) & 0xFF}, iteration {word & 0xFFFF}"
+
+
+def selftest_wait_giveup(stream: int, limit_cycles: int) -> None:
+    """Launch the one-warp kernel whose bounded wait runs out after `limit_cycles` (see the header)."""
+    _check(load().cu32_selftest_wait_giveup(int(stream), int(limit_cycles)), "cu32_selftest_wait_giveup")
 
 
 def version() -> str:

@@ -403,12 +403,17 @@ CU32_API int cu32_conv3D_GemmR_biased(const int64_t* streams, int length, const 
  *   "kc"       k-blocks (of 32) accumulated inside the tensor core before each FP32
  *              register add, FP32-accurate mode (default 2)
  *   "kc_fast"  same for the TF32 fast mode (default 4)
- *   "tile"     force a tile configuration: 0..4 = 128x64, 128x128, 128x256, 256x128 pair,
- *              256x256 pair (operands from shared memory); 5..7 = 256x192 pair, 128x64,
- *              128x128 with the A operand fed through TMEM; 8 = 256x64 pair; -1 = choose from the
- *              shape (default)
+ *   "tile"     force a tile configuration: 0..5 = 128x64, 128x128, 128x256, 256x128 pair,
+ *              256x256 pair, 256x64 pair; -1 = choose from the shape (default)
  *   "l2hint"   L2 eviction priority of the operand loads: 0 = none (default; measured best),
  *              1 = A evict-last and B evict-first, 2 = A evict-last only
+ *   "ring_raw", "ring_lo", "store_bufs"
+ *              shared-memory pipeline of the contraction kernel: slots for raw operand tiles (2..8), slots
+ *              for their low-order parts (1..ring_raw) and store-staging tiles per drain warp (1, 2);
+ *              0 = choose from the shape (default).  A combination that does not fit in shared memory
+ *              makes the call return cudaErrorInvalidValue.
+ *   "arrive_release"  1 = barrier arrivals between the two CTAs of a pair carry a cluster-scope release
+ *              (diagnostics: results must not depend on it); 0 = default
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
 CU32_API int cu32_tune(const char* key, int value);
 CU32_API int cu32_get_tune(const char* key, int* value);
@@ -417,6 +422,12 @@ CU32_API int cu32_get_tune(const char* key, int* value);
  * out of its bounded waits, else (role<<24 | stage<<16 | iteration) of the first one.
  * Synchronises the device; resets the word.  For tests and diagnostics only. */
 CU32_API int cu32_read_status(int* status);
+
+/* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits, for at most
+ * limit_cycles SM clock cycles (1 .. 100 000 000), on a barrier nobody arrives at.  The wait runs out, the kernel
+ * stores the give-up record (7<<24 | 1<<16 | 42) in the status word like the contraction kernel's roles do and
+ * returns normally; cu32_read_status then reports it.  Lets a host check the time-out path without any fault. */
+CU32_API int cu32_selftest_wait_giveup(int64_t stream, long long limit_cycles);
 
 /* "dragon_cu32 <version> sm_100a" */
 CU32_API const char* cu32_version(void);

@@ -82,7 +82,7 @@ def test_matmul_biased_equals_two_step_sequence(pkg, O, cuda, shape, mma):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 8])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5])
 def test_matmul_biased_every_tile(pkg, O, cuda, tile):
     import gpu_util as G
     pkg.cu32.tune("tile", tile)

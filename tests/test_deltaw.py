@@ -215,7 +215,7 @@ def test_deltaw_repeats_bit_for_bit_on_every_tile(pkg, O, cuda):
         pkg.cu32.tune("tile", 4)
         base = _run(pkg, "dconv3D_deltaW_GemmSK", X, dY, FH, FW, sh, sw, ph, pw, GZ=4)
         assert O.frob_rel(base, O.f64.deconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw)) <= 1e-6
-        for tile in (0, 1, 2, 3, 4, 8):
+        for tile in (0, 1, 2, 3, 4, 5):
             pkg.cu32.tune("tile", tile)
             for rep in range(6):
                 R = _run(pkg, "dconv3D_deltaW_GemmSK", X, dY, FH, FW, sh, sw, ph, pw, GZ=4)

@@ -167,7 +167,7 @@ def test_deltax_entry_point_aliases_and_W1(pkg, O, cuda):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 8])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5])
 def test_deltax_every_tile_same_bits(pkg, O, cuda, tile):
     rng = np.random.default_rng(63)
     N, IH, IW, IC, OC, FH, FW, ph, pw = 4, 20, 20, 136, 72, 3, 3, 1, 1
@@ -591,7 +591,7 @@ def test_strided_deltax_repeats_bit_for_bit_on_every_tile(pkg, O, cuda):
         pkg.cu32.tune("tile", 4)
         base = _run_strided(pkg, "ksIms2R", dY, W, IH, IW, sh, sw, ph, pw)
         assert O.frob_rel(base, O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)) <= 1e-6
-        for tile in (0, 1, 2, 3, 4, 8):
+        for tile in (0, 1, 2, 3, 4, 5):
             pkg.cu32.tune("tile", tile)
             for rep in range(6):
                 R = _run_strided(pkg, "crossAdd" if rep & 1 else "ksIms2R", dY, W, IH, IW, sh, sw, ph, pw)

@@ -187,8 +187,18 @@ def test_argument_errors_without_gpu(pkg):
     assert lib.cu32_conv3D_GemmR(s, 1, fake, 8, 8, fake, fake, 3, 3, fake, 8, 8, 4, 6, 8, 1, 1, 1, 1) == -4  # IC % 4
     assert lib.cu32_conv3D_GemmR(s, 1, fake, 8, 8, fake, fake, 3, 3, fake, 8, 8, 4, 8, 8, 0, 1, 1, 1) == -2  # stride 0
     assert lib.cu32_conv3D_GemmR_SGM(s, 1, fake, 8, 8, fake, fake, 3, 3, fake, 8, 8, 4, 8, 8, 1, 1, 1, 1, 0) == -8
+    # output extents that do not follow from the geometry (8x8, 3x3, pad 1, stride 1 gives 8x8, not 7x8)
+    assert lib.cu32_conv3D_GemmR(s, 1, fake, 8, 8, fake, fake, 3, 3, fake, 7, 8, 4, 8, 8, 1, 1, 1, 1) == -2
+    assert lib.cu32_conv3D(s, 1, fake, 8, 8, fake, 3, 3, fake, 8, 8, 4, 8, 8, 2, 2, 1, 1) == -2
+    # the allocation-free split-K refuses everything its two launches would refuse before the first one
+    assert lib.cu32_matMulT1SK_noalloc(s, 1, 4, fake, fake, odd, 8, 8, 512) == -4
+    assert lib.cu32_matMulT1SK_noalloc(s, 1, 4, null, fake, fake, 8, 8, 512) == -1
+    assert lib.cu32_matMulT1SK_noalloc(s, 1, 4, fake, fake, fake, 8, 6, 512) == -4
+    assert lib.cu32_matMulT1SK_noalloc(s, 1, 100, fake, fake, fake, 512, 512, 512) == -9
+    assert lib.cu32_selftest_wait_giveup(0, 0) == -8
+    assert lib.cu32_tune(b"ring_raw", 9) == -8 and lib.cu32_tune(b"store_bufs", 3) == -8
     assert lib.cu32_tune(b"nonsense", 1) == -8
-    assert lib.cu32_tune(b"tile", 9) == -8
+    assert lib.cu32_tune(b"tile", 6) == -8
     assert lib.cu32_tune(b"kc", 0) == -8
     v = ctypes.c_int(-5)
     assert lib.cu32_get_tune(b"kc", ctypes.byref(v)) == 0 and v.value >= 1

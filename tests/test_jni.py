@@ -276,3 +276,24 @@ def test_jni_deltaw_on_gpu(pkg, O, cuda):
       N, IC, OC, 1, 1, p, p)
     assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
     G.check_status(pkg)
+
+
+def test_refused_boolean_native_returns_false_without_an_exception(pkg):
+    """The Java engine tries the Winograd natives inside an else-if chain (`algo == X && native(...)`,
+    CudaFloat32EngineBase.java:2603-2616) and falls through to the general native on false, so a shape
+    this library refuses must come back as a plain false with no exception pending."""
+    lib = pkg.cu32.load()
+    jni = FakeJNI([0])
+    f = getattr(lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1conv3D_conv3D_1Im2col_1Winograd_1s8_1R_1texture")
+    f.argtypes = [c_void_p, c_void_p, ctypes.c_uint8, c_void_p, c_int32, c_int64, c_int32, c_int32, c_int64, c_int64,
+                  c_int32, c_int32, c_int64] + [c_int32] * 7
+    f.restype = ctypes.c_uint8
+    # IC = 6 is not a multiple of 4: refused with CU32_E_ALIGN before any CUDA call
+    handled = f(jni.env, None, 1, ARRAY_HANDLE, 1, 0x10000, 8, 8, 0x10000, 0x10000, 3, 3, 0x10000, 8, 8, 4, 6, 8, 1, 1)
+    assert handled == 0
+    assert jni.thrown is None and not any(e[0] in ("FindClass", "NewObjectA", "Throw") for e in jni.log)
+
+
+def test_kernel_status_native_is_exported(pkg):
+    lib = pkg.cu32.load()
+    assert hasattr(lib, "Java_z_dragon_engine_cuda_impl_math_Cuda_1matMul_kernelStatus")

@@ -106,7 +106,7 @@ def test_matmul_remainder_sweep(pkg, O, cuda):
         assert O.same_percent(C, G.ref_matmul(O, form, A, B, N, M, K), 1e-5) >= 0.999
 
 
-@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("tile", [0, 1, 2, 3, 4, 5])
 def test_every_tile_configuration(pkg, O, cuda, tile):
     pkg.cu32.tune("tile", tile)
     for form in ("AB", "T1", "T2"):
@@ -156,7 +156,7 @@ def test_results_repeat_bit_for_bit_on_every_tile(pkg, O, cuda):
     for name, fn in cases.items():
         pkg.cu32.tune("tile", 4)
         base = fn()
-        for tile in (0, 1, 2, 3, 4, 8):
+        for tile in (0, 1, 2, 3, 4, 5):
             pkg.cu32.tune("tile", tile)
             for rep in range(16):
                 Y = fn()
