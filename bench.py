@@ -20,6 +20,18 @@ cpu_baseline  the reference's CPU check loop timed on the host cores on a bounde
 --impl reference   times that CPU loop alone (the reference has no other CPU implementation of
            this path), all host threads, on the same configuration
 
+configs    (default run on one GPU) every other benchmark configuration timed the same way in the same run:
+           ms, TFLOP/s, GB/s, roofline fraction and the tile the library chose
+gpu_reference  the reference's own SIMT kernels (built from the reference tree into oracle/_ref) on the same
+           8192^3 operands on this GPU, in the same run
+clock      SM clock the kernels really ran at, from cycle and nanosecond counts taken inside the kernel, next to
+           the management library's samples; cycles per k-block against the tensor pipe's 1536
+sustained  the headline launched back to back for >= 2 s (power-capped clocks), against the sustained peak
+
+With N > 1 GPUs `value` includes the reassembly of the output shards (NCCL all-gather over NVLink, issued per row
+block so that it overlaps the next block's compute); `compute_only` is the figure without it, `strong` the
+8192^3 problem itself split over the ranks.
+
 Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2, c4_dw, c3_qk_scaled,
 c3_qk, c3_pv, c4, c5.
 """
@@ -152,10 +164,13 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU baseline (reference loops)
-def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, seconds_target: float = 12.0):
+CPU_BLOCK_ROWS = 128   # output rows per host thread and pass: the same block in every CPU leg
+
+
+def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, passes: int = 1):
     """Time the reference's CPU check loop (multiply*, Cuda_matMul/test.cuh:60-82) on a bounded
-    sample: every host thread runs the loop on its own block of `rows` output rows.  Returns
-    (TFLOP/s, cores, kind, sample description)."""
+    sample: every host thread runs the loop `passes` times on its own block of CPU_BLOCK_ROWS output
+    rows.  Returns (TFLOP/s, cores, kind, sample description)."""
     import numpy as np
     from oracle import oracle as O
     ref = O.ref_native("matmul")
@@ -165,10 +180,7 @@ def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, seconds_target: 
     names = {"AB": ("ref_cpu_multiply", "oracle_multiply"), "T1": ("ref_cpu_multiplyT1", "oracle_multiplyT1"),
              "T2": ("ref_cpu_multiplyT2", "oracle_multiplyT2")}[form]
     fn = getattr(ref, names[0]) if ref is not None else getattr(O.lib(), names[1])
-    # ~9 GFLOP/s per core for this loop order: size the row block for the target time
-    rows = int(max(4, min(N // cores, seconds_target * 9e9 / (2.0 * M * K))))
-    rows -= rows % 4
-    rows = max(rows, 4)
+    rows = max(4, min(CPU_BLOCK_ROWS, (N // cores) // 4 * 4))
     A = np.ascontiguousarray(A, dtype=np.float32)
     B = np.ascontiguousarray(B, dtype=np.float32)
     work = []
@@ -182,7 +194,9 @@ def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, seconds_target: 
         work.append((a, c))
 
     def run(a, c):
-        fn(a.ctypes.data_as(fp), B.ctypes.data_as(fp), c.ctypes.data_as(fp), rows, M, K)
+        for _ in range(passes):
+            c[:] = 0
+            fn(a.ctypes.data_as(fp), B.ctypes.data_as(fp), c.ctypes.data_as(fp), rows, M, K)
     threads = [threading.Thread(target=run, args=w) for w in work]
     t0 = time.perf_counter()
     for t in threads:
@@ -190,8 +204,9 @@ def cpu_reference_loop(form: str, N: int, M: int, K: int, A, B, seconds_target: 
     for t in threads:
         t.join()
     dt = time.perf_counter() - t0
-    flops = 2.0 * rows * M * K * cores
-    return flops / dt / 1e12, cores, kind, f"{cores} threads x {rows} output rows of the {N}x{M}x{K} problem ({dt:.1f} s)"
+    flops = 2.0 * rows * M * K * cores * passes
+    return (flops / dt / 1e12, cores, kind,
+            f"{cores} threads x {passes} pass(es) over {rows} output rows each of the {N}x{M}x{K} problem ({dt:.1f} s)")
 
 
 # ------------------------------------------------------------------ workloads on the device
@@ -199,8 +214,10 @@ class Workload:
     """Builds device operands and returns `launch()` (enqueue one step on the current stream),
     flops and algorithmic bytes per launch, plus host buffers for the end-to-end leg."""
 
-    def __init__(self, name, pkg, torch, rank, size=8192, batch=1024, images=256):
+    def __init__(self, name, pkg, torch, rank, size=8192, batch=1024, images=256, light=False):
         self.name, self.pkg, self.torch = name, pkg, torch
+        self.light = light          # no end-to-end leg: the host copies need not be pinned
+        pin = (lambda t: t) if light else (lambda t: t.pin_memory())
         W = pkg.workloads
         mm, bm, cv = pkg.cu32.Cuda_matMul, pkg.cu32.Cuda_batchMatMul, pkg.cu32.Cuda_conv3D
         st = lambda: [torch.cuda.current_stream().cuda_stream]
@@ -215,7 +232,7 @@ class Workload:
                 w = W.config5(K=1048576 // 8)   # one GPU's K shard of the 8-GPU configuration
             else:
                 w = W.config2({"c2_ab": "AB", "c2_bias": "AB", "c2_t1": "T1", "c2_t2": "T2"}[name], size)
-            self.hosts = [w.A.pin_memory(), w.B.pin_memory()]
+            self.hosts = [pin(w.A), pin(w.B)]
             self.dev_in = [torch.empty_like(h, device="cuda") for h in self.hosts]
             for d, h in zip(self.dev_in, self.hosts):
                 d.copy_(h)
@@ -249,7 +266,7 @@ class Workload:
         elif name in ("c3_qk", "c3_qk_scaled", "c3_pv"):
             w = W.config3(Batch=batch)
             if name in ("c3_qk", "c3_qk_scaled"):
-                self.hosts = [w.Q.pin_memory(), w.K.pin_memory()]
+                self.hosts = [pin(w.Q), pin(w.K)]
                 self.dev_in = [h.cuda() for h in self.hosts]
                 self.out = torch.empty((w.Batch, w.L, w.L), device="cuda")
                 dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
@@ -261,10 +278,16 @@ class Workload:
                                                                   w.Batch, w.L, w.L, w.L, w.D, alpha)
                     self.desc = f"batchMatMulT2_scaled Q*K^T/sqrt(d) Batch={w.Batch} {w.L}x{w.L}x{w.D}"
             else:
-                g = torch.Generator().manual_seed(3003)
-                P = torch.softmax(torch.randn((w.Batch, w.L, w.L), generator=g), dim=-1)
-                self.hosts = [P.pin_memory(), w.V.pin_memory()]
-                self.dev_in = [h.cuda() for h in self.hosts]
+                if light:   # softmax-normalised rows made on the device
+                    g = torch.Generator(device="cuda").manual_seed(3003)
+                    P = torch.softmax(torch.randn((w.Batch, w.L, w.L), generator=g, device="cuda"), dim=-1)
+                    self.hosts = [None, w.V]
+                    self.dev_in = [P, w.V.cuda()]
+                else:
+                    g = torch.Generator().manual_seed(3003)
+                    P = torch.softmax(torch.randn((w.Batch, w.L, w.L), generator=g), dim=-1)
+                    self.hosts = [P.pin_memory(), w.V.pin_memory()]
+                    self.dev_in = [h.cuda() for h in self.hosts]
                 self.out = torch.empty((w.Batch, w.L, w.D), device="cuda")
                 dA, dB, dC = self.dev_in[0], self.dev_in[1], self.out
                 self.launch = lambda: bm.batchMatMul(st(), 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), w.Batch, w.L, w.D, w.L, w.L)
@@ -274,7 +297,7 @@ class Workload:
         elif name == "c4":
             w = W.config4(N=images)
             d = w.dims
-            self.hosts = [w.X.pin_memory(), w.W.pin_memory()]
+            self.hosts = [pin(w.X), pin(w.W)]
             self.dev_in = [h.cuda() for h in self.hosts]
             self.out = torch.empty((d["N"], d["OH"], d["OW"], d["OC"]), device="cuda")
             self.cw = torch.empty(w.W.numel(), device="cuda")
@@ -297,7 +320,7 @@ class Workload:
             d = w.dims
             g = torch.Generator().manual_seed(4004)
             dYh = torch.randn((d["N"], d["OH"], d["OW"], d["OC"]), generator=g)
-            self.hosts = [dYh.pin_memory(), w.W.pin_memory()]
+            self.hosts = [pin(dYh), pin(w.W)]
             self.dev_in = [h.cuda() for h in self.hosts]
             self.out = torch.empty((d["N"], d["IH"], d["IW"], d["IC"]), device="cuda")
             ddY, dW, dDX = self.dev_in[0], self.dev_in[1], self.out
@@ -317,7 +340,7 @@ class Workload:
             g = torch.Generator().manual_seed(4005)
             dYh = torch.randn((N_, OH, OH, OC), generator=g)
             Wh = torch.randn((OC, F, F, IC), generator=g) * 0.03
-            self.hosts = [dYh.pin_memory(), Wh.pin_memory()]
+            self.hosts = [pin(dYh), pin(Wh)]
             self.dev_in = [h.cuda() for h in self.hosts]
             self.out = torch.empty((N_, IH, IH, IC), device="cuda")
             CF = (F + sd - 1) // sd
@@ -342,7 +365,7 @@ class Workload:
             d = w.dims
             g = torch.Generator().manual_seed(4006)
             dYh = torch.randn((d["N"], d["OH"], d["OW"], d["OC"]), generator=g)
-            self.hosts = [w.X.pin_memory(), dYh.pin_memory()]
+            self.hosts = [pin(w.X), pin(dYh)]
             self.dev_in = [h.cuda() for h in self.hosts]
             size = d["OC"] * d["FH"] * d["FW"] * d["IC"]
             self.out = torch.empty((d["OC"], d["FH"], d["FW"], d["IC"]), device="cuda")
@@ -447,6 +470,125 @@ def time_steps(torch, dist, fn, steps, world, on_start=None, on_stop=None):
     return ms
 
 
+TILE_NAMES = {0: "128x64", 1: "128x128", 2: "128x256", 3: "256x128 pair", 4: "256x256 pair", 5: "256x64 pair"}
+HBM_BOUND = ("c3_qk", "c3_qk_scaled", "c3_pv", "c3_attn")
+
+
+def roofline_of(name, wl, ms_step, pk, sustained=False, traffic=None):
+    """Roofline object for one launch: tensor bound (FP32-accurate = three TF32 products per term, TF32 at half
+    the bf16 rate) or HBM bound for the attention-shaped batched products."""
+    per_gpu = wl.flops / (ms_step * 1e-3) / 1e12
+    if name in HBM_BOUND:
+        gbs = wl.bytes / (ms_step * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                "traffic": traffic, "peak_basis": f"{pk['basis']} copy bandwidth"}
+    bf16 = pk["bf16_sustained"] if sustained else pk["bf16"]
+    ceiling = bf16 / 2.0 / 3.0
+    return {"bound": "tensor", "achieved": per_gpu, "peak": ceiling, "unit": "TFLOP/s", "frac": per_gpu / ceiling,
+            "traffic": traffic,
+            "peak_basis": f"{pk['basis']} bf16 {'sustained' if sustained else 'burst'} {bf16} TFLOP/s / 2 (TF32 rate) / 3 (hi*hi + hi*lo + lo*hi)"}
+
+
+def check_status(pkg):
+    st = pkg.cu32.read_status()
+    if st != 0:
+        raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
+
+
+def device_clock(pkg):
+    """Effective SM clock in MHz over the contraction launches since the last read (cycles and nanoseconds are
+    counted inside the kernel by CTA 0), or None if nothing ran."""
+    cyc, ns, launches = pkg.cu32.read_clock()
+    return {"effective_sm_mhz": cyc / ns * 1e3 if ns else None, "kernel_cycles": cyc, "kernel_ns": ns, "launches": launches}
+
+
+def other_configs(pkg, torch, pk, names, steps, warmup):
+    """Every other benchmark configuration, timed like the headline (CUDA events on the launching stream, inputs
+    resident, operands larger than L2 except config 1), one after the other on this GPU."""
+    out = {}
+    for name in names:
+        wl = Workload(name, pkg, torch, 0, light=True)
+        for _ in range(warmup):
+            wl.launch()
+        check_status(pkg)
+        pkg.cu32.read_clock()
+        ms = time_steps(torch, None, wl.launch, steps, 1) / steps
+        clk = device_clock(pkg)
+        check_status(pkg)
+        roof = roofline_of(name, wl, ms, pk)
+        tile = pkg.cu32.get_tune("last_tile")
+        entry = {"workload": wl.desc, "ms_per_step": ms, "tflops": wl.flops / (ms * 1e-3) / 1e12,
+                 "gbs": wl.bytes / (ms * 1e-3) / 1e9, "bound": roof["bound"], "frac": roof["frac"],
+                 "peak": roof["peak"], "unit": roof["unit"], "tile": TILE_NAMES.get(tile, tile),
+                 "launches_per_step": wl.kernels_per_step, "effective_sm_mhz": clk["effective_sm_mhz"],
+                 "l2": "operands larger than L2" if wl.bytes > 126e6 else "operands fit in L2 (not flushed)"}
+        if hasattr(wl, "images"):
+            entry["images_per_s"] = wl.images / (ms * 1e-3)
+        out[name] = entry
+        del wl
+        torch.cuda.empty_cache()
+    return out
+
+
+def gpu_reference_leg(torch, wl):
+    """The reference's own SIMT FP32 kernels (matMul4x, Cuda_matMul/matMul.cuh:47-119, compiled for sm_100a from the
+    reference tree into oracle/_ref) on the same device operands: best of 5 launches, CUDA events."""
+    from oracle import oracle as O
+    ref = O.ref_native("matmul")
+    if ref is None or wl.cpu_case is None:
+        return None
+    form, N, M, K = wl.cpu_case[:4]
+    fn = {"AB": ref.ref_gpu_matMul, "T1": ref.ref_gpu_matMulT1, "T2": ref.ref_gpu_matMulT2}[form]
+    fp = ctypes.POINTER(ctypes.c_float)
+    ptr = lambda t: ctypes.cast(ctypes.c_void_p(t.data_ptr()), fp)
+    streams = (ctypes.c_longlong * 10)(*([torch.cuda.current_stream().cuda_stream] * 10))
+    C = torch.zeros((N, M), device="cuda")
+    run = lambda: fn(streams, 10, ptr(wl.dev_in[0]), ptr(wl.dev_in[1]), ptr(C), N, M, K)
+    for _ in range(2):
+        if run() != 0:
+            return None
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run(); e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1)
+        best = t if best is None else min(best, t)
+    return {"value": wl.flops / (best * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": best,
+            "kind": "the reference's SIMT FP32 kernels built for sm_100a (oracle/_ref/libref_matmul.so), same operands"}
+
+
+class ShardedStep:
+    """One multi-GPU step of a row-shardable matMul: this rank's rows are cut into blocks; block b is multiplied
+    on the current stream and then all-gathered (NCCL over NVLink, its own stream) while block b+1 is being
+    multiplied.  Block b of every rank lands side by side in `gathered[b]`, i.e. the rows of the full output
+    are dealt to the ranks block-cyclically and the reassembled output is in row order."""
+
+    def __init__(self, torch, dist, pkg, wl, world, nblk):
+        form, N, M, K = wl.cpu_case[:4]
+        assert form in ("AB", "T2")
+        self.torch, self.dist, self.wl = torch, dist, wl
+        mm = pkg.cu32.Cuda_matMul
+        self.fn = mm.matMul if form == "AB" else mm.matMulT2
+        self.N, self.M, self.K, self.nblk = N, M, K, nblk
+        self.rows = N // nblk
+        self.gathered = torch.empty((nblk, world, self.rows * M), device="cuda")
+        self.bytes_received = (world - 1) * N * M * 4
+
+    def __call__(self):
+        torch, dist, wl = self.torch, self.dist, self.wl
+        dA, dB, dC = wl.dev_in[0], wl.dev_in[1], wl.out
+        cur = torch.cuda.current_stream()
+        works = []
+        for b in range(self.nblk):
+            r0, r1 = b * self.rows, (b + 1) * self.rows
+            self.fn([cur.cuda_stream], 1, dA[r0:r1].data_ptr(), dB.data_ptr(), dC[r0:r1].data_ptr(), r1 - r0, self.M, self.K)
+            works.append(dist.all_gather_into_tensor(self.gathered[b].view(-1), dC[r0:r1].reshape(-1), async_op=True))
+        for w in works:
+            w.wait()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -459,6 +601,8 @@ def main():
     ap.add_argument("--images", type=int, default=256, help="images of the c4 workload (smaller for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other configurations, the reference-kernel leg and the sustained leg (profiling runs)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -475,7 +619,7 @@ def main():
         w = pkg.workloads.config2("AB")
         vals, cores, kind, sample = [], 1, "port", ""
         for i in range(a.warmup + a.steps):
-            v, cores, kind, sample = cpu_reference_loop("AB", w.N, w.M, w.K, w.A.numpy(), w.B.numpy(), seconds_target=2.0)
+            v, cores, kind, sample = cpu_reference_loop("AB", w.N, w.M, w.K, w.A.numpy(), w.B.numpy())
             if i >= a.warmup:
                 vals.append(v)
         v = statistics.mean(vals)
@@ -499,14 +643,13 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg.cu32.load()
+    pkg.cu32.tune("clock", 1)
     pk = peaks()
 
     wl = Workload(a.workload, pkg, torch, rank, a.size, a.batch, a.images)
     for _ in range(a.warmup):
         wl.launch()
-    st = pkg.cu32.read_status()
-    if st != 0:
-        raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
+    check_status(pkg)
 
     gpu_uuid = None
     try:
@@ -521,16 +664,74 @@ def main():
 
     def stop_sampler():
         if "sampler" in box:
-            box["clocks"] = box["sampler"].stop()
+            box["clocks"] = box.pop("sampler").stop()
 
+    # ---- compute only (device-timed, inputs resident)
+    pkg.cu32.read_clock()
     ms = time_steps(torch, dist, wl.launch, a.steps, world, start_sampler, stop_sampler)
     clocks = box.get("clocks")
-    st = pkg.cu32.read_status()
-    if st != 0:
-        raise SystemExit("kernel gave up: " + pkg.cu32.decode_status(st))
-    ms_step = ms / a.steps
+    dev_clk = device_clock(pkg)
+    check_status(pkg)
+    ms_compute = ms / a.steps
+    tile = pkg.cu32.get_tune("last_tile")
+
+    # ---- N > 1: the step that counts includes the reassembly of the shards
+    collective = None
+    ms_step = ms_compute
+    launches_per_step = wl.kernels_per_step
+    if world > 1:
+        if a.workload in ("c5", "c4_dw"):
+            # K-sharded shapes: each rank reduces over its own rows (c5) or its own images (the convolution's
+            # weight gradient, the data-parallel training pattern) and the partial outputs are summed
+            def step_collective():
+                wl.launch()
+                dist.all_reduce(wl.out)
+            kind, nblk = "all-reduce of the partial products", 1
+            moved = 2.0 * wl.out.numel() * 4 * (world - 1) / world
+        elif wl.cpu_case is not None and wl.cpu_case[0] in ("AB", "T2") and wl.kernels_per_step == 1 and wl.cpu_case[1] >= 2048:
+            nblk = int(os.environ.get("DRAGON_BENCH_GATHER_BLOCKS", "4"))
+            step_collective = ShardedStep(torch, dist, pkg, wl, world, nblk)
+            kind = f"all-gather of the output shards in {nblk} row blocks, block b in flight while block b+1 is multiplied"
+            moved = float(step_collective.bytes_received)
+            launches_per_step = nblk
+        else:
+            gathered = torch.empty((world,) + tuple(wl.out.shape), device="cuda")
+
+            def step_collective():
+                wl.launch()
+                dist.all_gather_into_tensor(gathered, wl.out)
+            kind, nblk = "all-gather of the output shards after the launch", 1
+            moved = float((world - 1) * wl.out.numel() * 4)
+        for _ in range(3):
+            step_collective()
+        ms_step = time_steps(torch, dist, step_collective, a.steps, world) / a.steps
+        check_status(pkg)
+        exposed = max(ms_step - ms_compute, 1e-9)
+        collective = {"kind": kind, "ms_per_step": ms_step, "compute_only_ms": ms_compute,
+                      "bytes_received_per_rank": moved,
+                      "exposed_ms": ms_step - ms_compute,
+                      "nvlink_gbs_if_serial": moved / (exposed * 1e-3) / 1e9,
+                      "note": "NVLink reference on this pool: 770 GB/s peer copy per direction"}
     value = wl.flops * world / (ms_step * 1e-3) / 1e12
 
+    # ---- strong scaling: the 8192^3 problem itself, rows divided over the ranks, output all-gathered
+    strong = None
+    if world > 1 and a.workload == "c2_ab" and a.size % (world * 4 * 128) == 0:
+        rows = a.size // world
+        dA, dB, dC = wl.dev_in[0][:rows], wl.dev_in[1], wl.out[:rows]
+        full = torch.empty((world, rows * a.size), device="cuda")
+        mmf = pkg.cu32.Cuda_matMul.matMul
+
+        def strong_step():
+            mmf([torch.cuda.current_stream().cuda_stream], 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), rows, a.size, a.size)
+            dist.all_gather_into_tensor(full.view(-1), dC.reshape(-1))
+        for _ in range(3):
+            strong_step()
+        ms_s = time_steps(torch, dist, strong_step, a.steps, world) / a.steps
+        strong = {"value": 2.0 * a.size ** 3 / (ms_s * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_s,
+                  "workload": f"matMul AB 8192^3 in total: {rows} rows of A and C per rank, B replicated, C all-gathered"}
+
+    # ---- end to end with host buffers
     e2e = None
     if not a.no_e2e:
         wl.prepare_e2e()
@@ -541,67 +742,86 @@ def main():
         e2e = {"value": wl.flops * world / (ms_e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e,
                "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
 
-    reassemble = None
-    if world > 1:
-        # The only collective of the path: putting the shards' outputs back together (all-gather
-        # over NVLink), or for the K-sharded long-K shape summing the partial products.
-        if a.workload in ("c5", "c4_dw"):
-            # K-sharded shapes: each rank reduces over its own rows (c5) or its own images (the convolution's
-            # weight gradient, the data-parallel training pattern) and the partial outputs are summed
-            def step_collective():
-                wl.launch()
-                dist.all_reduce(wl.out)
-            kind = "all-reduce of the partial products"
-        else:
-            gathered = torch.empty((world,) + tuple(wl.out.shape), device="cuda")
+    # ---- sustained: the same launch back to back for >= 2 s, clocks sampled, against the sustained peak
+    sustained = None
+    extras = world == 1 and not a.no_extras and a.workload == "c2_ab" and a.size == 8192
+    if extras:
+        n_sus = max(a.steps, int(2200.0 / ms_compute))
+        pkg.cu32.read_clock()
+        ms_sus = time_steps(torch, dist, wl.launch, n_sus, world, start_sampler, stop_sampler) / n_sus
+        clk_sus = device_clock(pkg)
+        check_status(pkg)
+        roof_s = roofline_of(a.workload, wl, ms_sus, pk, sustained=True)
+        sustained = {"launches": n_sus, "seconds": n_sus * ms_sus * 1e-3, "ms_per_step": ms_sus,
+                     "value": wl.flops / (ms_sus * 1e-3) / 1e12, "unit": UNIT, "frac": roof_s["frac"], "peak": roof_s["peak"],
+                     "peak_basis": roof_s["peak_basis"], "effective_sm_mhz": clk_sus["effective_sm_mhz"],
+                     "clocks": box.get("clocks")}
 
-            def step_collective():
-                wl.launch()
-                dist.all_gather_into_tensor(gathered, wl.out)
-            kind = "all-gather of the output shards"
-        for _ in range(2):
-            step_collective()
-        rs = max(3, min(a.steps, 10))
-        ms_r = time_steps(torch, dist, step_collective, rs, world) / rs
-        reassemble = {"value": wl.flops * world / (ms_r * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_r, "collective": kind}
+    gpu_ref = gpu_reference_leg(torch, wl) if extras else None
+    if gpu_ref:
+        gpu_ref["ratio"] = (wl.flops / (ms_compute * 1e-3) / 1e12) / gpu_ref["value"]
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    per_gpu = wl.flops / (ms_step * 1e-3) / 1e12
-    sustained = a.steps * ms_step > 1500.0
-    bf16 = pk["bf16_sustained"] if sustained else pk["bf16"]
-    ceiling = bf16 / 2.0 / 3.0
-    bound = "hbm" if a.workload.startswith("c3") else "tensor"
-    if bound == "tensor":
-        roof = {"bound": "tensor", "achieved": per_gpu, "peak": ceiling, "unit": "TFLOP/s", "frac": per_gpu / ceiling,
-                "traffic": NCU_TRAFFIC_BYTES.get(a.workload) if a.size == 8192 else None,
-                "peak_basis": f"{pk['basis']} bf16 {'sustained' if sustained else 'burst'} {bf16} TFLOP/s / 2 (TF32 rate) / 3 (hi*hi + hi*lo + lo*hi)"}
-    else:
-        gbs = wl.bytes / (ms_step * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                "traffic": None, "peak_basis": f"{pk['basis']} copy bandwidth"}
+    roof = roofline_of(a.workload, wl, ms_compute, pk, sustained=a.steps * ms_compute > 1500.0,
+                       traffic=NCU_TRAFFIC_BYTES.get(a.workload) if a.size == 8192 else None)
+
+    # ---- where the fraction comes from: (tensor-pipe utilisation at the clock the kernel ran at) x (that clock / max)
+    clock = dict(dev_clk)
+    clock["nvml_median_mhz"] = clocks.get("sm_mhz") if clocks else None
+    clock["sm_max_mhz"] = clocks.get("sm_max_mhz") if clocks else None
+    if roof["bound"] == "tensor" and wl.cpu_case is not None and dev_clk["effective_sm_mhz"] and tile in (4,) \
+            and wl.kernels_per_step == 1:
+        form, N, M, K = wl.cpu_case[:4]
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        tiles = -(-N // 256) * -(-M // 256)
+        rounds = -(-tiles // (sms // 2))
+        kblocks = -(-K // 32)
+        cyc = ms_compute * 1e-3 * dev_clk["effective_sm_mhz"] * 1e6 / (rounds * kblocks)
+        clock.update({"tile_rounds": rounds, "k_blocks": kblocks, "cycles_per_kblock": cyc, "ideal_cycles_per_kblock": 1536,
+                      "pipe_utilisation": 1536.0 / cyc,
+                      "explains": "frac = pipe_utilisation x (tiles / (rounds x CTA pairs)) x effective clock x 4096 TF32-flop/clk/SM x SMs / 3 / peak"})
+        if clock["sm_max_mhz"]:
+            clock["clock_ratio"] = dev_clk["effective_sm_mhz"] / clock["sm_max_mhz"]
 
     cpu = None
     if world == 1 and not a.no_cpu_baseline and wl.cpu_case is not None:
         form, N, M, K, A, B = wl.cpu_case
-        v, cores, kind, sample = cpu_reference_loop(form, N, M, K, A.numpy(), B.numpy())
+        v, cores, kind, sample = cpu_reference_loop(form, N, M, K, A.numpy(), B.numpy(), passes=3)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+
+    configs = None
+    if extras:
+        del wl.dev_in, wl.out
+        torch.cuda.empty_cache()
+        configs = other_configs(pkg, torch, pk, ["c1", "c2_t1", "c2_t2", "c2_ragged", "c3_qk", "c3_pv", "c4", "c5"],
+                                a.steps, a.warmup)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3",
         "data": "synthetic",
-        "config": {"workload": wl.desc + (f"; {world} ranks, each its own shard of a {world}x larger problem" if world > 1 else ""),
+        "config": {"workload": wl.desc + (f"; {world} ranks, each its own shard of a {world}x larger problem, "
+                                                    "output shards all-gathered inside the step" if world > 1 else ""),
                    "l2": "operands larger than L2 (no flush needed)" if wl.bytes > 126e6 else "L2 not flushed: operands fit in L2",
-                   "kc": pkg.cu32.get_tune("kc"), "tile": pkg.cu32.get_tune("tile")},
-        "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": a.steps * wl.kernels_per_step,
-        "clocks": clocks,
+                   "kc": pkg.cu32.get_tune("kc"), "tile": TILE_NAMES.get(tile, tile)},
+        "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": a.steps * launches_per_step,
+        "clocks": clocks, "clock": clock,
     }
-    if reassemble:
-        line["with_collective"] = reassemble
+    if world > 1:
+        line["compute_only"] = {"value": wl.flops * world / (ms_compute * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_compute}
+        line["collective"] = collective
+        if strong:
+            line["strong"] = strong
+    if sustained:
+        line["sustained"] = sustained
+    if gpu_ref:
+        line["gpu_reference"] = gpu_ref
+    if configs:
+        line["configs"] = configs
     if hasattr(wl, "images"):
         line["images_per_s"] = wl.images * world / (ms_step * 1e-3)
     print(json.dumps(line))

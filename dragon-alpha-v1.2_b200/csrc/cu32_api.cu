@@ -59,6 +59,24 @@ static int* status_word_ptr(cudaError_t* err) {
   return static_cast<int*>(sym);
 }
 
+// Clock accumulator of the contraction kernel: {SM cycles, nanoseconds, launches} (see GemmParams::clock_acc).
+__device__ unsigned long long g_clock_acc[4];
+static std::atomic<int> g_clock_on{0};
+static std::atomic<int> g_last_tile{-1};
+
+static unsigned long long* clock_acc_ptr() {
+  if (!g_clock_on.load()) return nullptr;
+  static std::atomic<unsigned long long*> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  unsigned long long* p = cache[dev & 63].load(std::memory_order_acquire);
+  if (p) return p;
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, g_clock_acc) != cudaSuccess) return nullptr;
+  cache[dev & 63].store(static_cast<unsigned long long*>(sym), std::memory_order_release);
+  return static_cast<unsigned long long*>(sym);
+}
+
 // ------------------------------------------------------------------ tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -129,9 +147,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // rate.  The rates are FP32-accurate TFLOP/s measured at 8192^3 on a B200 with every SM
 // busy; padded rows and columns count as work, so narrow outputs pick narrow tiles and
 // small problems pick small tiles.
-static int pick_tile(long long M, int N, long long z) {
-  const int forced = g_tile.load();
-  if (forced >= 0) return forced;
+static int pick_tile_auto(long long M, int N, long long z) {
   // measured matMul 8192^3 rates per tile shape, TFLOP/s (order of the TileCfg enum)
   static const double rate[TILE_COUNT] = {123.0, 180.0, 200.0, 228.0, 278.0, 140.0};
   const double sms = static_cast<double>(device_sm_count());
@@ -146,16 +162,26 @@ static int pick_tile(long long M, int N, long long z) {
   }
   return best;
 }
+// The tile a call uses: the forced one if a tuning key set it, else the estimate's; remembered for diagnostics.
+static int pick_tile(long long M, int N, long long z) {
+  const int forced = g_tile.load();
+  const int t = forced >= 0 ? forced : pick_tile_auto(M, N, z);
+  g_last_tile = t;
+  return t;
+}
 
 // Ring lengths for a launch (see GemmParams): explicit tuning values win, otherwise 0 = the kernel
 // configuration's balanced default.
+// Also sets how many chunks are summed in registers between flushes to memory: 256 k-blocks (K = 8192).
 static void choose_rings(GemmParams* p) {
+  p->flush_chunks = 256 / p->kc > 1 ? 256 / p->kc : 1;
   p->ring_raw = g_ring_raw.load();
   p->ring_lo = g_ring_lo.load();
   p->store_bufs = g_store_bufs.load();
   if (p->ring_raw > 0 && p->ring_lo == 0) p->ring_lo = p->ring_raw;
   if (p->ring_raw == 0) p->ring_lo = 0;
   p->arrive_release = g_arrive_release.load();
+  p->clock_acc = clock_acc_ptr();
 }
 
 static int run_gemm(const GemmCall& c) {
@@ -1269,6 +1295,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "ring_lo")) { if (value < 0 || value > 8) return CU32_E_ARG; g_ring_lo = value; return CU32_OK; }
   if (!std::strcmp(key, "store_bufs")) { if (value < 0 || value > 2) return CU32_E_ARG; g_store_bufs = value; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { g_arrive_release = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "clock")) { g_clock_on = value ? 1 : 0; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {
@@ -1282,6 +1309,8 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "ring_lo")) { *value = g_ring_lo; return CU32_OK; }
   if (!std::strcmp(key, "store_bufs")) { *value = g_store_bufs; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { *value = g_arrive_release; return CU32_OK; }
+  if (!std::strcmp(key, "clock")) { *value = g_clock_on; return CU32_OK; }
+  if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_read_status(int* status) {
@@ -1293,6 +1322,17 @@ int cu32_read_status(int* status) {
   const int zero = 0;
   e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
   return static_cast<int>(e);
+}
+int cu32_read_clock(unsigned long long* out3) {
+  if (!out3) return CU32_E_NULL;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  unsigned long long v[4] = {0, 0, 0, 0};
+  e = cudaMemcpyFromSymbol(v, g_clock_acc, sizeof(v));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  out3[0] = v[0]; out3[1] = v[1]; out3[2] = v[2];
+  const unsigned long long zero[4] = {0, 0, 0, 0};
+  return static_cast<int>(cudaMemcpyToSymbol(g_clock_acc, zero, sizeof(zero)));
 }
 const char* cu32_version(void) { return "dragon_cu32 0.1 sm_100a"; }
 

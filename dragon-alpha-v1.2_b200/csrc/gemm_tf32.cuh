@@ -65,10 +65,13 @@ struct GemmParams {
   int gz;               // > 1: tiles run over gz split-K slices; else over zcount batches
   int zcount;           // batches (gz == 1) or slices (= gz) folded into the tile index
   int kc;               // k-blocks accumulated in TMEM before a drain (>= 1)
+  int flush_chunks;     // chunks summed in registers before the sums go to memory (>= 1): the first flush of a
+                        // tile stores, later ones add to what is there, so no FP32 register sum grows longer
   int vec4_ok;          // C, ldc and c_stride allow 16-byte stores
   int tma_store;        // tmC / tmCbuf are valid: store through shared memory + TMA
   int l2_hints;         // load A with evict-last and B with evict-first L2 priority
   int* status;          // device word, 0 = ok; first give-up code otherwise
+  unsigned long long* clock_acc;   // optional: {SM cycles, nanoseconds, launches} summed by CTA 0 of every launch
   // Shared-memory rings (sized by the host within the 227 KB a CTA may use).  A k-block's raw tiles
   // occupy a slot of the raw ring from the TMA issue until its MMAs have completed; its lo tiles
   // occupy a slot of the (shorter or equal) lo ring only from the split until then.  Memory-bound
@@ -123,7 +126,7 @@ struct GemmCfg {
   static constexpr int SPLIT_WARP0 = 2, SPLIT_WARPS = 6;
   static constexpr int DRAIN_WARP0 = 8, DRAIN_WARPS = 8;
   static constexpr int CW = BN / 2;          // columns per drain warp
-  static constexpr bool REALLOC = CW > 64;   // drainers need > 128 registers
+  static constexpr bool REALLOC = CW >= 64;  // drainers need more than the 128 registers a 512-thread CTA starts with
   // register budgets after reallocation (256 threads each side, 64 K registers per SM)
   static constexpr int REGS_MOVERS = 72;
   static constexpr int REGS_DRAINERS = 184;
@@ -281,6 +284,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   if (CTAS == 2) cluster_sync();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // CTA 0 times itself in SM cycles and in nanoseconds: summed over launches, cycles / ns is the clock the
+  // kernel really ran at (the management library's reading is a coarse sample and can miss short runs).
+  long long clk_t0 = 0;
+  unsigned long long clk_g0 = 0;
+  if (p.clock_acc != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    clk_t0 = clock64();
+    clk_g0 = globaltimer_ns();
+  }
 
   // Barrier addresses on the CTA that issues the MMAs (rank 0).
   auto leader_addr = [&](const uint64_t* bar) -> uint32_t {
@@ -608,154 +619,205 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
 #pragma unroll
       for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
       const int nchunks = (w.nkb + kc - 1) / kc;
-      for (int c = 0; c < nchunks; ++c, ++ch) {
-        const int buf = ch & 1;
-        const uint32_t par = (ch >> 1) & 1;
-        if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
-          if (lane == 0) give_up(ROLE_DRAIN, buf, c);
-          alive = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                            static_cast<uint32_t>(buf * BN + h * CW);
-        // 16-column pieces, the load of piece g+1 in flight while piece g is added; the
-        // buffer goes back to the MMA issuer as soon as the last piece has left TMEM.
-        constexpr int PIECES = CW / 16;
-        float va[16], vb[16];
-        tmem_ld_32x16(t0, va);
-#pragma unroll
-        for (int g = 0; g < PIECES; ++g) {
-          tmem_wait_ld();
-          float (&cur)[16] = (g & 1) ? vb : va;
-          float (&nxt)[16] = (g & 1) ? va : vb;
-          if (g + 1 < PIECES) {
-            tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
-          } else {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if (CTAS == 2 && rank != 0)
-                arrive_remote(leader_addr(&bar_tmem_empty[buf]));
-              else
-                mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-            }
+      // Long reductions leave the registers more than once: after every flush_chunks chunks the sums are
+      // stored (first time) or added to the output (later), which bounds the length of any FP32 register
+      // sum and with it the rounding error of non-negative data, whatever K is.  The additions to memory
+      // are one per element and flush, in a fixed order, so results stay reproducible.
+      const bool multi = nchunks > p.flush_chunks;
+      // a fused bias / scale is applied to the complete sum, so with several flushes the last one must read
+      // the output back: those tiles take the register path
+      const bool use_tma = p.tma_store && !(multi && (p.bias != nullptr || p.scale_on));
+      bool first = true;
+      int since = 0;
+      for (int c = 0;; ++c) {
+        if (c < nchunks) {
+          const int buf = ch & 1;
+          const uint32_t par = (ch >> 1) & 1;
+          if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
+            if (lane == 0) give_up(ROLE_DRAIN, buf, c);
+            alive = false;
+            break;
           }
+          tc_fence_after();
+          const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                              static_cast<uint32_t>(buf * BN + h * CW);
+          // 16-column pieces, the load of piece g+1 in flight while piece g is added; the
+          // buffer goes back to the MMA issuer as soon as the last piece has left TMEM.
+          constexpr int PIECES = CW / 16;
+          float va[16], vb[16];
+          tmem_ld_32x16(t0, va);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[g * 16 + j] += cur[j];
-        }
-      }
-      if (!alive) break;
-      // ---- fused bias row (optional): what the engine's linear_dual2D_row(C, bias, 1, 1, 0) does right
-      // after the product - one FP32 add per element, padding columns forced to zero.  Applied to
-      // each 4-column vector on its way out, so that no more than a few bias values are live.
-      auto with_bias = [&](int j, float4 v) -> float4 {
-        if (p.scale_on) {   // what a separate y = alpha*x + 0 kernel would store: one fused multiply-add per element
-          v.x = fmaf(v.x, p.alpha, 0.0f); v.y = fmaf(v.y, p.alpha, 0.0f);
-          v.z = fmaf(v.z, p.alpha, 0.0f); v.w = fmaf(v.w, p.alpha, 0.0f);
-        }
-        if (p.bias == nullptr) return v;
-        const int c = w.col0 + h * CW + j;   // a multiple of 4, like p.N: all four columns exist or none
-        if (c >= p.N) return v;
-        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + c));
-        v.x = (c + 0 < p.bias_width) ? v.x + b.x : 0.0f;
-        v.y = (c + 1 < p.bias_width) ? v.y + b.y : 0.0f;
-        v.z = (c + 2 < p.bias_width) ? v.z + b.z : 0.0f;
-        v.w = (c + 3 < p.bias_width) ? v.w + b.w : 0.0f;
-        return v;
-      };
-      // ---- store; the MMA warp is already filling the TMEM buffers with the next
-      // tile's chunks meanwhile
-      if (p.tma_store) {
-        // Each drain warp owns a 32-row x CW-column block.  32x32 pieces go through a
-        // swizzled 4 KB staging tile (row r, 16-byte chunk c at r*128 + ((c ^ (r & 7)) * 16):
-        // conflict-free for the row-per-lane writes) and leave as one TMA store each, which
-        // writes whole 128-byte row segments and clips rows >= M and columns >= N.  With two
-        // staging tiles per warp a piece is staged while the previous one is still being read.
-        const CUtensorMap* cmap = w.to_cbuf ? &p.tmCbuf : &p.tmC;
-#pragma unroll
-        for (int g = 0; g < CW / 32; ++g) {
-          const int c0 = w.col0 + h * CW + g * 32;
-          const int r0 = w.row0 + q * 32;
-          if (c0 < p.N && r0 < p.M) {   // warp-uniform
-            const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
-            if (lane == 0) {   // the store that last used this staging tile has read it
-              if (sbufs == 2u) tma_store_wait_read_1(); else tma_store_wait_read();
-            }
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              sts128(stg + lane * 128 + ((c ^ (lane & 7)) * 16),
-                     with_bias(g * 32 + c * 4, make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1],
-                                                           acc[g * 32 + c * 4 + 2], acc[g * 32 + c * 4 + 3])));
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(cmap, stg, c0, r0, w.zc);
-              tma_store_commit();
-            }
-            ++pc;
-          }
-        }
-      } else if (p.os_on) {
-        // Rows are strided pixels (one phase of a strided data gradient), which no tiled tensor map can
-        // describe.  Same staging tile as above, but the warp itself carries each 32x32 piece out: a
-        // lane stages its own row, then eight lanes together write one row's 128 bytes, four rows per
-        // instruction - whole 128-byte segments instead of 32 scattered 16-byte stores.
-        const uint32_t stg = stg0;
-        const int row = w.row0 + q * 32 + lane;
-        long long row_off = -1;   // rows >= M have no pixel
-        if (row < p.M) {
-          const int img = row / p.os_uv, r = row - img * p.os_uv;
-          const int u = r / p.os_v, v = r - u * p.os_v;
-          row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
-        }
-        const int sub = lane >> 3, chunk = lane & 7;
-#pragma unroll
-        for (int g = 0; g < CW / 32; ++g) {
-          const int c0 = w.col0 + h * CW + g * 32;
-          if (c0 < p.N && w.row0 + q * 32 < p.M) {   // warp-uniform
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              sts128(stg + lane * 128 + ((c ^ (lane & 7)) * 16),
-                     with_bias(g * 32 + c * 4, make_float4(acc[g * 32 + c * 4], acc[g * 32 + c * 4 + 1],
-                                                           acc[g * 32 + c * 4 + 2], acc[g * 32 + c * 4 + 3])));
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = i * 4 + sub;
-              const long long off = __shfl_sync(0xffffffffu, row_off, r);
-              const float4 v = lds128(stg + r * 128 + ((chunk ^ (r & 7)) * 16));
-              if (off >= 0 && c0 + chunk * 4 < p.N)   // p.N is a multiple of 4 here: a vector is whole or absent
-                *reinterpret_cast<float4*>(w.out + off + c0 + chunk * 4) = v;
-            }
-            __syncwarp();   // the piece has been read before the next one overwrites it
-          }
-        }
-      } else {
-        const int row = w.row0 + q * 32 + lane;
-        if (row < p.M) {
-          const long long row_off = static_cast<long long>(row) * p.ldc;
-          float* dst = w.out + row_off + w.col0 + h * CW;
-          const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
-          if (p.vec4_ok) {
-#pragma unroll
-            for (int j = 0; j < CW; j += 4) {
-              if (j + 3 < ncols) {
-                *reinterpret_cast<float4*>(dst + j) = with_bias(j, make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]));
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (j + e < ncols) dst[j + e] = acc[j + e];
+          for (int g = 0; g < PIECES; ++g) {
+            tmem_wait_ld();
+            float (&cur)[16] = (g & 1) ? vb : va;
+            float (&nxt)[16] = (g & 1) ? va : vb;
+            if (g + 1 < PIECES) {
+              tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
+            } else {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (CTAS == 2 && rank != 0)
+                  arrive_remote(leader_addr(&bar_tmem_empty[buf]));
+                else
+                  mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
               }
             }
-          } else {
 #pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (j < ncols) dst[j] = acc[j];
+            for (int j = 0; j < 16; ++j) acc[g * 16 + j] += cur[j];
+          }
+          ++ch;
+        }
+        const bool last = c + 1 >= nchunks;
+        if (!last && ++since < p.flush_chunks) continue;
+        // ---- fused bias row (optional): what the engine's linear_dual2D_row(C, bias, 1, 1, 0) does right
+        // after the product - one FP32 add per element, padding columns forced to zero.  Applied to
+        // each 4-column vector of the complete sum on its way out, so that no more than a few bias values are live.
+        auto with_bias = [&](int j, float4 v) -> float4 {
+          if (!last) return v;
+          if (p.scale_on) {   // what a separate y = alpha*x + 0 kernel would store: one fused multiply-add per element
+            v.x = fmaf(v.x, p.alpha, 0.0f); v.y = fmaf(v.y, p.alpha, 0.0f);
+            v.z = fmaf(v.z, p.alpha, 0.0f); v.w = fmaf(v.w, p.alpha, 0.0f);
+          }
+          if (p.bias == nullptr) return v;
+          const int cc = w.col0 + h * CW + j;   // a multiple of 4, like p.N: all four columns exist or none
+          if (cc >= p.N) return v;
+          const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + cc));
+          v.x = (cc + 0 < p.bias_width) ? v.x + b.x : 0.0f;
+          v.y = (cc + 1 < p.bias_width) ? v.y + b.y : 0.0f;
+          v.z = (cc + 2 < p.bias_width) ? v.z + b.z : 0.0f;
+          v.w = (cc + 3 < p.bias_width) ? v.w + b.w : 0.0f;
+          return v;
+        };
+        // The common case has neither: keep its loops free of the per-vector tests (measured: the tests cost more
+        // than the stores they guard).
+        const bool plain = !(last && (p.bias != nullptr || p.scale_on));
+        // what is already in memory for this vector (later flushes of a tile)
+        auto plus_old = [&](float4 v, const float* src) -> float4 {
+          if (first) return v;
+          const float4 o = *reinterpret_cast<const float4*>(src);
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+          return v;
+        };
+        // ---- store; the MMA warp is already filling the TMEM buffers with the next chunks meanwhile
+        if (use_tma) {
+          // Each drain warp owns a 32-row x CW-column block.  32x32 pieces go through a
+          // swizzled 4 KB staging tile (row r, 16-byte chunk c at r*128 + ((c ^ (r & 7)) * 16):
+          // conflict-free for the row-per-lane writes) and leave as one TMA store each, which
+          // writes whole 128-byte row segments and clips rows >= M and columns >= N.  With two
+          // staging tiles per warp a piece is staged while the previous one is still being read.
+          // Later flushes of a tile leave as TMA add-reductions, after the earlier ones have completed.
+          const CUtensorMap* cmap = w.to_cbuf ? &p.tmCbuf : &p.tmC;
+          if (!first) {
+            if (lane == 0) tma_store_wait_all();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int g = 0; g < CW / 32; ++g) {
+            const int c0 = w.col0 + h * CW + g * 32;
+            const int r0 = w.row0 + q * 32;
+            if (c0 < p.N && r0 < p.M) {   // warp-uniform
+              const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
+              if (lane == 0) {   // the store that last used this staging tile has read it
+                if (sbufs == 2u) tma_store_wait_read_1(); else tma_store_wait_read();
+              }
+              __syncwarp();
+              if (plain) {
+#pragma unroll
+                for (int cq = 0; cq < 8; ++cq)
+                  sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),
+                         make_float4(acc[g * 32 + cq * 4], acc[g * 32 + cq * 4 + 1], acc[g * 32 + cq * 4 + 2],
+                                     acc[g * 32 + cq * 4 + 3]));
+              } else {
+#pragma unroll
+                for (int cq = 0; cq < 8; ++cq)
+                  sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),
+                         with_bias(g * 32 + cq * 4, make_float4(acc[g * 32 + cq * 4], acc[g * 32 + cq * 4 + 1],
+                                                                acc[g * 32 + cq * 4 + 2], acc[g * 32 + cq * 4 + 3])));
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (first) tma_store_3d(cmap, stg, c0, r0, w.zc);
+                else tma_reduce_add_3d(cmap, stg, c0, r0, w.zc);
+                tma_store_commit();
+              }
+              ++pc;
+            }
+          }
+        } else if (p.os_on) {
+          // Rows are strided pixels (one phase of a strided data gradient), which no tiled tensor map can
+          // describe.  Same staging tile as above, but the warp itself carries each 32x32 piece out: a
+          // lane stages its own row, then eight lanes together write one row's 128 bytes, four rows per
+          // instruction - whole 128-byte segments instead of 32 scattered 16-byte stores.
+          const uint32_t stg = stg0;
+          const int row = w.row0 + q * 32 + lane;
+          long long row_off = -1;   // rows >= M have no pixel
+          if (row < p.M) {
+            const int img = row / p.os_uv, r = row - img * p.os_uv;
+            const int u = r / p.os_v, v = r - u * p.os_v;
+            row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
+          }
+          const int sub = lane >> 3, chunk = lane & 7;
+#pragma unroll
+          for (int g = 0; g < CW / 32; ++g) {
+            const int c0 = w.col0 + h * CW + g * 32;
+            if (c0 < p.N && w.row0 + q * 32 < p.M) {   // warp-uniform
+#pragma unroll
+              for (int cq = 0; cq < 8; ++cq)
+                sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),
+                       make_float4(acc[g * 32 + cq * 4], acc[g * 32 + cq * 4 + 1], acc[g * 32 + cq * 4 + 2],
+                                   acc[g * 32 + cq * 4 + 3]));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = i * 4 + sub;
+                const long long off = __shfl_sync(0xffffffffu, row_off, r);
+                const float4 v = lds128(stg + r * 128 + ((chunk ^ (r & 7)) * 16));
+                if (off >= 0 && c0 + chunk * 4 < p.N) {   // p.N is a multiple of 4 here: a vector is whole or absent
+                  float* dst = w.out + off + c0 + chunk * 4;
+                  if (plain && first) *reinterpret_cast<float4*>(dst) = v;
+                  else *reinterpret_cast<float4*>(dst) = with_bias(g * 32 + chunk * 4, plus_old(v, dst));
+                }
+              }
+              __syncwarp();   // the piece has been read before the next one overwrites it
+            }
+          }
+        } else {
+          const int row = w.row0 + q * 32 + lane;
+          if (row < p.M) {
+            const long long row_off = static_cast<long long>(row) * p.ldc;
+            float* dst = w.out + row_off + w.col0 + h * CW;
+            const int ncols = p.N - (w.col0 + h * CW);  // columns left in this row segment
+            if (p.vec4_ok) {
+#pragma unroll
+              for (int j = 0; j < CW; j += 4) {
+                if (j + 3 < ncols) {
+                  if (plain && first)
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                  else
+                    *reinterpret_cast<float4*>(dst + j) =
+                        with_bias(j, plus_old(make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]), dst + j));
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (j + e < ncols) dst[j + e] = first ? acc[j + e] : dst[j + e] + acc[j + e];
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (j < ncols) dst[j] = first ? acc[j] : dst[j] + acc[j];
+            }
           }
         }
+        if (last) break;
+        first = false;
+        since = 0;
+#pragma unroll
+        for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
       }
+      if (!alive) break;
     }
     // stores still in flight read this CTA's shared memory: let them finish before exit
     if (lane == 0) tma_store_wait_all();
@@ -764,6 +826,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   // ---- common exit: everyone arrives here, also after a give-up
   tc_fence_before();
   __syncthreads();
+  if (p.clock_acc != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    atomicAdd(p.clock_acc + 0, static_cast<unsigned long long>(clock64() - clk_t0));
+    atomicAdd(p.clock_acc + 1, globaltimer_ns() - clk_g0);
+    atomicAdd(p.clock_acc + 2, 1ull);
+  }
   if (CTAS == 2) cluster_sync();
   if (warp == 2) {
     tc_fence_after();

@@ -157,6 +157,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
                "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// Tiled add-reduction shared -> global: every element of the box is added (FP32, round to nearest) to the
+// element in memory; clipping and coordinates as for the store.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -365,6 +372,13 @@ __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
   return pred != 0;
+}
+
+// Nanoseconds of the GPU's global timer (same time base for every SM).
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 // What the tensor core itself makes of an FP32 operand under kind::tf32: the low 13

@@ -138,6 +138,7 @@ SIGNATURES = {
     "cu32_get_tune": [c_char_p, POINTER(c_int)],
     "cu32_read_status": [POINTER(c_int)],
     "cu32_selftest_wait_giveup": [c_int64, ctypes.c_longlong],
+    "cu32_read_clock": [POINTER(ctypes.c_ulonglong)],
 }
 
 
@@ -196,6 +197,14 @@ def decode_status(word: int) -> str:
     roles = {1: "tma-producer", 2: "splitter", 3: "mma(operands)", 4: "mma(tmem-buffer)", 5: "drainer",
              7: "self-test"}
     return f"{roles.get(word >> 24, word >> 24)} gave up at stage/buffer {(word >> 16) & 0xFF}, iteration {word & 0xFFFF}"
+
+
+def read_clock():
+    """(SM cycles, nanoseconds, launches) accumulated by the contraction kernels since the last read, while the
+    "clock" tuning key is on; cycles / nanoseconds is the SM clock in GHz the kernels ran at."""
+    v = (ctypes.c_ulonglong * 3)()
+    _check(load().cu32_read_clock(v), "cu32_read_clock")
+    return int(v[0]), int(v[1]), int(v[2])
 
 
 def selftest_wait_giveup(stream: int, limit_cycles: int) -> None:

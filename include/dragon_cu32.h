@@ -412,6 +412,9 @@ CU32_API int cu32_conv3D_GemmR_biased(const int64_t* streams, int length, const 
  *              for their low-order parts (1..ring_raw) and store-staging tiles per drain warp (1, 2);
  *              0 = choose from the shape (default).  A combination that does not fit in shared memory
  *              makes the call return cudaErrorInvalidValue.
+ *   "clock"    1 = CTA 0 of every contraction launch adds its run time in SM cycles and in nanoseconds to a
+ *              device-side accumulator (cu32_read_clock); 0 = off (default)
+ *   "last_tile" (read only) tile configuration of the most recent contraction call of this process
  *   "arrive_release"  1 = barrier arrivals between the two CTAs of a pair carry a cluster-scope release
  *              (diagnostics: results must not depend on it); 0 = default
  * Returns 0, or CU32_E_ARG for an unknown key / out-of-range value. */
@@ -422,6 +425,11 @@ CU32_API int cu32_get_tune(const char* key, int* value);
  * out of its bounded waits, else (role<<24 | stage<<16 | iteration) of the first one.
  * Synchronises the device; resets the word.  For tests and diagnostics only. */
 CU32_API int cu32_read_status(int* status);
+
+/* Reads and clears the clock accumulator the "clock" tuning key switches on: out3 = {SM cycles, nanoseconds,
+ * launches} summed over the contraction launches since the last read.  cycles / nanoseconds is the SM clock in
+ * GHz the kernels actually ran at.  Synchronises the device.  No counterpart in the reference. */
+CU32_API int cu32_read_clock(unsigned long long* out3);
 
 /* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits, for at most
  * limit_cycles SM clock cycles (1 .. 100 000 000), on a barrier nobody arrives at.  The wait runs out, the kernel
