@@ -933,6 +933,86 @@ static int bmm_any(int form, bool x3, const int64_t* s, int n, const float* A, c
   return run_gemm(c);
 }
 
+// ---- attention scores: batched A * B^T, scale and row softmax in one pass (no counterpart among the reference's
+// natives: its attention block runs batchMatMulT2, linear2D (the 1/sqrt(d) scale), row_max, row_softmax and
+// div2D_field as five kernels over the score tensor, nn/unit/complex/block/ImageMHA.java:67-68,
+// CudaFloat32EngineBase.java:5738-5775)
+}  // extern "C"
+namespace dragon {
+// Row softmax in place, one warp per row: y = exp(x - max) / sum over the first `width` columns of each row of
+// `stride` floats, padding columns zeroed.  Used when a row does not fit the fused kernel.
+__global__ void row_softmax_kernel(float* __restrict__ P, long long rows, int stride, int width) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    float* x = P + row * stride;
+    float m = -INFINITY;
+    for (int c = lane; c < width; c += 32) m = fmaxf(m, x[c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      const float e = expf(x[c] - m);
+      x[c] = e;
+      sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float rinv = 1.0f / sum;
+    for (int c = lane; c < stride; c += 32) x[c] = c < width ? x[c] * rinv : 0.f;
+  }
+}
+}  // namespace dragon
+extern "C" {
+int cu32_batchMatMulT2_softmax(const int64_t* s, int n, const float* A, const float* B, float* P, int Batch, int N,
+                               int CM, int BM, int K, float alpha) {
+  load_env_once();
+  cudaStream_t st;
+  if (int rc = check_streams(s, n, &st)) return rc;
+  if (!A || !B || !P) return CU32_E_NULL;
+  if (Batch <= 0 || N <= 0 || CM <= 0 || BM <= 0 || K <= 0 || CM < BM) return CU32_E_DIM;
+  if ((K & 3) || (CM & 3) || !aligned16(A) || !aligned16(B) || !aligned16(P)) return CU32_E_ALIGN;
+  if (static_cast<long long>(Batch) * N * CM >= (1LL << 40)) return CU32_E_DIM;
+  const int nkb = (K + 31) / 32;
+  if (CM > 512 || nkb > g_kc.load()) {
+    // rows too long for the two TMEM buffers, or a reduction longer than one in-TMEM chunk (the softmax turns the
+    // scores' absolute error into relative error of P, so the chunk is not stretched): scaled product, then a row
+    // softmax in place
+    if (int rc = bmm_any(FORM_T2, true, s, n, A, B, P, Batch, N, CM, BM, K, true, alpha)) return rc;
+    const long long rows = static_cast<long long>(Batch) * N;
+    long long blocks = (rows + 7) / 8;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    row_softmax_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(P, rows, CM, BM);
+    return static_cast<int>(cudaPeekAtLastError());
+  }
+  if (!load_driver_entry_points()) return CU32_E_DRIVER;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  const uint64_t nb = static_cast<uint64_t>(Batch);
+  if (int rc = make_map3(&p.tmA, A, K, N, nb, K, static_cast<uint64_t>(N) * K, 32, 128, false)) return rc;
+  if (int rc = make_map3(&p.tmB, B, K, BM, nb, K, static_cast<uint64_t>(BM) * K, 32, 128, false)) return rc;
+  if (int rc = make_map3(&p.tmC, P, CM, N, nb, CM, static_cast<uint64_t>(N) * CM, 32, 32, false)) return rc;
+  p.C = P; p.ldc = CM; p.c_stride = static_cast<long long>(N) * CM;
+  p.M = N; p.N = CM;
+  p.nkb_total = nkb;
+  p.tiles_m = (N + 255) / 256;
+  p.tiles_n = (CM + 255) / 256;
+  p.unit_tiles = p.tiles_n;
+  p.gz = 1;
+  p.kc = nkb;            // the whole reduction is one chunk, so a tile's result is complete in TMEM
+  choose_rings(&p);
+  if (p.ring_raw == 0) { p.ring_raw = 3; p.ring_lo = 2; p.store_bufs = 1; }   // leaves room for the row statistics
+  p.vec4_ok = 1; p.tma_store = 1;
+  p.alpha = alpha; p.sm_width = BM;
+  cudaError_t e;
+  p.status = status_word_ptr(&e);
+  if (!p.status) return static_cast<int>(e);
+  g_last_tile = TILE_2x256;
+  e = launch_gemm_kk_softmax(p, Batch, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
 // ---- data gradient / transposed convolution + bias row in one pass (no counterpart among the reference's natives:
 // the Java engine's deconv3D_biased runs Cuda_function.linear_dual2D_row(Y, bias, 1, 1, 0) as a second kernel,
 // CudaFloat32EngineBase.java:2620-2650).  Bias has IC entries (the channels of the output), width <= IC are real.

@@ -51,6 +51,8 @@ cudaError_t launch_gemm_kk(int tile_cfg, bool x3, bool im2col, const GemmParams&
 cudaError_t launch_gemm_kn(int tile_cfg, bool x3, bool im2col, const GemmParams& p, int grid_z,
                            cudaStream_t stream);
 cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
+//   KK + row softmax : P = softmax_rows(alpha * A * B^T), at most 512 columns, reduction of at most kc k-blocks
+cudaError_t launch_gemm_kk_softmax(const GemmParams& p, int grid_z, cudaStream_t stream);
 //   NN + im2col : A[K][M], B = im2col walk over an NHWC image, K = output pixels (weight gradient; FP32-accurate only)
 cudaError_t launch_gemm_nn_im2col(int tile_cfg, const GemmParams& p, int grid_z, cudaStream_t stream);
 
@@ -92,10 +94,12 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
     if (units < 1) return cudaErrorLaunchOutOfResources;
     __atomic_store_n(&resident_units[dev & 63], units, __ATOMIC_RELEASE);
   }
-  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * grid_z;
-  const long long grid_units = total_tiles < units ? total_tiles : units;
   GemmParams q = p;
   q.zcount = grid_z;
+  if (q.unit_tiles < 1) q.unit_tiles = 1;
+  // work units: tiles, or (softmax mode) groups of unit_tiles tiles that one CTA pair takes in a row
+  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * grid_z / (Cfg::SOFTMAX ? q.unit_tiles : 1);
+  const long long grid_units = total_tiles < units ? total_tiles : units;
   // Rings: 0 = the balanced default (as many raw + lo pairs as fit beside one staging tile per drain warp).
   if (q.ring_raw == 0) { q.ring_raw = Cfg::STAGES; q.ring_lo = Cfg::STAGES; }
   if (q.store_bufs == 0) q.store_bufs = 1;

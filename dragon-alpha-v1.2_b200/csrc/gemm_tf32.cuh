@@ -93,6 +93,8 @@ struct GemmParams {
   // image * os_sn + u * os_su + v * os_sv; stores go straight from registers.
   int scale_on;         // multiply every output element by alpha on its way out (one FP32 rounding)
   float alpha;
+  int unit_tiles;       // tiles a CTA (pair) takes in a row before moving on: 1, or tiles_n in the softmax mode
+  int sm_width;         // softmax mode: columns < sm_width take part, the others (pitch padding) are stored as 0
   int ztaps;            // > 0: weight gradient, the z index is slice * ztaps + filter tap
   int os_on, os_uv, os_v;
   long long os_sn, os_su, os_sv;
@@ -100,10 +102,15 @@ struct GemmParams {
 
 enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5, ROLE_SELFTEST = 7 };
 
-template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false>
+template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false, bool SOFTMAX_ = false>
 struct GemmCfg {
   static constexpr int BN = BN_, CTAS = CTAS_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, X3 = X3_, IM2COL = IM2COL_;
+  // SOFTMAX: the rows of the product (at most 512 columns: the two TMEM buffers side by side) are normalised
+  // with a softmax before they leave the SM - the attention scores never exist in memory.
+  static constexpr bool SOFTMAX = SOFTMAX_;
+  static_assert(!SOFTMAX_ || (BN_ == 256 && CTAS_ == 2 && X3_ && !A_MN_ && !B_MN_ && !IM2COL_),
+                "the row softmax is built on the 256x256 pair tile of the A * B^T form");
   static constexpr int BM = 128;            // rows of A (and TMEM lanes) per CTA
   static constexpr int BK = 32;             // one 128-byte swizzle row of FP32
   static constexpr int BN_CTA = BN / CTAS;  // B columns staged per CTA
@@ -112,7 +119,7 @@ struct GemmCfg {
   static constexpr int HI_BYTES = A_BYTES + B_BYTES;   // bytes one k-block brings in by TMA: a raw slot [A][B]
   // Shared memory: [raw ring][lo ring (FP32-accurate mode)][store staging]; the ring lengths are launch
   // parameters.  MAX_DYN_SMEM leaves room for the static barriers inside the 227 KB a CTA may use.
-  static constexpr int MAX_DYN_SMEM = 226 * 1024;
+  static constexpr int MAX_DYN_SMEM = (SOFTMAX_ ? 220 : 226) * 1024;   // the softmax mode keeps 4 KB of row statistics in static shared memory
   static constexpr int MAX_RING = 8;
   static constexpr int STAGING_TILE = 4096;   // one 32x32 FP32 piece
   // the default, balanced rings: as many (raw + lo) pairs as fit beside one staging tile per drain warp
@@ -187,6 +194,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   __shared__ __align__(8) uint64_t bar_empty[8];
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ __align__(8) uint64_t bar_red[2];       // softmax: the drain warps have published their row maxima / sums
+  __shared__ float red[Cfg::SOFTMAX ? 2 : 1][2][2][Cfg::SOFTMAX ? Cfg::BM : 1];   // softmax: [parity][max, sum][column half][row]
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int abort_flag;
 
@@ -209,6 +218,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   const long long tile_first = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const long long tile_step = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int kc = p.kc;
+  // The i-th tile of this CTA (pair), or -1 past the end.  A unit is one tile, except in the softmax mode,
+  // where it is the tiles_n tiles that hold whole rows: those are taken one after the other.
+  const int subs = Cfg::SOFTMAX ? p.unit_tiles : 1;
+  const long long total_units = total_tiles / subs;
+  auto tile_at = [&](long long i) -> long long {
+    const long long u = tile_first + (Cfg::SOFTMAX ? i / subs : i) * tile_step;
+    if (u >= total_units) return -1;
+    return Cfg::SOFTMAX ? u * subs + i % subs : u;
+  };
 
   auto decode = [&](long long t) -> TileWork {
     constexpr int GROUP = 8;
@@ -217,8 +235,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     const int per_group = GROUP * p.tiles_n;
     const int g_first = (r / per_group) * GROUP;
     const int g_size = min(p.tiles_m - g_first, GROUP);
-    const int tm = g_first + (r % per_group) % g_size;
-    const int tn = (r % per_group) / g_size;
+    const int tm = Cfg::SOFTMAX ? r / p.tiles_n : g_first + (r % per_group) % g_size;
+    const int tn = Cfg::SOFTMAX ? r % p.tiles_n : (r % per_group) / g_size;
     TileWork w;
     w.row0 = (tm * CTAS + static_cast<int>(rank)) * Cfg::BM;
     w.col0 = tn * BN;
@@ -270,6 +288,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tmem_full[b]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[b]), Cfg::DRAIN_WARPS * CTAS);
+      mbar_init(smem_u32(&bar_red[b]), Cfg::DRAIN_WARPS);
     }
     fence_mbar_init();
     tma_prefetch_desc(&p.tmA);
@@ -324,7 +343,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       // L2, evict each other in exactly the order they are needed again).
       const uint64_t pol_a = p.l2_hints ? l2_policy_evict_last() : 0ull;
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
-      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+      for (long long i_tile = 0, t; alive && (t = tile_at(i_tile)) >= 0; ++i_tile) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == R) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
@@ -444,7 +463,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       uint32_t l = 0;     // lo slot = it % L
       uint32_t kk = 0;    // k-blocks already in the current chunk
       bool alive = true;
-      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+      for (long long i_tile = 0, t; alive && (t = tile_at(i_tile)) >= 0; ++i_tile) {
         const TileWork w = decode(t);
         kk = 0;
         for (int i = 0; i < w.nkb; ++i, ++it) {
@@ -532,7 +551,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       uint32_t l = 0;             // lo slot = it % L
       uint32_t sp = 0, php = 0;   // raw slot and phase parity of k-block it - L, the previous user of lo slot l
       bool alive = true;
-      for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+      for (long long i_tile = 0, t; alive && (t = tile_at(i_tile)) >= 0; ++i_tile) {
         const TileWork w = decode(t);
         for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == R) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_full_tma[s]), ph, &abort_flag)) {
@@ -613,8 +632,141 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     const uint32_t sbufs = static_cast<uint32_t>(p.store_bufs);
     const uint32_t stg0 = stg_base + (warp - Cfg::DRAIN_WARP0) * sbufs * Cfg::STAGING_TILE;
     bool alive = true;
-    for (long long t = tile_first; alive && t < total_tiles; t += tile_step) {
+    for (long long i_tile = 0, t; alive && (t = tile_at(Cfg::SOFTMAX ? i_tile * subs : i_tile)) >= 0; ++i_tile) {
       const TileWork w = decode(t);
+      if constexpr (Cfg::SOFTMAX) {
+        // ---------------------------------------------------------------- row softmax of the finished products
+        // The unit's tiles (one chunk each: the host makes kc cover the whole reduction) sit side by side in the
+        // TMEM buffers: this thread owns row q*32 + lane and, in each buffer, the CW columns of its half h.
+        //   pass 1  x' = fma(x, alpha, 0), row maximum     (the two halves exchange through shared memory)
+        //   pass 2  e = exp(x' - max) written back to TMEM, row sum (exchanged likewise)
+        //   pass 3  e * (1 / sum) -> staging tile -> TMA store; a buffer is handed back after its last load
+        // Same values as the engine's sequence scale -> row_max -> row_softmax -> div2D_field up to the order of
+        // the row sum and the reciprocal (one rounding each).
+        const uint32_t upar = static_cast<uint32_t>(i_tile) & 1u;
+        bool ok = true;
+        for (int b = 0; ok && b < subs; ++b) {
+          const uint32_t cb = ch + b;
+          if (!mbar_wait(smem_u32(&bar_tmem_full[cb & 1u]), (cb >> 1) & 1u, &abort_flag)) {
+            if (lane == 0) give_up(ROLE_DRAIN, static_cast<int>(cb & 1u), b);
+            ok = false;
+          }
+        }
+        if (!ok) { alive = false; break; }
+        tc_fence_after();
+        const int myrow = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        constexpr int PIECES = CW / 16;
+        // ---- pass 1
+        float m = -INFINITY;
+        for (int b = 0; b < subs; ++b) {
+          const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
+          const int c_first = b * BN + h * CW;
+          float va[16], vb[16];
+          tmem_ld_32x16(t0, va);
+#pragma unroll
+          for (int g = 0; g < PIECES; ++g) {
+            tmem_wait_ld();
+            float (&cur)[16] = (g & 1) ? vb : va;
+            float (&nxt)[16] = (g & 1) ? va : vb;
+            if (g + 1 < PIECES) tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c_first + g * 16 + j < p.sm_width) m = fmaxf(m, fmaf(cur[j], p.alpha, 0.0f));
+          }
+        }
+        red[upar][0][h][myrow] = m;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_red[0]));
+        if (!mbar_wait(smem_u32(&bar_red[0]), upar, &abort_flag)) {
+          if (lane == 0) give_up(ROLE_DRAIN, 20, 0);
+          alive = false;
+          break;
+        }
+        m = fmaxf(red[upar][0][0][myrow], red[upar][0][1][myrow]);
+        // ---- pass 2
+        float sum = 0.0f;
+        for (int b = 0; b < subs; ++b) {
+          const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
+          const int c_first = b * BN + h * CW;
+          float va[16], vb[16], ev[16];
+          tmem_ld_32x16(t0, va);
+#pragma unroll
+          for (int g = 0; g < PIECES; ++g) {
+            tmem_wait_ld();
+            float (&cur)[16] = (g & 1) ? vb : va;
+            float (&nxt)[16] = (g & 1) ? va : vb;
+            if (g + 1 < PIECES) tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
+            if (g > 0) tmem_wait_st();   // the previous piece has left ev
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              ev[j] = (c_first + g * 16 + j < p.sm_width) ? expf(fmaf(cur[j], p.alpha, 0.0f) - m) : 0.0f;
+              sum += ev[j];
+            }
+            tmem_st_32x16(t0 + g * 16, ev);
+          }
+          tmem_wait_st();
+        }
+        red[upar][1][h][myrow] = sum;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_red[1]));
+        if (!mbar_wait(smem_u32(&bar_red[1]), upar, &abort_flag)) {
+          if (lane == 0) give_up(ROLE_DRAIN, 21, 0);
+          alive = false;
+          break;
+        }
+        const float rinv = 1.0f / (red[upar][1][0][myrow] + red[upar][1][1][myrow]);
+        // ---- pass 3
+        for (int b = 0; b < subs; ++b) {
+          const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
+          const uint32_t buf = (ch + b) & 1u;
+#pragma unroll
+          for (int g = 0; g < CW / 32; ++g) {
+            float va[16], vb[16];
+            tmem_ld_32x16(t0 + g * 32, va);
+            tmem_ld_32x16(t0 + g * 32 + 16, vb);
+            const int c0 = b * BN + h * CW + g * 32;
+            const int r0 = w.row0 + q * 32;
+            const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
+            const bool inside = c0 < p.N && r0 < p.M;   // warp-uniform
+            if (inside) {
+              if (lane == 0) {   // the store that last used this staging tile has read it
+                if (sbufs == 2u) tma_store_wait_read_1(); else tma_store_wait_read();
+              }
+              __syncwarp();
+            }
+            tmem_wait_ld();
+            if (g + 1 == CW / 32) {
+              // this buffer's last values have left TMEM: hand it back to the MMA issuer
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (rank != 0) arrive_remote(leader_addr(&bar_tmem_empty[buf]));
+                else mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+              }
+            }
+            if (inside) {
+#pragma unroll
+              for (int cq = 0; cq < 4; ++cq)
+                sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),
+                       make_float4(va[cq * 4] * rinv, va[cq * 4 + 1] * rinv, va[cq * 4 + 2] * rinv, va[cq * 4 + 3] * rinv));
+#pragma unroll
+              for (int cq = 0; cq < 4; ++cq)
+                sts128(stg + lane * 128 + (((cq + 4) ^ (lane & 7)) * 16),
+                       make_float4(vb[cq * 4] * rinv, vb[cq * 4 + 1] * rinv, vb[cq * 4 + 2] * rinv, vb[cq * 4 + 3] * rinv));
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&p.tmC, stg, c0, r0, w.zc);
+                tma_store_commit();
+              }
+              ++pc;
+            }
+          }
+        }
+        ch += static_cast<uint32_t>(subs);
+        continue;
+      }
       float acc[CW];
 #pragma unroll
       for (int j = 0; j < CW; ++j) acc[j] = 0.0f;

@@ -328,6 +328,7 @@ JNIEXPORT void JNICALL JNAME_DX(dconv3D_1deltaX_1ksImsR_1biased)(JNIEnv* env, jc
 BMM_SCALED(batchMatMul_1scaled, cu32_batchMatMul_scaled)
 BMM_SCALED(batchMatMulT1_1scaled, cu32_batchMatMulT1_scaled)
 BMM_SCALED(batchMatMulT2_1scaled, cu32_batchMatMulT2_scaled)
+BMM_SCALED(batchMatMulT2_1softmax, cu32_batchMatMulT2_softmax)
 
 // ---- Cuda_dconv3D_deltaW (Java declarations: Cuda_dconv3D_deltaW.java:288-640)
 #define JNAME_DW(method) Java_z_dragon_engine_cuda_impl_math_Cuda_1dconv3D_1deltaW_##method

@@ -118,6 +118,7 @@ SIGNATURES = {
     "cu32_batchMatMul_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_batchMatMulT1_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_batchMatMulT2_scaled": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
+    "cu32_batchMatMulT2_softmax": [_sp, _I, _fp, _fp, _fp, _I, _I, _I, _I, _I, ctypes.c_float],
     "cu32_dconv3D_deltaX_s1_biased": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 7 + [_fp, _I],
     "cu32_dconv3D_deltaX_ksImsR_biased": [_sp, _I, _fp, _I, _I, _fp, _I, _I, _fp] + [_I] * 9 + [_fp, _I],
     "cu32_matMul_biased": [_sp, _I, _fp, _fp, _fp, _fp, _I, _I, _I, _I],
@@ -386,6 +387,11 @@ class Cuda_batchMatMul:
     @staticmethod
     def batchMatMulT2_scaled(streamArray, length, dA, dB, dC, Batch, N, CM, BM, K, alpha):
         Cuda_batchMatMul._scaled("batchMatMulT2_scaled", streamArray, length, dA, dB, dC, Batch, N, CM, BM, K, alpha)
+
+    @staticmethod
+    def batchMatMulT2_softmax(streamArray, length, dA, dB, dP, Batch, N, CM, BM, K, alpha):
+        """P = softmax over rows of alpha * A * B^T in one pass (scores never stored unnormalised)."""
+        Cuda_batchMatMul._scaled("batchMatMulT2_softmax", streamArray, length, dA, dB, dP, Batch, N, CM, BM, K, alpha)
 
 
 class Cuda_conv3D:

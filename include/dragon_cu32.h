@@ -396,6 +396,20 @@ CU32_API int cu32_conv3D_GemmR_biased(const int64_t* streams, int length, const 
                              int OW, int N, int IC, int OC, int sh, int sw, int ph, int pw,
                              const float* dBias, int width);
 
+/* Attention scores in one pass (no counterpart among the reference's natives).
+ * P[b][N, CM] = softmax over each row of alpha * A[b][N,K] * B[b][BM,K]^T: columns 0..BM-1 hold the softmax,
+ * the pitch padding BM..CM-1 holds zeros.  Arguments as cu32_batchMatMulT2 plus the scale.
+ * What it replaces in the reference's attention block (nn/unit/complex/block/ImageMHA.java:67-68): batchMatMulT2,
+ * then linear2D (sdiv by sqrt(d), Engine.java:4002), then softmax2D = row_max + row_softmax + div2D_field
+ * (CudaFloat32EngineBase.java:5738-5775) - five kernels that write the score tensor three times and read it four.
+ * For rows of at most 512 columns and K <= 64 the product stays in tensor memory until the row is normalised, so
+ * the scores are written once and never read; longer rows or reductions run the scaled product followed by one
+ * in-place row softmax.  Values: x' = fma(x, alpha, 0), e = expf(x' - max x'), p = e * (1 / sum e); they differ
+ * from the five-kernel sequence only in the order of the row sum and in multiplying by the reciprocal instead of
+ * dividing (a few units in the last place). */
+CU32_API int cu32_batchMatMulT2_softmax(const int64_t* streams, int length, const float* dA, const float* dB,
+                                        float* dP, int Batch, int N, int CM, int BM, int K, float alpha);
+
 /* ------------------------------------------------------------------ library control
  * No counterpart in the reference (its only native-side switch is a compile-time macro). */
 

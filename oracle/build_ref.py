@@ -33,6 +33,7 @@ PROJECTS = {
     "bmm": ("ref_wrap_bmm.cu", "Cuda_batchMatMul/Cuda_batchMatMul", "libref_bmm.so"),
     "conv": ("ref_wrap_conv.cu", "Cuda_conv3D/Cuda_conv3D", "libref_conv.so"),
     "function": ("ref_wrap_function.cu", "Cuda_function/Cuda_function", "libref_function.so"),
+    "reduce": ("ref_wrap_reduce.cu", "Cuda_reduce/Cuda_reduce", "libref_reduce.so"),
     "deltax": ("ref_wrap_deltax.cu", "Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX", "libref_deltax.so"),
 }
 
@@ -99,11 +100,14 @@ def build(reference: Path, names: list[str], force: bool = False) -> list[Path]:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("DRAGON_REFERENCE_TREE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("DRAGON_REFERENCE_TREE"),
+                    help="root of the reference tree (or set DRAGON_REFERENCE_TREE)")
     ap.add_argument("--conv", action="store_true", help="also build Cuda_conv3D (about 25 minutes)")
     ap.add_argument("--deltax", action="store_true", help="also build Cuda_dconv3D_deltaX (long)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
-    names = ["matmul", "bmm", "function"] + (["conv"] if a.conv else []) + (["deltax"] if a.deltax else [])
+    if not a.reference:
+        ap.error("give --reference <tree> or set DRAGON_REFERENCE_TREE")
+    names = ["matmul", "bmm", "function", "reduce"] + (["conv"] if a.conv else []) + (["deltax"] if a.deltax else [])
     for p in build(Path(a.reference), names, a.force):
         print(p)

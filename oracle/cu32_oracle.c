@@ -17,6 +17,12 @@
  *   ks_remode / ks_remodev2 (filter workspace of the strided data gradient; GPU kernels, restated element by
  *   element)                                         dconv3D_dX_kernelSplit_remode_v1.cuh:28-66, _v2.cuh:31-66
  *   linear2D (y = alpha*x + beta, the attention block's scale; a GPU kernel)   Cuda_function/type1_linear2D.cuh:40-58
+ *   softmax2D (the engine's row softmax: row_max, row_softmax, div2D_field; GPU kernels, restated row by row - the
+ *   arithmetic per element is theirs, the order of the row sum is not: the kernels sum strided partial sums with
+ *   Kahan compensation through a tree, here one compensated sum runs along the row, so the results agree to a
+ *   few units in the last place and are pinned on the GPU with that tolerance)
+ *                                                    Cuda_reduce/row_max.cuh:60-105, row_softmax.cuh:45-120,
+ *                                                    Cuda_function/type1_div2D_field.cuh:42-68
  *   deconv3d_deltaW_naive (the Java check loop of the weight gradient; PARITY UNPINNED, see below)
  *                                                    ZUTIL-STD-1.2/src/z/util/math/vector/Tense.java:1276-1318
  *   linear_dual2D_row (the bias-row add the engine applies right after matMul / conv3D;
@@ -436,4 +442,34 @@ void oracle_deconv3D_deltaW_f64(const float* X, int IH, int IW, const float* del
  * with simdLinear4, micro.cuh:54-58: x * alpha + beta, which nvcc contracts to one fused multiply-add). */
 void oracle_linear2D(float alpha, const float* X, float beta, float* Y, long long length) {
   for (long long i = 0; i < length; i++) Y[i] = fmaf(X[i], alpha, beta);
+}
+
+/* Row softmax as the engine's softmax2D computes it (CudaFloat32EngineBase.java:5738-5775):
+ *   row_max      m = max over the whole row of `stride` floats, pitch padding included (row_max.cuh:60-105)
+ *   row_softmax  e = expf(x - m), zero beyond `width`; V = sum of e, Kahan-compensated, four elements per step
+ *                (row_softmax.cuh:62-75, micro.cuh:170-174)
+ *   div2D_field  y = e * (1 / V) + 0, zero beyond `width` (type1_div2D_field.cuh:42-68 with alpha = 1, beta = gamma = 0)
+ * stride is a multiple of 4. */
+void oracle_softmax2D(const float* X, float* Y, long long rows, int stride, int width) {
+    for (long long r = 0; r < rows; ++r) {
+        const float* x = X + r * stride;
+        float* y = Y + r * stride;
+        float m = -3.402823466e+38f;
+        for (int c = 0; c < stride; ++c) m = fmaxf(m, x[c]);
+        float v = 0.0f, comp = 0.0f;
+        for (int c = 0; c < stride; c += 4) {
+            float e[4];
+            for (int j = 0; j < 4; ++j) {
+                e[j] = expf(x[c + j] - m);
+                e[j] *= (float)((c + j) % stride < width);
+                y[c + j] = e[j];
+            }
+            const float dv = (e[0] + e[1] + e[2] + e[3]) - comp;
+            const float t = v + dv;
+            comp = (t - v) - dv;
+            v = t;
+        }
+        const float rv = 1.0f / (1.0f * v + 0.0f);
+        for (int c = 0; c < stride; ++c) y[c] = (c < width) ? (y[c] * rv + 0.0f) : 0.0f;
+    }
 }

@@ -185,6 +185,17 @@ class ref_loops:
         return Y
 
     @staticmethod
+    def softmax2D(X, width=None):
+        """Row softmax of X[..., stride] over the first `width` columns as the engine's three-kernel softmax2D
+        computes it (see oracle_softmax2D); padding columns come out 0."""
+        X = _c32(X)
+        stride = X.shape[-1]
+        width = stride if width is None else width
+        Y = np.empty_like(X)
+        lib().oracle_softmax2D(_f(X), _f(Y), ctypes.c_longlong(X.size // stride), stride, width)
+        return Y
+
+    @staticmethod
     def ks_remode(W, sh, sw, v2=True, fill=np.nan):
         """W [OC, FH, FW, IC] -> the kernel-split workspace as a flat array of sh*sw*OC*mCFH*mCFW*IC floats
         (dconv3D_dX_kernelSplit_remode_v1.cuh:28-66 / _v2.cuh:31-66); untouched elements keep `fill`."""
@@ -263,6 +274,18 @@ class f64:
         if CM is not None and CM > C.shape[2]:
             C = np.concatenate([C, np.zeros(C.shape[:2] + (CM - C.shape[2],))], axis=2)
         return C
+
+    @staticmethod
+    def softmax_rows(S, alpha=1.0, width=None):
+        """softmax over the last axis of alpha * S in FP64 (S float64 scores); columns >= width are padding: 0."""
+        S = np.asarray(S, np.float64) * np.float64(np.float32(alpha))
+        width = S.shape[-1] if width is None else width
+        Z = S[..., :width]
+        Z = np.exp(Z - Z.max(axis=-1, keepdims=True))
+        Z /= Z.sum(axis=-1, keepdims=True)
+        out = np.zeros(S.shape, np.float64)
+        out[..., :width] = Z
+        return out
 
     @staticmethod
     def conv3D(X, W, OH, OW, sh, sw, ph, pw, n_begin=0, n_end=None):
