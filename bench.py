@@ -33,7 +33,7 @@ block so that it overlaps the next block's compute); `compute_only` is the figur
 8192^3 problem itself split over the ranks.
 
 Other workloads (for profiling and the reports in profiles/): c1, c2_bias, c2_t1, c2_t2, c2_ragged, c4_dx, dx_s2, c4_dw, c3_qk_scaled,
-c3_qk, c3_pv, c4, c5.
+c3_qk, c3_pv, c3_sm, c3_attn, c4, c5.
 """
 from __future__ import annotations
 
@@ -294,6 +294,40 @@ class Workload:
                 self.desc = f"batchMatMul P*V Batch={w.Batch} {w.L}x{w.D}x{w.L}"
             self.flops = w.flops_each
             self.bytes = w.algorithmic_bytes_each
+        elif name in ("c3_sm", "c3_attn"):
+            # the attention block's scores in one pass - P = softmax(Q K^T / sqrt(d)) - and, for c3_attn, O = P V after it
+            w = W.config3(Batch=batch)
+            self.hosts = [pin(w.Q), pin(w.K), pin(w.V)]
+            self.dev_in = [h.cuda() for h in (w.Q, w.K, w.V)]
+            self.P = torch.empty((w.Batch, w.L, w.L), device="cuda")
+            dQ, dK, dV, dP = self.dev_in[0], self.dev_in[1], self.dev_in[2], self.P
+            alpha = 1.0 / (w.D ** 0.5)
+            score_bytes = 4.0 * w.Batch * w.L * w.L
+            qkv_bytes = 4.0 * w.Batch * w.L * w.D
+            if name == "c3_sm":
+                self.out = self.P
+                self.launch = lambda: bm.batchMatMulT2_softmax(st(), 1, dQ.data_ptr(), dK.data_ptr(), dP.data_ptr(), w.Batch,
+                                                                w.L, w.L, w.L, w.D, alpha)
+                self.flops = w.flops_each
+                self.bytes = 2 * qkv_bytes + score_bytes
+                self.desc = f"batchMatMulT2_softmax P=softmax(Q*K^T/sqrt(d)) Batch={w.Batch} {w.L}x{w.L}x{w.D}"
+            else:
+                self.out = torch.empty((w.Batch, w.L, w.D), device="cuda")
+                dO = self.out
+                self.kernels_per_step = 2
+
+                def launch():
+                    s = st()
+                    bm.batchMatMulT2_softmax(s, 1, dQ.data_ptr(), dK.data_ptr(), dP.data_ptr(), w.Batch, w.L, w.L, w.L, w.D, alpha)
+                    bm.batchMatMul(s, 1, dP.data_ptr(), dV.data_ptr(), dO.data_ptr(), w.Batch, w.L, w.D, w.L, w.L)
+                self.launch = launch
+                self.flops = 2 * w.flops_each
+                self.bytes = 4 * qkv_bytes + 2 * score_bytes
+                # the reference's block moves the score tensor nine times (product w, scale r+w, row_max r,
+                # row_softmax r+w, div2D_field r+w, P*V r), this one twice
+                self.reference_sequence_bytes = 4 * qkv_bytes + 9 * score_bytes
+                self.desc = (f"attention block Batch={w.Batch} L={w.L} d={w.D}: batchMatMulT2_softmax + batchMatMul "
+                             f"(score tensor written once, read once)")
         elif name == "c4":
             w = W.config4(N=images)
             d = w.dims
@@ -471,7 +505,7 @@ def time_steps(torch, dist, fn, steps, world, on_start=None, on_stop=None):
 
 
 TILE_NAMES = {0: "128x64", 1: "128x128", 2: "128x256", 3: "256x128 pair", 4: "256x256 pair", 5: "256x64 pair"}
-HBM_BOUND = ("c3_qk", "c3_qk_scaled", "c3_pv", "c3_attn")
+HBM_BOUND = ("c3_qk", "c3_qk_scaled", "c3_pv", "c3_sm", "c3_attn")
 
 
 def roofline_of(name, wl, ms_step, pk, sustained=False, traffic=None):
@@ -524,6 +558,9 @@ def other_configs(pkg, torch, pk, names, steps, warmup):
                  "l2": "operands larger than L2" if wl.bytes > 126e6 else "operands fit in L2 (not flushed)"}
         if hasattr(wl, "images"):
             entry["images_per_s"] = wl.images / (ms * 1e-3)
+        if hasattr(wl, "reference_sequence_bytes"):
+            entry["algorithmic_bytes"] = wl.bytes
+            entry["reference_sequence_bytes"] = wl.reference_sequence_bytes
         out[name] = entry
         del wl
         torch.cuda.empty_cache()
@@ -797,7 +834,7 @@ def main():
     if extras:
         del wl.dev_in, wl.out
         torch.cuda.empty_cache()
-        configs = other_configs(pkg, torch, pk, ["c1", "c2_t1", "c2_t2", "c2_ragged", "c3_qk", "c3_pv", "c4", "c5"],
+        configs = other_configs(pkg, torch, pk, ["c1", "c2_t1", "c2_t2", "c2_ragged", "c3_qk", "c3_pv", "c3_attn", "c4", "c5"],
                                 a.steps, a.warmup)
 
     line = {

@@ -163,11 +163,10 @@ static int pick_tile_auto(long long M, int N, long long z) {
   return best;
 }
 // The tile a call uses: the forced one if a tuning key set it, else the estimate's; remembered for diagnostics.
+static int note_tile(int t) { g_last_tile = t; return t; }
 static int pick_tile(long long M, int N, long long z) {
   const int forced = g_tile.load();
-  const int t = forced >= 0 ? forced : pick_tile_auto(M, N, z);
-  g_last_tile = t;
-  return t;
+  return note_tile(forced >= 0 ? forced : pick_tile_auto(M, N, z));
 }
 
 // Ring lengths for a launch (see GemmParams): explicit tuning values win, otherwise 0 = the kernel
@@ -200,6 +199,14 @@ static int run_gemm(const GemmCall& c) {
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
+  // Shapes below the ridge of the FP32-accurate roofline (about 44 flop per byte: short reductions such as the
+  // attention-shaped batched products) are paced by loads, stores and the split, not by the tensor pipe; measured
+  // on B200 at batch 1024: a 64-column output is fastest on the one-CTA 128x64 tile with six raw slots, a wide
+  // output on the 256x256 pair tile with two store-staging tiles per drain warp.
+  const double intensity = 2.0 * c.M * c.n_store * c.K / (4.0 * (static_cast<double>(c.M) * c.K +
+                           static_cast<double>(c.K) * c.n_store + static_cast<double>(c.M) * c.n_store));
+  const bool below_ridge = c.x3 && c.gz == 1 && intensity < 44.0;
+  if (below_ridge && g_tile.load() < 0 && c.n_store <= 64 && c.M >= 128) tile = note_tile(TILE_1x64);
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -229,6 +236,10 @@ static int run_gemm(const GemmCall& c) {
   p.gz = c.gz;
   p.kc = c.x3 ? g_kc.load() : g_kc_fast.load();
   choose_rings(&p);
+  if (below_ridge && p.ring_raw == 0) {
+    if (tile == TILE_1x64) { p.ring_raw = 6; p.ring_lo = 2; p.store_bufs = 1; }
+    else if (tile == TILE_2x256) { p.ring_raw = 3; p.ring_lo = 2; p.store_bufs = 2; }
+  }
   p.l2_hints = (p.tiles_n > 1 && p.tiles_m > 1) ? g_l2hint.load() : 0;
   p.vec4_ok = (aligned16(c.C) && !(c.ldc & 3) && !(c.sC & 3) && (c.gz == 1 || aligned16(c.Cbuf))) ? 1 : 0;
   if (p.bias && !p.vec4_ok) return CU32_E_ALIGN;   // the bias is applied on the vector store paths only

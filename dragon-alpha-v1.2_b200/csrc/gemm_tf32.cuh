@@ -656,26 +656,31 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         tc_fence_after();
         const int myrow = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        constexpr int PIECES = CW / 16;
+        static_assert(CW == 128, "the passes below read a warp's 128 columns as two loads of 64");
+        float va[64], vb[64];
+        // fl(x * alpha) is monotonic in x, so the maximum of x' is the scaled maximum (minimum for alpha < 0) of x
+        const bool up = p.alpha >= 0.0f;
         // ---- pass 1
-        float m = -INFINITY;
+        float m = up ? -INFINITY : INFINITY;
         for (int b = 0; b < subs; ++b) {
           const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
           const int c_first = b * BN + h * CW;
-          float va[16], vb[16];
-          tmem_ld_32x16(t0, va);
+          if (c_first >= p.sm_width) break;   // warp-uniform: nothing but pitch padding from here on
+          tmem_ld_32x64(t0, va);
+          tmem_ld_32x64(t0 + 64, vb);
+          tmem_wait_ld();
+          if (c_first + CW <= p.sm_width) {
 #pragma unroll
-          for (int g = 0; g < PIECES; ++g) {
-            tmem_wait_ld();
-            float (&cur)[16] = (g & 1) ? vb : va;
-            float (&nxt)[16] = (g & 1) ? va : vb;
-            if (g + 1 < PIECES) tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
+            for (int j = 0; j < 64; ++j) m = up ? fmaxf(m, fmaxf(va[j], vb[j])) : fminf(m, fminf(va[j], vb[j]));
+          } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c_first + g * 16 + j < p.sm_width) m = fmaxf(m, fmaf(cur[j], p.alpha, 0.0f));
+            for (int j = 0; j < 64; ++j) {
+              if (c_first + j < p.sm_width) m = up ? fmaxf(m, va[j]) : fminf(m, va[j]);
+              if (c_first + 64 + j < p.sm_width) m = up ? fmaxf(m, vb[j]) : fminf(m, vb[j]);
+            }
           }
         }
-        red[upar][0][h][myrow] = m;
+        red[upar][0][h][myrow] = fmaf(m, p.alpha, 0.0f);   // +-inf stays: a half without valid columns never wins
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_red[0]));
         if (!mbar_wait(smem_u32(&bar_red[0]), upar, &abort_flag)) {
@@ -689,22 +694,27 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         for (int b = 0; b < subs; ++b) {
           const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
           const int c_first = b * BN + h * CW;
-          float va[16], vb[16], ev[16];
-          tmem_ld_32x16(t0, va);
+          tmem_ld_32x64(t0, va);
+          tmem_ld_32x64(t0 + 64, vb);
+          tmem_wait_ld();
+          const bool whole = c_first + CW <= p.sm_width;   // warp-uniform
+          float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;   // partial sums: shorter chains, smaller rounding error
 #pragma unroll
-          for (int g = 0; g < PIECES; ++g) {
-            tmem_wait_ld();
-            float (&cur)[16] = (g & 1) ? vb : va;
-            float (&nxt)[16] = (g & 1) ? va : vb;
-            if (g + 1 < PIECES) tmem_ld_32x16(t0 + (g + 1) * 16, nxt);
-            if (g > 0) tmem_wait_st();   // the previous piece has left ev
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              ev[j] = (c_first + g * 16 + j < p.sm_width) ? expf(fmaf(cur[j], p.alpha, 0.0f) - m) : 0.0f;
-              sum += ev[j];
+          for (int j = 0; j < 64; j += 2) {
+            float e0 = expf(fmaf(va[j], p.alpha, 0.0f) - m), e1 = expf(fmaf(va[j + 1], p.alpha, 0.0f) - m);
+            float e2 = expf(fmaf(vb[j], p.alpha, 0.0f) - m), e3 = expf(fmaf(vb[j + 1], p.alpha, 0.0f) - m);
+            if (!whole) {
+              if (c_first + j >= p.sm_width) e0 = 0.0f;
+              if (c_first + j + 1 >= p.sm_width) e1 = 0.0f;
+              if (c_first + 64 + j >= p.sm_width) e2 = 0.0f;
+              if (c_first + 64 + j + 1 >= p.sm_width) e3 = 0.0f;
             }
-            tmem_st_32x16(t0 + g * 16, ev);
+            va[j] = e0; va[j + 1] = e1; vb[j] = e2; vb[j + 1] = e3;
+            s0 += e0; s1 += e1; s2 += e2; s3 += e3;
           }
+          sum += (s0 + s1) + (s2 + s3);
+          tmem_st_32x64(t0, va);
+          tmem_st_32x64(t0 + 64, vb);
           tmem_wait_st();
         }
         red[upar][1][h][myrow] = sum;
@@ -720,40 +730,33 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
         for (int b = 0; b < subs; ++b) {
           const uint32_t t0 = lane_addr + static_cast<uint32_t>(((ch + b) & 1u) * BN + h * CW);
           const uint32_t buf = (ch + b) & 1u;
+          tmem_ld_32x64(t0, va);
+          tmem_ld_32x64(t0 + 64, vb);
+          tmem_wait_ld();
+          // this buffer's values have left TMEM: hand it back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (rank != 0) arrive_remote(leader_addr(&bar_tmem_empty[buf]));
+            else mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+          }
 #pragma unroll
           for (int g = 0; g < CW / 32; ++g) {
-            float va[16], vb[16];
-            tmem_ld_32x16(t0 + g * 32, va);
-            tmem_ld_32x16(t0 + g * 32 + 16, vb);
             const int c0 = b * BN + h * CW + g * 32;
             const int r0 = w.row0 + q * 32;
-            const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
-            const bool inside = c0 < p.N && r0 < p.M;   // warp-uniform
-            if (inside) {
+            if (c0 < p.N && r0 < p.M) {   // warp-uniform
+              const uint32_t stg = stg0 + ((sbufs == 2u) ? (pc & 1u) : 0u) * Cfg::STAGING_TILE;
               if (lane == 0) {   // the store that last used this staging tile has read it
                 if (sbufs == 2u) tma_store_wait_read_1(); else tma_store_wait_read();
               }
               __syncwarp();
-            }
-            tmem_wait_ld();
-            if (g + 1 == CW / 32) {
-              // this buffer's last values have left TMEM: hand it back to the MMA issuer
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) {
-                if (rank != 0) arrive_remote(leader_addr(&bar_tmem_empty[buf]));
-                else mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
-              }
-            }
-            if (inside) {
 #pragma unroll
-              for (int cq = 0; cq < 4; ++cq)
+              for (int cq = 0; cq < 8; ++cq) {
+                const int j = (g & 1) * 32 + cq * 4;
+                const float (&src)[64] = (g < 2) ? va : vb;
                 sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),
-                       make_float4(va[cq * 4] * rinv, va[cq * 4 + 1] * rinv, va[cq * 4 + 2] * rinv, va[cq * 4 + 3] * rinv));
-#pragma unroll
-              for (int cq = 0; cq < 4; ++cq)
-                sts128(stg + lane * 128 + (((cq + 4) ^ (lane & 7)) * 16),
-                       make_float4(vb[cq * 4] * rinv, vb[cq * 4 + 1] * rinv, vb[cq * 4 + 2] * rinv, vb[cq * 4 + 3] * rinv));
+                       make_float4(src[j] * rinv, src[j + 1] * rinv, src[j + 2] * rinv, src[j + 3] * rinv));
+              }
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
