@@ -596,6 +596,37 @@ def gpu_reference_leg(torch, wl):
             "kind": "the reference's SIMT FP32 kernels built for sm_100a (oracle/_ref/libref_matmul.so), same operands"}
 
 
+class FusedGatherStep:
+    """One multi-GPU step of a row-shardable matMul with the reassembly inside the kernel: the epilogue stores each
+    tile of this rank's rows into its own copy of the full output and into every peer's copy (peer memory mapped into
+    this process), so no collective follows the launch and nothing is loaded over NVLink."""
+
+    def __init__(self, torch, dist, pkg, wl, world, rank):
+        form, N, M, K = wl.cpu_case[:4]
+        assert form in ("AB", "T2")
+        self.torch, self.wl = torch, wl
+        mm = pkg.cu32.Cuda_matMul
+        self.fn = mm.matMul_replicated if form == "AB" else mm.matMulT2_replicated
+        self.N, self.M, self.K = N, M, K
+        self.pg = pkg.shard.PeerGather(dist, world, rank, (N, M), torch.device("cuda", torch.cuda.current_device()))
+        self.bytes_sent = (world - 1) * N * M * 4
+
+    def __call__(self):
+        wl, pg = self.wl, self.pg
+        cur = self.torch.cuda.current_stream()
+        self.fn([cur.cuda_stream], 1, wl.dev_in[0].data_ptr(), wl.dev_in[1].data_ptr(), pg.local.data_ptr(), pg.replicas,
+                self.N, self.M, self.K)
+
+    def check(self):
+        """Every rank multiplies the same seeded operands here, so every block of the gathered output must equal
+        this rank's own block bit for bit once all ranks have finished."""
+        pg = self.pg
+        pg.barrier()
+        ok = all(bool(self.torch.equal(pg.block(r), pg.local)) for r in range(pg.world))
+        pg.barrier()
+        return ok
+
+
 class ShardedStep:
     """One multi-GPU step of a row-shardable matMul: this rank's rows are cut into blocks; block b is multiplied
     on the current stream and then all-gathered (NCCL over NVLink, its own stream) while block b+1 is being
@@ -726,11 +757,25 @@ def main():
             kind, nblk = "all-reduce of the partial products", 1
             moved = 2.0 * wl.out.numel() * 4 * (world - 1) / world
         elif wl.cpu_case is not None and wl.cpu_case[0] in ("AB", "T2") and wl.kernels_per_step == 1 and wl.cpu_case[1] >= 2048:
-            nblk = int(os.environ.get("DRAGON_BENCH_GATHER_BLOCKS", "4"))
-            step_collective = ShardedStep(torch, dist, pkg, wl, world, nblk)
-            kind = f"all-gather of the output shards in {nblk} row blocks, block b in flight while block b+1 is multiplied"
-            moved = float(step_collective.bytes_received)
-            launches_per_step = nblk
+            fused = None
+            if os.environ.get("DRAGON_BENCH_GATHER", "fused") == "fused":
+                try:
+                    fused = FusedGatherStep(torch, dist, pkg, wl, world, rank)
+                except Exception as ex:   # no peer-addressable memory on this box: fall back to the collective
+                    if rank == 0:
+                        print(f"peer-mapped output unavailable ({type(ex).__name__}: {ex}); using NCCL all-gather", file=sys.stderr)
+            if fused is not None:
+                step_collective = fused
+                nblk = 1
+                kind = ("output shards reassembled by the contraction kernel itself: every tile is stored into each rank's "
+                        "copy of the full output over NVLink (stores only), no collective after the launch")
+                moved = float(fused.bytes_sent)
+            else:
+                nblk = int(os.environ.get("DRAGON_BENCH_GATHER_BLOCKS", "2"))
+                step_collective = ShardedStep(torch, dist, pkg, wl, world, nblk)
+                kind = f"NCCL all-gather of the output shards in {nblk} row blocks, block b in flight while block b+1 is multiplied"
+                moved = float(step_collective.bytes_received)
+                launches_per_step = nblk
         else:
             gathered = torch.empty((world,) + tuple(wl.out.shape), device="cuda")
 
@@ -739,34 +784,53 @@ def main():
                 dist.all_gather_into_tensor(gathered, wl.out)
             kind, nblk = "all-gather of the output shards after the launch", 1
             moved = float((world - 1) * wl.out.numel() * 4)
+        # the collective's kernels need SMs of their own while the persistent contraction grid runs
+        reserve = int(os.environ.get("DRAGON_BENCH_SM_RESERVE", "0")) if nblk > 1 else 0
+        pkg.cu32.tune("sm_reserve", reserve)
         for _ in range(3):
             step_collective()
         ms_step = time_steps(torch, dist, step_collective, a.steps, world) / a.steps
+        pkg.cu32.tune("sm_reserve", 0)
         check_status(pkg)
+        gathered_ok = step_collective.check() if isinstance(step_collective, FusedGatherStep) else None
         exposed = max(ms_step - ms_compute, 1e-9)
         collective = {"kind": kind, "ms_per_step": ms_step, "compute_only_ms": ms_compute,
-                      "bytes_received_per_rank": moved,
+                      "bytes_over_nvlink_per_rank": moved, "sms_left_to_the_collective": reserve,
+                      "gathered_output_verified": gathered_ok,
                       "exposed_ms": ms_step - ms_compute,
-                      "nvlink_gbs_if_serial": moved / (exposed * 1e-3) / 1e9,
+                      "nvlink_gbs_over_the_step": moved / (ms_step * 1e-3) / 1e9,
                       "note": "NVLink reference on this pool: 770 GB/s peer copy per direction"}
     value = wl.flops * world / (ms_step * 1e-3) / 1e12
 
-    # ---- strong scaling: the 8192^3 problem itself, rows divided over the ranks, output all-gathered
+    # ---- strong scaling: the 8192^3 problem itself, rows divided over the ranks, output reassembled
     strong = None
     if world > 1 and a.workload == "c2_ab" and a.size % (world * 4 * 128) == 0:
         rows = a.size // world
-        dA, dB, dC = wl.dev_in[0][:rows], wl.dev_in[1], wl.out[:rows]
-        full = torch.empty((world, rows * a.size), device="cuda")
-        mmf = pkg.cu32.Cuda_matMul.matMul
+        dA, dB = wl.dev_in[0][:rows], wl.dev_in[1]
+        mm = pkg.cu32.Cuda_matMul
+        pg = None
+        if isinstance(step_collective, FusedGatherStep):
+            pg = pkg.shard.PeerGather(dist, world, rank, (rows, a.size), torch.device("cuda", torch.cuda.current_device()))
 
-        def strong_step():
-            mmf([torch.cuda.current_stream().cuda_stream], 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), rows, a.size, a.size)
-            dist.all_gather_into_tensor(full.view(-1), dC.reshape(-1))
+            def strong_step():
+                mm.matMul_replicated([torch.cuda.current_stream().cuda_stream], 1, dA.data_ptr(), dB.data_ptr(),
+                                     pg.local.data_ptr(), pg.replicas, rows, a.size, a.size)
+            how = "C reassembled by the kernel's own stores into every rank's copy"
+        else:
+            dC = wl.out[:rows]
+            full = torch.empty((world, rows * a.size), device="cuda")
+
+            def strong_step():
+                mm.matMul([torch.cuda.current_stream().cuda_stream], 1, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), rows, a.size, a.size)
+                dist.all_gather_into_tensor(full.view(-1), dC.reshape(-1))
+            how = "C all-gathered (NCCL) after the launch"
         for _ in range(3):
             strong_step()
         ms_s = time_steps(torch, dist, strong_step, a.steps, world) / a.steps
+        if pg is not None:
+            pg.barrier()
         strong = {"value": 2.0 * a.size ** 3 / (ms_s * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_s,
-                  "workload": f"matMul AB 8192^3 in total: {rows} rows of A and C per rank, B replicated, C all-gathered"}
+                  "workload": f"matMul AB 8192^3 in total: {rows} rows of A and C per rank, B replicated, {how}"}
 
     # ---- end to end with host buffers
     e2e = None

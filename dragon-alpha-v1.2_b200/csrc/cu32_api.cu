@@ -27,6 +27,7 @@ static std::atomic<int> g_ring_raw{0};        // 0 = chosen per call (see choose
 static std::atomic<int> g_ring_lo{0};
 static std::atomic<int> g_store_bufs{0};
 static std::atomic<int> g_arrive_release{0};
+static std::atomic<int> g_sm_reserve{0};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -139,6 +140,8 @@ struct GemmCall {
   int bias_width;           // true width of the rows: columns beyond it are stored as zeros
   bool scale_on = false;   // store alpha * result (one rounding), vector store paths only
   float alpha = 1.0f;
+  float* const* replicas = nullptr;   // further output buffers that receive the same stores as C (same layout)
+  int n_replicas = 0;
 };
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -180,6 +183,7 @@ static void choose_rings(GemmParams* p) {
   if (p->ring_raw > 0 && p->ring_lo == 0) p->ring_lo = p->ring_raw;
   if (p->ring_raw == 0) p->ring_lo = 0;
   p->arrive_release = g_arrive_release.load();
+  p->sm_reserve = g_sm_reserve.load();
   p->clock_acc = clock_acc_ptr();
 }
 
@@ -196,6 +200,7 @@ static int run_gemm(const GemmCall& c) {
     if (!aligned16(c.bias) || (c.n_store & 3)) return CU32_E_ALIGN;
   }
   if (c.scale_on && (c.gz != 1 || c.bias)) return CU32_E_ARG;
+  if (c.n_replicas < 0 || c.n_replicas > 7 || (c.n_replicas > 0 && (!c.replicas || c.gz != 1))) return CU32_E_ARG;
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
@@ -253,7 +258,16 @@ static int run_gemm(const GemmCall& c) {
     if (!rc && c.gz > 1) rc = make_map3(&p.tmCbuf, c.Cbuf, c.n_store, c.M, c.gz - 1, c.ldc, sc, 32, 32, false);
     if (rc) return rc;
     p.tma_store = 1;
+    for (int i = 0; i < c.n_replicas; ++i) {
+      if (!c.replicas[i]) return CU32_E_NULL;
+      if (!aligned16(c.replicas[i])) return CU32_E_ALIGN;
+      if (int r2 = make_map3(&p.tmRep[i], c.replicas[i], c.n_store, c.M, zs_c, c.ldc, sc, 32, 32, false)) return r2;
+    }
+    p.n_rep = c.n_replicas;
+  } else if (c.n_replicas > 0) {
+    return CU32_E_ALIGN;   // the copies are written by the tensor-map store path only
   }
+  if (c.n_replicas > 0 && (c.bias || c.scale_on)) return CU32_E_ARG;
   cudaError_t e;
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
@@ -280,7 +294,7 @@ enum MatForm { FORM_AB, FORM_T1, FORM_T2 };
 
 static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length, int GridZ,
                       const float* dA, const float* dB, float* dC, float* dCbuf, int N, int M, int K,
-                      const float* dBias = nullptr, int width = 0) {
+                      const float* dBias = nullptr, int width = 0, float* const* replicas = nullptr, int n_replicas = 0) {
   cudaStream_t st;
   if (int rc = check_streams(streams, length, &st)) return rc;
   if (N <= 0 || M <= 0 || K <= 0) return CU32_E_DIM;
@@ -293,6 +307,7 @@ static int matmul_any(MatForm form, bool x3, const int64_t* streams, int length,
   c.sC = static_cast<long long>(N) * M;  // distance between split-K partial buffers
   c.gz = GridZ; c.x3 = x3; c.stream = st;
   c.bias = dBias; c.bias_width = width;
+  c.replicas = replicas; c.n_replicas = n_replicas;
   switch (form) {
     case FORM_AB: c.a_mn = false; c.lda = K; c.b_mn = true;  c.ldb = M; break;
     case FORM_T1: c.a_mn = true;  c.lda = N; c.b_mn = true;  c.ldb = M; break;
@@ -812,6 +827,15 @@ int cu32_matMulT1SK(const int64_t* s, int n, int GZ, const float* A, const float
 int cu32_matMulT2SK(const int64_t* s, int n, int GZ, const float* A, const float* B, float* C,
                     float* Cbuf, int N, int M, int K) {
   return matmul_any(FORM_T2, true, s, n, GZ, A, B, C, Cbuf, N, M, K);
+}
+// ---- product stored to several buffers at once (no counterpart in the reference, which runs on one GPU)
+int cu32_matMul_replicated(const int64_t* s, int n, const float* A, const float* B, float* C, float* const* replicas,
+                           int n_replicas, int N, int M, int K) {
+  return matmul_any(FORM_AB, true, s, n, 1, A, B, C, nullptr, N, M, K, nullptr, 0, replicas, n_replicas);
+}
+int cu32_matMulT2_replicated(const int64_t* s, int n, const float* A, const float* B, float* C, float* const* replicas,
+                             int n_replicas, int N, int M, int K) {
+  return matmul_any(FORM_T2, true, s, n, 1, A, B, C, nullptr, N, M, K, nullptr, 0, replicas, n_replicas);
 }
 int cu32_matMul_mma(const int64_t* s, int n, const float* A, const float* B, float* C, int N, int M, int K) {
   return matmul_any(FORM_AB, false, s, n, 1, A, B, C, nullptr, N, M, K);
@@ -1387,6 +1411,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "store_bufs")) { if (value < 0 || value > 2) return CU32_E_ARG; g_store_bufs = value; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { g_arrive_release = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { g_clock_on = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
 int cu32_get_tune(const char* key, int* value) {
@@ -1401,6 +1426,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "store_bufs")) { *value = g_store_bufs; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { *value = g_arrive_release; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { *value = g_clock_on; return CU32_OK; }
+  if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;
 }

@@ -99,7 +99,10 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   if (q.unit_tiles < 1) q.unit_tiles = 1;
   // work units: tiles, or (softmax mode) groups of unit_tiles tiles that one CTA pair takes in a row
   const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * grid_z / (Cfg::SOFTMAX ? q.unit_tiles : 1);
-  const long long grid_units = total_tiles < units ? total_tiles : units;
+  // a host that runs a collective beside the contraction can keep some SMs out of the persistent grid
+  int usable = units - (q.sm_reserve > 0 ? (q.sm_reserve + Cfg::CTAS - 1) / Cfg::CTAS : 0);
+  if (usable < 1) usable = 1;
+  const long long grid_units = total_tiles < usable ? total_tiles : usable;
   // Rings: 0 = the balanced default (as many raw + lo pairs as fit beside one staging tile per drain warp).
   if (q.ring_raw == 0) { q.ring_raw = Cfg::STAGES; q.ring_lo = Cfg::STAGES; }
   if (q.store_bufs == 0) q.store_bufs = 1;

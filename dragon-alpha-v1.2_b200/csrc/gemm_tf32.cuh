@@ -53,6 +53,9 @@ struct GemmParams {
                         // MN-major B: dims (N, K, batch), box (32, 32, 1)
   CUtensorMap tmC;      // output C: dims (N, M, batches), box (32, 32, 1), 128B swizzle
   CUtensorMap tmCbuf;   // split-K partial buffers: dims (N, M, gz-1), same box
+  CUtensorMap tmRep[7];  // further copies of the output (same dims and box as tmC), e.g. the same rows of a gathered
+                         // output in the memory of the other GPUs of an NVLink domain, mapped into this process
+  int n_rep;             // how many of them are valid: every store to C is repeated to each (stores only, never loads)
   float* C;             // output of batch 0 / split-K slice 0
   const float* bias;    // optional row vector added to every output row before the store (gz == 1 only)
   int bias_width;       // columns < bias_width get acc + bias[col]; columns >= bias_width are stored as 0
@@ -80,6 +83,7 @@ struct GemmParams {
   int ring_lo;          // lo slots, 1..ring_raw (FP32-accurate mode only)
   int store_bufs;       // 4 KB store-staging tiles per drain warp, 1 or 2
   int arrive_release;   // debugging aid: remote mbarrier arrives carry a cluster-scope release
+  int sm_reserve;       // SMs the persistent grid leaves free (for a collective's kernels running beside it)
   // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
   // conv_icb blocks of 32 channels, so a k-block never straddles two taps.
@@ -895,6 +899,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               if (lane == 0) {
                 if (first) tma_store_3d(cmap, stg, c0, r0, w.zc);
                 else tma_reduce_add_3d(cmap, stg, c0, r0, w.zc);
+                for (int i = 0; i < p.n_rep; ++i) {   // the same piece to every further copy of the output
+                  if (first) tma_store_3d(&p.tmRep[i], stg, c0, r0, w.zc);
+                  else tma_reduce_add_3d(&p.tmRep[i], stg, c0, r0, w.zc);
+                }
                 tma_store_commit();
               }
               ++pc;

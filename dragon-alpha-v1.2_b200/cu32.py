@@ -61,6 +61,8 @@ SIGNATURES = {
     "cu32_matMulT1SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMulT2SK": [_sp, _I, _I, _fp, _fp, _fp, _fp, _I, _I, _I],
     "cu32_SKbuf_summary": [c_int64, _fp, _fp, _I, _I],
+    "cu32_matMul_replicated": [_sp, _I, _fp, _fp, _fp, POINTER(_fp), _I, _I, _I, _I],
+    "cu32_matMulT2_replicated": [_sp, _I, _fp, _fp, _fp, POINTER(_fp), _I, _I, _I, _I],
     "cu32_matMulT1SK_noalloc": [_sp, _I, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMul_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
     "cu32_matMulT1_mma": [_sp, _I, _fp, _fp, _fp, _I, _I, _I],
@@ -310,6 +312,22 @@ class Cuda_matMul:
     def matMul_biased(streamArray, length, dA, dB, dC, dBias, N, M, K, width):
         s, n = _streams(streamArray, length)
         _check(load().cu32_matMul_biased(s, n, _p(dA), _p(dB), _p(dC), _p(dBias), N, M, K, width), "matMul_biased")
+
+    # the product stored to several buffers at once (no counterpart in the reference): `replicas` are device
+    # addresses of further [N, M] outputs, typically this rank's rows inside the peers' copies of a gathered output
+    @staticmethod
+    def _replicated(name, streamArray, length, dA, dB, dC, replicas, N, M, K):
+        s, n = _streams(streamArray, length)
+        arr = (_fp * max(len(replicas), 1))(*[_p(r) for r in replicas])
+        _check(getattr(load(), "cu32_" + name)(s, n, _p(dA), _p(dB), _p(dC), arr, len(replicas), N, M, K), name)
+
+    @staticmethod
+    def matMul_replicated(streamArray, length, dA, dB, dC, replicas, N, M, K):
+        Cuda_matMul._replicated("matMul_replicated", streamArray, length, dA, dB, dC, replicas, N, M, K)
+
+    @staticmethod
+    def matMulT2_replicated(streamArray, length, dA, dB, dC, replicas, N, M, K):
+        Cuda_matMul._replicated("matMulT2_replicated", streamArray, length, dA, dB, dC, replicas, N, M, K)
 
     @staticmethod
     def matMul_mma_biased(streamArray, length, dA, dB, dC, dBias, N, M, K, width):

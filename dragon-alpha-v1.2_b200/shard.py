@@ -68,3 +68,43 @@ def reduce_partials(dist, partial, dst: int = 0):
     """Sum the per-rank [N, M] partial products of a K-sharded A^T B onto `dst`."""
     dist.reduce(partial, dst=dst, op=dist.ReduceOp.SUM)
     return partial
+
+
+class PeerGather:
+    """Gathered output of a row-sharded product without a collective after it: every rank holds a copy of the full
+    output in memory that its peers can address (one allocation per rank, exchanged once over the process group),
+    and each rank's product is stored by the contraction kernel itself into its own block of every copy
+    (``cu32_matMul_replicated``).  Only stores cross NVLink; nothing is loaded from a peer.
+
+    ``block(r)`` is rank r's block inside this rank's copy; ``local`` is this rank's own block (the kernel's C),
+    ``replicas`` the device addresses of this rank's block inside the peers' copies."""
+
+    def __init__(self, dist, world: int, rank: int, block_shape, device):
+        import torch
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank = world, rank
+        n = 1
+        for d in block_shape:
+            n *= int(d)
+        self.block_elems = n
+        self.full = symm.empty((world, n), dtype=torch.float32, device=device)
+        self.handle = symm.rendezvous(self.full, dist.group.WORLD)
+        self.block_shape = tuple(block_shape)
+        self.local = self.full[rank].view(self.block_shape)
+        self.replicas = []
+        self._keep = []
+        for r in range(world):
+            if r == rank:
+                continue
+            peer = self.handle.get_buffer(r, (world, n), torch.float32)
+            self._keep.append(peer)
+            self.replicas.append(peer[rank].data_ptr())
+
+    def block(self, r: int):
+        return self.full[r].view(self.block_shape)
+
+    def barrier(self):
+        """All ranks' kernels have drained and their stores are visible everywhere."""
+        import torch
+        torch.cuda.synchronize()
+        self.handle.barrier()

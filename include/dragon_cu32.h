@@ -93,6 +93,19 @@ CU32_API int cu32_matMulT1_mma(const int64_t* streams, int length, const float* 
 CU32_API int cu32_matMulT2_mma(const int64_t* streams, int length, const float* dA, const float* dB,
                       float* dC, int N, int M, int K);
 
+/* Product stored to several buffers at once.  No counterpart in the reference (a single-GPU engine).
+ * C = A*B (cu32_matMul_replicated) or A*B^T (cu32_matMulT2_replicated) exactly as the plain entry points, and every
+ * store to dC is repeated, from the same shared-memory tile, to each of the n_replicas (0..7) buffers in
+ * dC_replicas (same [N, M] layout, 16-byte aligned).  The use: the ranks of one NVLink domain each own a block of
+ * rows of a larger product; a rank passes, for every peer, the address of its own block inside the peer's copy of
+ * the full output (peer memory mapped into this process), and the reassembly that would otherwise be an all-gather
+ * after the product rides on the epilogue's stores - nothing is ever loaded from a peer.  The caller orders the
+ * end of the call before any peer reads (a barrier over the ranks after the stream has drained). */
+CU32_API int cu32_matMul_replicated(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                                    float* const* dC_replicas, int n_replicas, int N, int M, int K);
+CU32_API int cu32_matMulT2_replicated(const int64_t* streams, int length, const float* dA, const float* dB, float* dC,
+                                      float* const* dC_replicas, int n_replicas, int N, int M, int K);
+
 /* Split-K A^T*B that allocates nothing and needs no partial buffer from the caller.
  * No counterpart in the reference (its split-K natives always take a caller-allocated Cbuf).
  *
@@ -428,6 +441,8 @@ CU32_API int cu32_batchMatMulT2_softmax(const int64_t* streams, int length, cons
  *              makes the call return cudaErrorInvalidValue.
  *   "clock"    1 = CTA 0 of every contraction launch adds its run time in SM cycles and in nanoseconds to a
  *              device-side accumulator (cu32_read_clock); 0 = off (default)
+ *   "sm_reserve" SMs the contraction kernel's persistent grid leaves free, for kernels a host runs beside it on
+ *              another stream (a collective that reassembles output shards); 0 = none (default)
  *   "last_tile" (read only) tile configuration of the most recent contraction call of this process
  *   "arrive_release"  1 = barrier arrivals between the two CTAs of a pair carry a cluster-scope release
  *              (diagnostics: results must not depend on it); 0 = default

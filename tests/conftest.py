@@ -55,7 +55,7 @@ def _default_tuning(request):
         p.cu32.tune("tile", -1)
         p.cu32.tune("kc", DEFAULT_KC["kc"])
         p.cu32.tune("kc_fast", DEFAULT_KC["kc_fast"])
-        for key in ("ring_raw", "ring_lo", "store_bufs", "arrive_release"):
+        for key in ("ring_raw", "ring_lo", "store_bufs", "arrive_release", "sm_reserve"):
             p.cu32.tune(key, 0)
 
 

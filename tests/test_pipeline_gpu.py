@@ -102,3 +102,30 @@ def test_pair_tiles_match_the_single_cta_tile_with_either_arrive(pkg, cuda):
                 for rep in range(4):
                     Y = f()
                     assert np.array_equal(Y, base[k]), (tile, release, k, rep, int((Y != base[k]).sum()))
+
+
+def test_replicated_stores_write_every_copy(pkg, cuda):
+    """cu32_matMul_replicated repeats each store of the product to further buffers (on several GPUs: the peers'
+    copies of a gathered output; here all local).  Every copy equals the plain product bit for bit, canaries
+    around each copy stay intact, and a request the tensor-map store path cannot serve is refused."""
+    mm = pkg.cu32.Cuda_matMul
+    for form, fn in (("AB", mm.matMul_replicated), ("T2", mm.matMulT2_replicated)):
+        for (N, M, K) in [(520, 388, 260), (256, 256, 64), (132, 68, 96)]:
+            sa, sb = G.mm_shapes(form, N, M, K)
+            A, B = G.rand_pm1(sa, 11), G.rand_pm1(sb, 12)
+            base = G.matmul(pkg, form, A, B, N, M, K)
+            dA, dB = G.dev(A), G.dev(B)
+            for n_rep in (0, 1, 3, 7):
+                outs = [G.Out(N * M) for _ in range(n_rep + 1)]
+                fn([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), outs[0].ptr, [o.ptr for o in outs[1:]], N, M, K)
+                for i, o in enumerate(outs):
+                    assert np.array_equal(o.host((N, M)), base), (form, N, M, K, n_rep, i)
+                G.check_status(pkg)
+    dA, dB = G.dev(G.rand_pm1((64, 64), 1)), G.dev(G.rand_pm1((64, 64), 2))
+    out = G.Out(64 * 64)
+    with pytest.raises(pkg.cu32.CudaException) as ei:
+        mm.matMul_replicated([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr, [out.ptr + 4], 64, 64, 64)
+    assert ei.value.code == -4      # a copy that is not 16-byte aligned
+    with pytest.raises(pkg.cu32.CudaException) as ei:
+        mm.matMul_replicated([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), out.ptr, [out.ptr] * 8, 64, 64, 64)
+    assert ei.value.code == -8      # more than seven copies
