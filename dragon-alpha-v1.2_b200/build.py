@@ -16,6 +16,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 LIB = HERE / "libdragon_cu32.so"
+BRIDGE_LIB = HERE / "libdragon_cuda.so"      # the Linux port of the reference's `Cuda` runtime-bridge natives
+BRIDGE_SOURCE = "cuda_bridge.cu"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -23,7 +25,8 @@ CUFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler"
 
 CU_SOURCES = ["cu32_api.cu", "gemm_kk.cu", "gemm_kk_softmax.cu", "gemm_kn.cu", "gemm_nn.cu", "gemm_nn_im2col.cu"]
 CPP_SOURCES = ["jni_exports.cpp"]
-HEADERS = ["sm100_ptx.cuh", "gemm_tf32.cuh", "gemm_launch.h", "jni_min.h", "../../include/dragon_cu32.h"]
+HEADERS = ["sm100_ptx.cuh", "gemm_tf32.cuh", "gemm_launch.h", "jni_min.h", "../../include/dragon_cu32.h",
+           "../../include/dragon_cuda.h"]
 
 
 def _stale(target: Path, deps: list[Path]) -> bool:
@@ -57,11 +60,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(o)
         if force or _stale(o, [CSRC / src] + hdrs):
             jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-c", str(CSRC / src), "-o", str(o)])
+    bridge_obj = OBJ / (BRIDGE_SOURCE + ".o")
+    if force or _stale(bridge_obj, [CSRC / BRIDGE_SOURCE] + hdrs):
+        jobs.append([NVCC, *ARCH, *CUFLAGS, "-c", str(CSRC / BRIDGE_SOURCE), "-o", str(bridge_obj)])
     if jobs:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
             list(ex.map(_run, jobs))
     if force or jobs or _stale(LIB, objs):
         _run([NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "shared"])
+    if force or _stale(BRIDGE_LIB, [bridge_obj]):
+        _run([NVCC, *ARCH, "-shared", "-o", str(BRIDGE_LIB), str(bridge_obj), "-cudart", "shared"])
     return LIB
 
 
