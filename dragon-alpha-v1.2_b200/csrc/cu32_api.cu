@@ -28,6 +28,7 @@ static std::atomic<int> g_ring_lo{0};
 static std::atomic<int> g_store_bufs{0};
 static std::atomic<int> g_arrive_release{0};
 static std::atomic<int> g_sm_reserve{0};
+static std::atomic<int> g_force_gather{0};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -395,7 +396,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   if (int rc = check_streams(streams, length, &st)) return rc;
   if (!dX || !dW || !dY) return CU32_E_NULL;
   if (IH <= 0 || IW <= 0 || FH <= 0 || FW <= 0 || OH <= 0 || OW <= 0 || N <= 0 || IC <= 0 || OC <= 0 ||
-      sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+      sh <= 0 || sw <= 0 || (!flip && (ph < 0 || pw < 0)))
     return CU32_E_DIM;
   if ((IC & 3) || !aligned16(dX) || !aligned16(dW)) return CU32_E_ALIGN;
   // forward entry points: the output extents must be the ones the geometry gives (the data-gradient callers
@@ -427,14 +428,14 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   if (!g_encode_im2col) return CU32_E_DRIVER;
   // The im2col tensor map walks "base pixels" (the top-left input pixel of each output
   // position) inside the box [lower, extent - 1 + upper] with the convolution stride;
-  // the filter tap is added per load as an offset.  Corners must fit 8 signed bits and
-  // offsets 8 unsigned bits for two spatial dimensions.
+  // the filter tap is added per load as an offset.  Corners must fit 8 signed bits,
+  // offsets 8 unsigned bits and strides 3 bits; a geometry beyond that (or one the driver's
+  // encoder refuses) is served by the kernel's gather path, slower but without limits.
   const int lower_w = -pw, lower_h = -ph;
   const int upper_w = lower_w + (OW - 1) * sw - (IW - 1);
   const int upper_h = lower_h + (OH - 1) * sh - (IH - 1);
-  if (lower_w < -128 || lower_h < -128 || upper_w < -128 || upper_w > 127 || upper_h < -128 ||
-      upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8)
-    return CU32_E_GEOMETRY;
+  bool gather = g_force_gather.load() != 0 || lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 ||
+                upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8;
 
   int tile = pick_tile(GM, OC, 1);
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
@@ -449,11 +450,12 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
     int lower[2] = {lower_w, lower_h};
     int upper[2] = {upper_w, upper_h};
     cuuint32_t trav[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
-    CUresult r = g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dX), dims,
-                                 strides, lower, upper, /*channelsPerPixel=*/32, /*pixelsPerColumn=*/128,
-                                 trav, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+    CUresult r = gather ? CUDA_ERROR_INVALID_VALUE
+                        : g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dX), dims,
+                                          strides, lower, upper, /*channelsPerPixel=*/32, /*pixelsPerColumn=*/128,
+                                          trav, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) gather = true;
     // Drivers up to CUDA 13.1 set a descriptor flag that mis-handles im2col maps over
     // tensors smaller than 128 KiB; NVIDIA's CUTLASS clears bit 21 of the second 64-bit
     // word in that case (cute/atom/copy_traits_sm90_im2col.hpp), and so does this.
@@ -503,6 +505,7 @@ static int conv_any(bool x3, const int64_t* streams, int length, const float* dX
   }
   p.conv_OW = OW; p.conv_OH = OH; p.conv_FW = FW; p.conv_IC = IC;
   p.conv_sw = sw; p.conv_sh = sh; p.conv_pw = pw; p.conv_ph = ph;
+  p.gather = gather ? 1 : 0; p.g_img = dX; p.g_H = IH; p.g_W = IW; p.g_N = N;
   cudaError_t e;
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
@@ -522,9 +525,9 @@ static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, i
   if (!dDY || !dW || !dDX) return CU32_E_NULL;
   if (FH <= 0 || FW <= 0 || ph < 0 || pw < 0 || IC <= 0 || OC <= 0) return CU32_E_DIM;
   if ((IC & 3) || (OC & 3)) return CU32_E_ALIGN;
-  if (ph > FH - 1 || pw > FW - 1) return CU32_E_GEOMETRY;   // padding larger than the filter reach
   if (IH != OH - 1 + FH - 2 * ph || IW != OW - 1 + FW - 2 * pw) return CU32_E_DIM;
-  if (FH > 16 || FW > 16) return CU32_E_GEOMETRY;           // the tap index travels in the batch coordinate
+  // padding beyond the filter reach makes the equivalent forward padding negative (the outermost pixels of deltaY
+  // are never used); conv_any takes it as it is
   return conv_any(true, streams, length, dDY, OH, OW, dW, FH, FW, dDX, IH, IW, N, /*in*/ OC, /*out*/ IC, 1, 1,
                   FH - 1 - ph, FW - 1 - pw, dBias, width, true);
 }
@@ -604,11 +607,11 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
     return CU32_E_DIM;
   if (static_cast<long long>(N) * IH * IW * IC >= (1LL << 31) || static_cast<long long>(N) * OH * OW * OC >= (1LL << 31))
     return CU32_E_DIM;
-  if (sh > 16 || sw > 16 || FH > 256 || FW > 256) return CU32_E_GEOMETRY;
+  if (static_cast<long long>(sh) * sw > 4096) return CU32_E_DIM;   // one launch per phase
   if (dBias) {
     if (width <= 0 || width > IC) return CU32_E_DIM;
     if (!aligned16(dBias)) return CU32_E_ALIGN;
-    if (FH < sh || FW < sw) return CU32_E_GEOMETRY;   // pixels no tap reaches would need the bias alone
+    if (FH < sh || FW < sw) return CU32_E_ARG;   // pixels no tap reaches would need the bias alone: use the unbiased native + bias kernel
   }
   if (!load_driver_entry_points() || !g_encode_im2col) return CU32_E_DRIVER;
   const int mCFH = (FH + sh - 1) / sh, mCFW = (FW + sw - 1) / sw;
@@ -630,9 +633,8 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       if (U <= 0 || V <= 0) continue;
       const int lower_h = u0 - (CFH - 1), lower_w = v0 - (CFW - 1);
       const int upper_h = lower_h + (U - 1) - (OH - 1), upper_w = lower_w + (V - 1) - (OW - 1);
-      if (lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 || upper_w < -128 || upper_w > 127 ||
-          upper_h < -128 || upper_h > 127)
-        return CU32_E_GEOMETRY;
+      bool gather = g_force_gather.load() != 0 || lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 ||
+                    upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127 || CFH > 256 || CFW > 256;
       const long long GM = static_cast<long long>(N) * U * V;
       int tile = pick_tile(GM, IC, 1);
       const int ctas = tile_ctas(tile), bn = tile_bn(tile);
@@ -646,11 +648,12 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
         int lower[2] = {lower_w, lower_h};
         int upper[2] = {upper_w, upper_h};
         cuuint32_t trav[4] = {1, 1, 1, 1};
-        CUresult r = g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dDY), dims, strides,
-                                     lower, upper, 32, 128, trav, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+        CUresult r = gather ? CUDA_ERROR_INVALID_VALUE
+                            : g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dDY), dims, strides,
+                                              lower, upper, 32, 128, trav, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) gather = true;
         int drv = 0;   // same driver workaround as in conv_any
         if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
             static_cast<long long>(N) * OH * OW * OC * 4 < 131072)
@@ -696,6 +699,7 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       p.tma_store = 0;
       p.conv_OW = V; p.conv_OH = U; p.conv_FW = CFW; p.conv_IC = OC;
       p.conv_sw = 1; p.conv_sh = 1; p.conv_pw = -lower_w; p.conv_ph = -lower_h;
+      p.gather = gather ? 1 : 0; p.g_img = dDY; p.g_H = OH; p.g_W = OW; p.g_N = N;
       p.status = status;
       e = launch_gemm_kn(tile, true, true, p, 1, st);
       if (e != cudaSuccess) return static_cast<int>(e);
@@ -748,9 +752,8 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
   const int lower_w = -pw, lower_h = -ph;
   const int upper_w = lower_w + (OW - 1) * sw - (IW - 1);
   const int upper_h = lower_h + (OH - 1) * sh - (IH - 1);
-  if (lower_w < -128 || lower_h < -128 || upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127 ||
-      FW > 256 || FH > 256 || sw > 8 || sh > 8)
-    return CU32_E_GEOMETRY;
+  bool gather = g_force_gather.load() != 0 || lower_w < -128 || lower_h < -128 || upper_w < -128 || upper_w > 127 ||
+                upper_h < -128 || upper_h > 127 || FW > 256 || FH > 256 || sw > 8 || sh > 8;
 
   const int zs = static_cast<int>(taps) * GridZ;
   int tile = pick_tile(OC, IC, zs);
@@ -767,11 +770,12 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
     int lower[2] = {lower_w, lower_h};
     int upper[2] = {upper_w, upper_h};
     cuuint32_t trav[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
-    CUresult r = g_encode_im2col(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dX), dims, strides,
-                                 lower, upper, /*channelsPerPixel=*/32, /*pixelsPerColumn=*/32, trav,
-                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
-                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
+    CUresult r = gather ? CUDA_ERROR_INVALID_VALUE
+                        : g_encode_im2col(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dX), dims, strides,
+                                          lower, upper, /*channelsPerPixel=*/32, /*pixelsPerColumn=*/32, trav,
+                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) gather = true;
     int drv = 0;   // same driver workaround as in conv_any
     if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
         static_cast<long long>(N) * IH * IW * IC * 4 < 131072)
@@ -792,6 +796,7 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
   p.tma_store = 0;   // a tap's columns end inside the row: register stores clip there
   p.conv_OW = OW; p.conv_OH = OH; p.conv_FW = FW; p.conv_IC = IC;
   p.conv_sw = sw; p.conv_sh = sh; p.conv_pw = pw; p.conv_ph = ph;
+  p.gather = gather ? 1 : 0; p.g_img = dX; p.g_H = IH; p.g_W = IW; p.g_N = N;
   cudaError_t e;
   p.status = status_word_ptr(&e);
   if (!p.status) return static_cast<int>(e);
@@ -1411,6 +1416,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "store_bufs")) { if (value < 0 || value > 2) return CU32_E_ARG; g_store_bufs = value; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { g_arrive_release = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { g_clock_on = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "gather")) { g_force_gather = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
@@ -1426,6 +1432,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "store_bufs")) { *value = g_store_bufs; return CU32_OK; }
   if (!std::strcmp(key, "arrive_release")) { *value = g_arrive_release; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { *value = g_clock_on; return CU32_OK; }
+  if (!std::strcmp(key, "gather")) { *value = g_force_gather; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;

@@ -92,6 +92,11 @@ struct GemmParams {
   // The tap a k-block needs is tap_base + tap_sy * fh + tap_sx * fw (fh, fw: the tap of the im2col load), which
   // expresses reversed and strided tap orders over a filter that stays where it is.
   int tap_base, tap_sy, tap_sx;
+  // Geometries no im2col tensor map can express (strides above 8, window corners outside +-128, taps above 255):
+  // the producer warp gathers the image operand itself with plain loads into the same swizzled tile.
+  int gather;           // 1: gather instead of the im2col-mode tensor map
+  const float* g_img;   // the NHWC tensor the walk runs over (X, or deltaY for the data gradient)
+  int g_H, g_W, g_N;    // its spatial extents and image count; its channel count is conv_IC
   int bmap_order;       // 0: B map coordinates (n, tap, k) - filter W[k][tap][n];  1: (n, k, tap) - filter CW[tap][k][n]
   // Strided output rows (data gradient for strides > 1): row -> (image, u, v) -> element offset
   // image * os_sn + u * os_su + v * os_sv; stores go straight from registers.
@@ -386,10 +391,65 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             oh = r / p.conv_OW;
             ow = r - oh * p.conv_OW;
           }
+          uint32_t tx_bytes = Cfg::HI_BYTES;
+          if (Cfg::IM2COL && p.gather) {
+            // Slow path: the whole warp builds the im2col tile with 16-byte loads, zero outside the image, in the
+            // layout the tensor map would have produced, then publishes it to the async proxy; only the other
+            // operand still arrives by TMA.
+            const int ohw = p.conv_OH * p.conv_OW;
+            const int chunk = lane & 7, sub = lane >> 3;
+            if (Cfg::IM2COL_A) {
+              // K-major A tile: row r = output pixel row0 + r, 32 channels = 8 chunks at r*128 + ((c ^ (r & 7)) * 16)
+#pragma unroll 1
+              for (int rr = 0; rr < Cfg::BM / 4; ++rr) {
+                const int r = rr * 4 + sub;
+                const int pix = w.row0 + r;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (pix < p.M && ic0 + chunk * 4 < p.conv_IC) {
+                  const int pn = pix / ohw, pr = pix - pn * ohw;
+                  const int poh = pr / p.conv_OW, pow_ = pr - poh * p.conv_OW;
+                  const int ih = poh * p.conv_sh - p.conv_ph + fh, iw = pow_ * p.conv_sw - p.conv_pw + fw;
+                  if (ih >= 0 && ih < p.g_H && iw >= 0 && iw < p.g_W)
+                    v = __ldg(reinterpret_cast<const float4*>(
+                        p.g_img + ((static_cast<long long>(pn) * p.g_H + ih) * p.g_W + iw) * p.conv_IC + ic0 + chunk * 4));
+                }
+                sts128(a_dst + r * 128 + ((chunk ^ (r & 7)) * 16), v);
+              }
+              tx_bytes = Cfg::B_BYTES;
+            } else {
+              // MN-major B slabs of [32 pixels][32 channels], 32-byte-unit swizzle: 16-byte chunk c of pixel row k at
+              // k*128 + (((c >> 1) ^ (k & 3)) << 5) + (c & 1) * 16
+              const long long gk = static_cast<long long>(p.nkb_total) * Cfg::BK;   // >= the true pixel count; rows beyond the images read zeros below
+#pragma unroll 1
+              for (int j = 0; j < Cfg::BN_CTA / 32; ++j) {
+                const int ch0 = w.bcol0 + 32 * j + chunk * 4;
+#pragma unroll 1
+                for (int kk2 = 0; kk2 < 8; ++kk2) {
+                  const int k = kk2 * 4 + sub;
+                  const long long pix = static_cast<long long>(k0) + k;
+                  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                  if (pix < gk && ch0 < p.N) {
+                    const int pn = static_cast<int>(pix / ohw), pr = static_cast<int>(pix - static_cast<long long>(pn) * ohw);
+                    const int poh = pr / p.conv_OW, pow_ = pr - poh * p.conv_OW;
+                    const int ih = poh * p.conv_sh - p.conv_ph + fh, iw = pow_ * p.conv_sw - p.conv_pw + fw;
+                    if (pn < p.g_N && ih >= 0 && ih < p.g_H && iw >= 0 && iw < p.g_W)
+                      v = __ldg(reinterpret_cast<const float4*>(
+                          p.g_img + ((static_cast<long long>(pn) * p.g_H + ih) * p.g_W + iw) * p.conv_IC + ch0));
+                  }
+                  sts128(b_dst + j * 4096 + k * 128 + ((((chunk >> 1) ^ (k & 3)) << 5) | ((chunk & 1) << 4)), v);
+                }
+              }
+              tx_bytes = Cfg::A_BYTES;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
           // one single-thread region for all copies of the k-block
           if (elect_one()) {
-            mbar_arrive_expect_tx(full, Cfg::HI_BYTES);
-            if (Cfg::IM2COL_A) {
+            mbar_arrive_expect_tx(full, tx_bytes);
+            if (Cfg::IM2COL_A && p.gather) {
+              // the A tile is in place already
+            } else if (Cfg::IM2COL_A) {
               tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
                                  oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
                                  static_cast<uint16_t>(fh), pol_a);
@@ -400,7 +460,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             } else {
               tma_load_3d(a_dst, &p.tmA, full, k0, w.row0, w.batch, pol_a);
             }
-            if (Cfg::IM2COL_B) {
+            if (Cfg::IM2COL_B && p.gather) {
+              // the B slabs are in place already
+            } else if (Cfg::IM2COL_B) {
               // 32 pixels x 32 channels of tap (fh, fw) per slab; slabs that would start past the last
               // channel re-read the last block instead (their output columns are never stored)
               const int cmax = ((p.N - 1) >> 5) << 5;

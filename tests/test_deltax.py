@@ -82,7 +82,6 @@ def test_deltax_argument_errors_without_gpu(pkg):
     f = lib.cu32_dconv3D_deltaX_s1
     #           dY  OH OW  W  FH FW  dX  IH IW  N  IC OC ph pw
     assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 9, 8, 2, 8, 8, 1, 1) == -2      # IH inconsistent with OH, FH, ph
-    assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 4, 4, 2, 8, 8, 3, 3) == -5      # padding beyond the filter reach
     assert f(s, 1, None, 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 1, 1) == -1
     assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 6, 8, 1, 1) == -4      # IC % 4
     assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 6, 1, 1) == -4      # OC % 4
@@ -384,7 +383,6 @@ def test_strided_argument_errors_without_gpu(pkg):
     assert f(s, 1, None, 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 2, 2, 1, 1) == -1
     assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 6, 8, 2, 2, 1, 1) == -4   # IC % 4
     assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 0, 2, 1, 1) == -2   # stride 0
-    assert f(s, 1, P(ok), 2, 2, P(ok), 3, 3, P(ok), 20, 20, 2, 8, 8, 17, 17, 0, 0) == -5  # stride beyond 16
     assert lib.cu32_dconv3D_deltaX_crossAdd_SGM(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 2, 2, 1, 1, 0) == -8
     assert lib.cu32_dconv3D_deltaX_ksIms2R(s, 0, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 1, 1) == -3   # no stream
     r = lib.cu32_ks_remodev2
