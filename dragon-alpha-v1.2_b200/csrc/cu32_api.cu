@@ -29,6 +29,7 @@ static std::atomic<int> g_store_bufs{0};
 static std::atomic<int> g_arrive_release{0};
 static std::atomic<int> g_sm_reserve{0};
 static std::atomic<int> g_force_gather{0};
+static std::atomic<int> g_phase_overlap{1};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -622,6 +623,7 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
   }
   int* status = status_word_ptr(&e);
   if (!status) return static_cast<int>(e);
+  int launched = 0;   // phases write disjoint pixels: every phase after the first may overlap the one before it
   for (int y = 0; y < sh; ++y)
     for (int x = 0; x < sw; ++x) {
       if (y >= FH || x >= FW) continue;
@@ -701,8 +703,10 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       p.conv_sw = 1; p.conv_sh = 1; p.conv_pw = -lower_w; p.conv_ph = -lower_h;
       p.gather = gather ? 1 : 0; p.g_img = dDY; p.g_H = OH; p.g_W = OW; p.g_N = N;
       p.status = status;
+      p.overlap_prev = (launched > 0 && g_phase_overlap.load()) ? 1 : 0;
       e = launch_gemm_kn(tile, true, true, p, 1, st);
       if (e != cudaSuccess) return static_cast<int>(e);
+      ++launched;
     }
   return static_cast<int>(cudaPeekAtLastError());
 }
@@ -1417,6 +1421,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "arrive_release")) { g_arrive_release = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { g_clock_on = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "gather")) { g_force_gather = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "phase_overlap")) { g_phase_overlap = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
@@ -1433,6 +1438,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "arrive_release")) { *value = g_arrive_release; return CU32_OK; }
   if (!std::strcmp(key, "clock")) { *value = g_clock_on; return CU32_OK; }
   if (!std::strcmp(key, "gather")) { *value = g_force_gather; return CU32_OK; }
+  if (!std::strcmp(key, "phase_overlap")) { *value = g_phase_overlap; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;

@@ -83,6 +83,8 @@ struct GemmParams {
   int ring_lo;          // lo slots, 1..ring_raw (FP32-accurate mode only)
   int store_bufs;       // 4 KB store-staging tiles per drain warp, 1 or 2
   int arrive_release;   // debugging aid: remote mbarrier arrives carry a cluster-scope release
+  int overlap_prev;     // host side only: this launch may start while the previous launch on the stream is still
+                        // running (it does not depend on its results - the phases of a strided data gradient)
   int sm_reserve;       // SMs the persistent grid leaves free (for a collective's kernels running beside it)
   // im2col geometry (A gathered from an NHWC feature map); unused otherwise.
   // The reduction index runs over (fh, fw, ic) with every filter tap padded to
@@ -312,6 +314,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   if (CTAS == 2) cluster_sync();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // A launch that declared itself independent of this one (GemmParams::overlap_prev) may be scheduled from here on;
+  // its CTAs then take over SMs as this grid's CTAs retire, instead of waiting for the whole grid.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // CTA 0 times itself in SM cycles and in nanoseconds: summed over launches, cycles / ns is the clock the
   // kernel really ran at (the management library's reading is a coarse sample and can miss short runs).
   long long clk_t0 = 0;

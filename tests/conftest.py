@@ -55,8 +55,9 @@ def _default_tuning(request):
         p.cu32.tune("tile", -1)
         p.cu32.tune("kc", DEFAULT_KC["kc"])
         p.cu32.tune("kc_fast", DEFAULT_KC["kc_fast"])
-        for key in ("ring_raw", "ring_lo", "store_bufs", "arrive_release", "sm_reserve"):
+        for key in ("ring_raw", "ring_lo", "store_bufs", "arrive_release", "sm_reserve", "gather"):
             p.cu32.tune(key, 0)
+        p.cu32.tune("phase_overlap", 1)
 
 
 DEFAULT_KC = {"kc": 2, "kc_fast": 4}
