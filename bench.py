@@ -57,7 +57,9 @@ UNIT = "TFLOP/s"
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
 # one ncu capture of the same workload; the captures are summarised in profiles/).
 NCU_TRAFFIC_BYTES = {
-    "c2_ab": 2.53e9,     # profiles/gemm_tf32_matMul_AB_8192_traffic.md
+    "c2_ab": 2.54e9,     # profiles/gemm_tf32_matMul_AB_8192_traffic.md (same file for the two below)
+    "c3_qk": 1.291e9,
+    "c3_sm": 1.283e9,
 }
 
 
@@ -868,7 +870,7 @@ def main():
         return
 
     roof = roofline_of(a.workload, wl, ms_compute, pk, sustained=a.steps * ms_compute > 1500.0,
-                       traffic=NCU_TRAFFIC_BYTES.get(a.workload) if a.size == 8192 else None)
+                       traffic=NCU_TRAFFIC_BYTES.get(a.workload) if (a.size == 8192 and a.batch == 1024) else None)
 
     # ---- where the fraction comes from: (tensor-pipe utilisation at the clock the kernel ran at) x (that clock / max)
     clock = dict(dev_clk)
