@@ -669,6 +669,8 @@ def main():
     ap.add_argument("--size", type=int, default=8192, help="edge of the c2_* cubes (profiling on a smaller case)")
     ap.add_argument("--batch", type=int, default=1024, help="batch of the c3_* workloads (smaller for profiling)")
     ap.add_argument("--images", type=int, default=256, help="images of the c4 workload (smaller for profiling)")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="cu32_tune setting applied before anything runs (diagnostics), e.g. rep_lazy=0")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -678,6 +680,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:   # peer-mapped output copies use plain mappings, never an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
     import __graft_entry__ as entry
     pkg = entry.load_package()
@@ -714,6 +718,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg.cu32.load()
     pkg.cu32.tune("clock", 1)
+    for kv in a.tune:
+        key, _, val = kv.partition("=")
+        pkg.cu32.tune(key, int(val))
     pk = peaks()
 
     wl = Workload(a.workload, pkg, torch, rank, a.size, a.batch, a.images)

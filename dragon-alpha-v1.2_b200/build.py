@@ -23,7 +23,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CUFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-CU_SOURCES = ["cu32_api.cu", "gemm_kk.cu", "gemm_kk_softmax.cu", "gemm_kn.cu", "gemm_nn.cu", "gemm_nn_im2col.cu"]
+CU_SOURCES = ["cu32_api.cu", "gemm_kk.cu", "gemm_kk_softmax.cu", "gemm_rep.cu", "gemm_kn.cu", "gemm_nn.cu", "gemm_nn_im2col.cu"]
 CPP_SOURCES = ["jni_exports.cpp"]
 HEADERS = ["sm100_ptx.cuh", "gemm_tf32.cuh", "gemm_launch.h", "jni_min.h", "../../include/dragon_cu32.h",
            "../../include/dragon_cuda.h"]

@@ -30,6 +30,7 @@ static std::atomic<int> g_arrive_release{0};
 static std::atomic<int> g_sm_reserve{0};
 static std::atomic<int> g_force_gather{0};
 static std::atomic<int> g_phase_overlap{1};
+static std::atomic<int> g_rep_lazy{1};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -203,6 +204,8 @@ static int run_gemm(const GemmCall& c) {
   }
   if (c.scale_on && (c.gz != 1 || c.bias)) return CU32_E_ARG;
   if (c.n_replicas < 0 || c.n_replicas > 7 || (c.n_replicas > 0 && (!c.replicas || c.gz != 1))) return CU32_E_ARG;
+  // the copies are written by two instantiations only: FP32-accurate, row-major A, not a convolution
+  if (c.n_replicas > 0 && (!c.x3 || c.a_mn)) return CU32_E_ARG;
   if (!load_driver_entry_points()) return CU32_E_DRIVER;
 
   int tile = pick_tile(c.M, c.n_store, c.gz > 1 ? c.gz : c.batch);
@@ -214,6 +217,7 @@ static int run_gemm(const GemmCall& c) {
                            static_cast<double>(c.K) * c.n_store + static_cast<double>(c.M) * c.n_store));
   const bool below_ridge = c.x3 && c.gz == 1 && intensity < 44.0;
   if (below_ridge && g_tile.load() < 0 && c.n_store <= 64 && c.M >= 128) tile = note_tile(TILE_1x64);
+  if (c.n_replicas > 0) tile = note_tile(TILE_2x256);
   const int ctas = tile_ctas(tile), bn = tile_bn(tile);
 
   GemmParams p;
@@ -266,6 +270,10 @@ static int run_gemm(const GemmCall& c) {
       if (int r2 = make_map3(&p.tmRep[i], c.replicas[i], c.n_store, c.M, zs_c, c.ldc, sc, 32, 32, false)) return r2;
     }
     p.n_rep = c.n_replicas;
+    if (c.n_replicas > 0 && g_rep_lazy.load() && c.batch == 1 && c.gz == 1) {
+      p.rep_lazy = 1;
+      for (int i = 0; i < c.n_replicas; ++i) p.rep_ptr[i] = c.replicas[i];
+    }
   } else if (c.n_replicas > 0) {
     return CU32_E_ALIGN;   // the copies are written by the tensor-map store path only
   }
@@ -276,7 +284,8 @@ static int run_gemm(const GemmCall& c) {
 
   // Batches (or split-K slices) are folded into the kernel's tile index.
   const int zs = c.gz > 1 ? c.gz : c.batch;
-  if (c.a_mn && c.b_mn)       e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
+  if (c.n_replicas > 0)       e = launch_gemm_rep(c.b_mn, p, zs, c.stream);
+  else if (c.a_mn && c.b_mn)  e = launch_gemm_nn(tile, c.x3, p, zs, c.stream);
   else if (!c.a_mn && c.b_mn) e = launch_gemm_kn(tile, c.x3, false, p, zs, c.stream);
   else if (!c.a_mn)           e = launch_gemm_kk(tile, c.x3, false, p, zs, c.stream);
   else return CU32_E_ARG;
@@ -1422,6 +1431,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "clock")) { g_clock_on = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "gather")) { g_force_gather = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "phase_overlap")) { g_phase_overlap = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "rep_lazy")) { g_rep_lazy = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
@@ -1439,6 +1449,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "clock")) { *value = g_clock_on; return CU32_OK; }
   if (!std::strcmp(key, "gather")) { *value = g_force_gather; return CU32_OK; }
   if (!std::strcmp(key, "phase_overlap")) { *value = g_phase_overlap; return CU32_OK; }
+  if (!std::strcmp(key, "rep_lazy")) { *value = g_rep_lazy; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;

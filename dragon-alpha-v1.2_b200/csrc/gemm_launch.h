@@ -53,6 +53,8 @@ cudaError_t launch_gemm_kn(int tile_cfg, bool x3, bool im2col, const GemmParams&
 cudaError_t launch_gemm_nn(int tile_cfg, bool x3, const GemmParams& p, int grid_z, cudaStream_t stream);
 //   KK + row softmax : P = softmax_rows(alpha * A * B^T), at most 512 columns, reduction of at most kc k-blocks
 cudaError_t launch_gemm_kk_softmax(const GemmParams& p, int grid_z, cudaStream_t stream);
+// output kept in further copies: A[M][K] x B[K][N] (b_mn) or A[M][K] x B[N][K]^T, 256x256 pair tile, FP32-accurate
+cudaError_t launch_gemm_rep(bool b_mn, const GemmParams& p, int grid_z, cudaStream_t stream);
 //   NN + im2col : A[K][M], B = im2col walk over an NHWC image, K = output pixels (weight gradient; FP32-accurate only)
 cudaError_t launch_gemm_nn_im2col(int tile_cfg, const GemmParams& p, int grid_z, cudaStream_t stream);
 

@@ -56,6 +56,11 @@ struct GemmParams {
   CUtensorMap tmRep[7];  // further copies of the output (same dims and box as tmC), e.g. the same rows of a gathered
                          // output in the memory of the other GPUs of an NVLink domain, mapped into this process
   int n_rep;             // how many of them are valid: every store to C is repeated to each (stores only, never loads)
+  float* rep_ptr[7];     // the same copies as plain pointers (same pitch as C), for the lazy mode below
+  int rep_lazy;          // 1: the drain warps store a finished block to C only and carry it to the copies while the
+                         // next tile is being multiplied - 16-byte loads of C from L2, 16-byte stores to every
+                         // copy, a row segment at a time between two drains - so that the links to the other GPUs
+                         // see a steady stream instead of every CTA's whole tile at once (one batch, no split-K)
   float* C;             // output of batch 0 / split-K slice 0
   const float* bias;    // optional row vector added to every output row before the store (gz == 1 only)
   int bias_width;       // columns < bias_width get acc + bias[col]; columns >= bias_width are stored as 0
@@ -113,13 +118,17 @@ struct GemmParams {
 
 enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5, ROLE_SELFTEST = 7 };
 
-template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false, bool SOFTMAX_ = false>
+template <int BN_, int CTAS_, bool A_MN_, bool B_MN_, bool X3_, bool IM2COL_ = false, bool SOFTMAX_ = false,
+          bool REP_ = false>
 struct GemmCfg {
   static constexpr int BN = BN_, CTAS = CTAS_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, X3 = X3_, IM2COL = IM2COL_;
   // SOFTMAX: the rows of the product (at most 512 columns: the two TMEM buffers side by side) are normalised
   // with a softmax before they leave the SM - the attention scores never exist in memory.
   static constexpr bool SOFTMAX = SOFTMAX_;
+  // REP: the output is kept in up to seven further copies (GemmParams::tmRep / rep_ptr); the other
+  // instantiations carry none of that code.
+  static constexpr bool REP = REP_;
   static_assert(!SOFTMAX_ || (BN_ == 256 && CTAS_ == 2 && X3_ && !A_MN_ && !B_MN_ && !IM2COL_),
                 "the row softmax is built on the 256x256 pair tile of the A * B^T form");
   static constexpr int BM = 128;            // rows of A (and TMEM lanes) per CTA
@@ -703,6 +712,49 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     const uint32_t sbufs = static_cast<uint32_t>(p.store_bufs);
     const uint32_t stg0 = stg_base + (warp - Cfg::DRAIN_WARP0) * sbufs * Cfg::STAGING_TILE;
     bool alive = true;
+    // Lazy copies: the block this warp stored last (32 rows x CW columns of C) is carried to the further copies
+    // in FW_STEPS steps of one 16-byte vector per lane.
+    constexpr int FW_VPR = CW / 4;                 // vectors per row segment
+    constexpr int FW_RPS = 32 / FW_VPR > 0 ? 32 / FW_VPR : 1;   // rows per step
+    constexpr int FW_STEPS = 32 / FW_RPS;
+    static_assert(CW <= 128 && (CW % 4) == 0, "a row segment of a drain warp is at most 32 vectors");
+    int fw_step = FW_STEPS, fw_r0 = 0, fw_c0 = 0;   // nothing pending
+    bool fw_fresh = false;                          // the block's own stores to C have not been waited for yet
+    auto forward_until = [&](int target, bool batched) {
+      if (fw_step >= target) return;
+      if (fw_fresh) {   // the TMA stores of the block (issued by lane 0) have completed before anyone reads C
+        if (lane == 0) { tma_store_wait_all(); fence_proxy_async_all(); }
+        __syncwarp();
+        fw_fresh = false;
+      }
+      const int cc = fw_c0 + (lane % FW_VPR) * 4;
+      const bool col_ok = cc < p.N;               // p.N is a multiple of 4 on this path
+      auto off_of = [&](int step) -> long long {
+        const int r = fw_r0 + step * FW_RPS + lane / FW_VPR;
+        return (col_ok && r < p.M) ? static_cast<long long>(r) * p.ldc + cc : -1;
+      };
+      // four loads in flight where the registers are free for them (between tiles and at the end)
+      if (batched) for (; fw_step + 4 <= target; fw_step += 4) {
+        long long o[4];
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          o[u] = off_of(fw_step + u);
+          if (o[u] >= 0) v[u] = ldg128_l2(p.C + o[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (o[u] >= 0)
+            for (int i = 0; i < p.n_rep; ++i) *reinterpret_cast<float4*>(p.rep_ptr[i] + o[u]) = v[u];
+      }
+      for (; fw_step < target; ++fw_step) {
+        const long long o = off_of(fw_step);
+        if (o >= 0) {
+          const float4 v = ldg128_l2(p.C + o);
+          for (int i = 0; i < p.n_rep; ++i) *reinterpret_cast<float4*>(p.rep_ptr[i] + o) = v;
+        }
+      }
+    };
     for (long long i_tile = 0, t; alive && (t = tile_at(Cfg::SOFTMAX ? i_tile * subs : i_tile)) >= 0; ++i_tile) {
       const TileWork w = decode(t);
       if constexpr (Cfg::SOFTMAX) {
@@ -857,6 +909,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       int since = 0;
       for (int c = 0;; ++c) {
         if (c < nchunks) {
+          // the previous block's way to the copies is spread evenly over this tile's chunks
+          if constexpr (Cfg::REP)
+            if (fw_step < FW_STEPS) forward_until(((c + 1) * FW_STEPS + nchunks - 1) / nchunks, false);
           const int buf = ch & 1;
           const uint32_t par = (ch >> 1) & 1;
           if (!mbar_wait(smem_u32(&bar_tmem_full[buf]), par, &abort_flag)) {
@@ -966,14 +1021,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               if (lane == 0) {
                 if (first) tma_store_3d(cmap, stg, c0, r0, w.zc);
                 else tma_reduce_add_3d(cmap, stg, c0, r0, w.zc);
-                for (int i = 0; i < p.n_rep; ++i) {   // the same piece to every further copy of the output
-                  if (first) tma_store_3d(&p.tmRep[i], stg, c0, r0, w.zc);
-                  else tma_reduce_add_3d(&p.tmRep[i], stg, c0, r0, w.zc);
+                if constexpr (Cfg::REP) if (!p.rep_lazy) {
+                  for (int i = 0; i < p.n_rep; ++i) {   // the same piece to every further copy of the output
+                    if (first) tma_store_3d(&p.tmRep[i], stg, c0, r0, w.zc);
+                    else tma_reduce_add_3d(&p.tmRep[i], stg, c0, r0, w.zc);
+                  }
                 }
                 tma_store_commit();
               }
               ++pc;
             }
+          }
+          if constexpr (Cfg::REP) if (last && p.rep_lazy) {   // this block becomes the pending one (the previous one has gone out by now)
+            forward_until(FW_STEPS, true);
+            fw_step = 0; fw_r0 = w.row0 + q * 32; fw_c0 = w.col0 + h * CW; fw_fresh = true;
           }
         } else if (p.os_on) {
           // Rows are strided pixels (one phase of a strided data gradient), which no tiled tensor map can
@@ -1049,6 +1110,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
       }
       if (!alive) break;
     }
+    if constexpr (Cfg::REP)
+      if (alive) forward_until(FW_STEPS, true);   // the last block's copies
     // stores still in flight read this CTA's shared memory: let them finish before exit
     if (lane == 0) tma_store_wait_all();
   }

@@ -101,6 +101,20 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Orders this thread's generic-proxy accesses to global memory after async-proxy (TMA) accesses it has
+// waited for, and the other way round.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// A 16-byte load that is served by L2 (never by a stale L1 line): for data another unit of this GPU wrote.
+__device__ __forceinline__ float4 ldg128_l2(const float* ptr) {
+  float4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------- TMA loads
 // Tiled loads: coordinates innermost first.  The innermost coordinate times the
 // element size must be a multiple of 16 bytes (callers pass multiples of 32 floats).

@@ -80,6 +80,10 @@ class PeerGather:
     ``replicas`` the device addresses of this rank's block inside the peers' copies."""
 
     def __init__(self, dist, world: int, rank: int, block_shape, device):
+        import os
+        # plain peer mappings only: no NVLink multicast object is bound to this memory (a rank that exits early
+        # must not leave one behind)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch
         import torch.distributed._symmetric_memory as symm
         self.world, self.rank = world, rank

@@ -58,6 +58,7 @@ def _default_tuning(request):
         for key in ("ring_raw", "ring_lo", "store_bufs", "arrive_release", "sm_reserve", "gather"):
             p.cu32.tune(key, 0)
         p.cu32.tune("phase_overlap", 1)
+        p.cu32.tune("rep_lazy", 1)
 
 
 DEFAULT_KC = {"kc": 2, "kc_fast": 4}

@@ -109,18 +109,24 @@ def test_replicated_stores_write_every_copy(pkg, cuda):
     copies of a gathered output; here all local).  Every copy equals the plain product bit for bit, canaries
     around each copy stay intact, and a request the tensor-map store path cannot serve is refused."""
     mm = pkg.cu32.Cuda_matMul
+    # shapes: ragged edges; one tile; fewer rows than a tile; more tiles than CTA pairs (a block is carried to the
+    # copies while the next tile is multiplied); a reduction long enough to leave the registers twice
+    shapes = [(520, 388, 260), (256, 256, 64), (132, 68, 96), (2308, 2304, 160), (260, 516, 8192 + 96)]
     for form, fn in (("AB", mm.matMul_replicated), ("T2", mm.matMulT2_replicated)):
-        for (N, M, K) in [(520, 388, 260), (256, 256, 64), (132, 68, 96)]:
+        for (N, M, K) in shapes:
             sa, sb = G.mm_shapes(form, N, M, K)
             A, B = G.rand_pm1(sa, 11), G.rand_pm1(sb, 12)
             base = G.matmul(pkg, form, A, B, N, M, K)
             dA, dB = G.dev(A), G.dev(B)
-            for n_rep in (0, 1, 3, 7):
-                outs = [G.Out(N * M) for _ in range(n_rep + 1)]
-                fn([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), outs[0].ptr, [o.ptr for o in outs[1:]], N, M, K)
-                for i, o in enumerate(outs):
-                    assert np.array_equal(o.host((N, M)), base), (form, N, M, K, n_rep, i)
-                G.check_status(pkg)
+            for lazy in (1, 0):     # copies carried over from C between drains / every store repeated at once
+                pkg.cu32.tune("rep_lazy", lazy)
+                for n_rep in ((0, 1, 3, 7) if N * M < 1 << 20 else (2, 7)):
+                    outs = [G.Out(N * M) for _ in range(n_rep + 1)]
+                    fn([G.stream()], 1, dA.data_ptr(), dB.data_ptr(), outs[0].ptr, [o.ptr for o in outs[1:]], N, M, K)
+                    for i, o in enumerate(outs):
+                        assert np.array_equal(o.host((N, M)), base), (form, N, M, K, lazy, n_rep, i)
+                    G.check_status(pkg)
+            pkg.cu32.tune("rep_lazy", 1)
     dA, dB = G.dev(G.rand_pm1((64, 64), 1)), G.dev(G.rand_pm1((64, 64), 2))
     out = G.Out(64 * 64)
     with pytest.raises(pkg.cu32.CudaException) as ei:
