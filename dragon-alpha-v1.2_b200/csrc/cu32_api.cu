@@ -31,6 +31,8 @@ static std::atomic<int> g_sm_reserve{0};
 static std::atomic<int> g_force_gather{0};
 static std::atomic<int> g_phase_overlap{1};
 static std::atomic<int> g_rep_lazy{1};
+static std::atomic<int> g_ring_paired{1};
+static std::atomic<int> g_ring_fixed{1};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -186,6 +188,8 @@ static void choose_rings(GemmParams* p) {
   if (p->ring_raw > 0 && p->ring_lo == 0) p->ring_lo = p->ring_raw;
   if (p->ring_raw == 0) p->ring_lo = 0;
   p->arrive_release = g_arrive_release.load();
+  p->ring_paired = g_ring_paired.load();
+  p->ring_fixed = g_ring_fixed.load();   // allowed; the launcher decides whether the rings are the default ones
   p->sm_reserve = g_sm_reserve.load();
   p->clock_acc = clock_acc_ptr();
 }
@@ -1432,6 +1436,8 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "gather")) { g_force_gather = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "phase_overlap")) { g_phase_overlap = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "rep_lazy")) { g_rep_lazy = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "ring_paired")) { g_ring_paired = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "ring_fixed")) { g_ring_fixed = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
@@ -1450,6 +1456,8 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "gather")) { *value = g_force_gather; return CU32_OK; }
   if (!std::strcmp(key, "phase_overlap")) { *value = g_phase_overlap; return CU32_OK; }
   if (!std::strcmp(key, "rep_lazy")) { *value = g_rep_lazy; return CU32_OK; }
+  if (!std::strcmp(key, "ring_paired")) { *value = g_ring_paired; return CU32_OK; }
+  if (!std::strcmp(key, "ring_fixed")) { *value = g_ring_fixed; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;

@@ -87,6 +87,8 @@ struct GemmParams {
   int ring_raw;         // raw slots, 2..8
   int ring_lo;          // lo slots, 1..ring_raw (FP32-accurate mode only)
   int store_bufs;       // 4 KB store-staging tiles per drain warp, 1 or 2
+  int ring_paired;      // equally long rings: lo tiles interleaved with the raw tiles (1) or in a ring of their own (0)
+  int ring_fixed;       // set by the launcher: the rings are the configuration's default, use the compile-time path
   int arrive_release;   // debugging aid: remote mbarrier arrives carry a cluster-scope release
   int overlap_prev;     // host side only: this launch may start while the previous launch on the stream is still
                         // running (it does not depend on its results - the phases of a strided data gradient)
@@ -200,8 +202,12 @@ struct TileWork {
   bool to_cbuf;  // this tile's output goes to the split-K partial buffers
 };
 
-template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
+// FIXED: the rings are the configuration's balanced default (Cfg::STAGES raw slots, as many lo slots, each lo
+// tile right behind its raw tile), known at compile time - slot addresses and wrap-arounds fold into constants,
+// which the shared-memory-bound narrower tiles need (measured: 12-15 % on the 256x128 pair tile).  Otherwise the
+// ring geometry comes from the launch parameters.
+template <class Cfg, bool FIXED>
+__device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
   using namespace ptx;
   constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, CW = Cfg::CW;
   constexpr bool X3 = Cfg::X3;
@@ -224,11 +230,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
 
   // ring geometry (launch parameters, uniform over the grid)
-  const uint32_t R = static_cast<uint32_t>(p.ring_raw);
-  const uint32_t L = X3 ? static_cast<uint32_t>(p.ring_lo) : R;
+  const uint32_t R = FIXED ? static_cast<uint32_t>(Cfg::STAGES) : static_cast<uint32_t>(p.ring_raw);
+  const uint32_t L = FIXED ? R : (X3 ? static_cast<uint32_t>(p.ring_lo) : R);
   const uint32_t raw_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t lo_base = raw_base + R * Cfg::HI_BYTES;
-  const uint32_t stg_base = lo_base + (X3 ? L * Cfg::HI_BYTES : 0u);
+  // With equally long rings a k-block's lo tiles sit right behind its raw tiles ([raw 0][lo 0][raw 1][lo 1]...);
+  // with a shorter lo ring the two rings are separate ([raw 0..R-1][lo 0..L-1]).
+  const bool paired = FIXED ? X3 : (X3 && L == R && p.ring_paired);
+  const uint32_t raw_stride = paired ? 2u * Cfg::HI_BYTES : static_cast<uint32_t>(Cfg::HI_BYTES);
+  const uint32_t lo_stride = raw_stride;
+  const uint32_t lo_base = paired ? raw_base + Cfg::HI_BYTES : raw_base + R * Cfg::HI_BYTES;
+  const uint32_t stg_base = raw_base + R * Cfg::HI_BYTES + (X3 ? L * Cfg::HI_BYTES : 0u);
 
   // ---- persistent tile loop: this CTA (pair) takes tiles first, first + step, ...
   // Tile ids run over (z, m-group, n, m-in-group); concurrently resident tiles are
@@ -376,7 +387,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
           }
           const uint32_t full = smem_u32(&bar_full_tma[s]);
           int k0 = (w.kb0 + i) * Cfg::BK;
-          const uint32_t a_dst = raw_base + s * Cfg::HI_BYTES;
+          const uint32_t a_dst = raw_base + s * raw_stride;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           // im2col coordinates: k-block -> (filter tap, block of 32 channels inside the tap);
           // row0 addresses output pixel (n, oh, ow), and the run of 128 pixels wraps over
@@ -572,9 +583,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
             }
           }
           tc_fence_after();
-          const uint32_t a_hi = raw_base + s * Cfg::HI_BYTES;
+          const uint32_t a_hi = raw_base + s * raw_stride;
           const uint32_t b_hi = a_hi + Cfg::A_BYTES;
-          const uint32_t a_lo = lo_base + l * Cfg::HI_BYTES;
+          const uint32_t a_lo = lo_base + l * lo_stride;
           const uint32_t b_lo = a_lo + Cfg::A_BYTES;
           const uint32_t d = tmem_base + buf * BN;
           // The tensor core truncates (rounds toward zero) its FP32 accumulator after every
@@ -650,8 +661,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
               break;
             }
           }
-          const uint32_t hi_base = raw_base + s * Cfg::HI_BYTES;
-          const uint32_t lo_slot = lo_base + l * Cfg::HI_BYTES;
+          const uint32_t hi_base = raw_base + s * raw_stride;
+          const uint32_t lo_slot = lo_base + l * lo_stride;
           if (X3) {
             // lo = tf32(x - trunc(x)); x itself stays where TMA put it (the tensor core drops the low
             // 13 mantissa bits of an FP32 operand by itself, so the raw tile already is the hi operand).
@@ -709,7 +720,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
     const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
     uint32_t ch = 0;                                     // chunks drained so far, over all tiles
     uint32_t pc = 0;                                     // 32x32 pieces this warp has sent through TMA stores
-    const uint32_t sbufs = static_cast<uint32_t>(p.store_bufs);
+    const uint32_t sbufs = FIXED ? 1u : static_cast<uint32_t>(p.store_bufs);
     const uint32_t stg0 = stg_base + (warp - Cfg::DRAIN_WARP0) * sbufs * Cfg::STAGING_TILE;
     bool alive = true;
     // Lazy copies: the block this warp stored last (32 rows x CW columns of C) is carried to the further copies
@@ -1128,6 +1139,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
+  if constexpr (Cfg::SOFTMAX) {
+    gemm_tf32_body<Cfg, false>(p);   // always launched with rings of its own
+  } else {
+    if (p.ring_fixed) gemm_tf32_body<Cfg, true>(p);
+    else gemm_tf32_body<Cfg, false>(p);
   }
 }
 

@@ -444,6 +444,9 @@ CU32_API int cu32_batchMatMulT2_softmax(const int64_t* streams, int length, cons
  *   "gather"   1 = the convolution family builds its im2col tiles with plain loads even where a tensor map could
  *              (diagnostics: same bits); 0 = only for geometries no tensor map can express (default)
  *   "phase_overlap" 1 = the launches of a strided data gradient's phases may overlap one another (default); 0 = serial
+ *   "ring_fixed"    1 = launches whose rings are the tile's default use the kernel path with compile-time ring geometry
+ *                   (default); 0 = always the launch-parameter path (diagnostics: same bits)
+ *   "ring_paired"   1 = with equally long rings each lo tile sits right behind its raw tile (default); 0 = two separate rings
  *   "rep_lazy"      1 = the replicated entry points store a finished block to C and carry it to the copies while the
  *                   next tile is multiplied (default); 0 = every store is repeated to every copy at once
  *   "sm_reserve" SMs the contraction kernel's persistent grid leaves free, for kernels a host runs beside it on

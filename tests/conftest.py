@@ -59,6 +59,8 @@ def _default_tuning(request):
             p.cu32.tune(key, 0)
         p.cu32.tune("phase_overlap", 1)
         p.cu32.tune("rep_lazy", 1)
+        p.cu32.tune("ring_fixed", 1)
+        p.cu32.tune("ring_paired", 1)
 
 
 DEFAULT_KC = {"kc": 2, "kc_fast": 4}

@@ -58,6 +58,15 @@ def test_ring_geometry_does_not_change_the_result(pkg, cuda, tile):
                 Y = f()
                 assert np.array_equal(Y, base[k]), (tile, raw, lo, bufs, k, rep, int((Y != base[k]).sum()))
     assert tried >= 3
+    # the default rings through the launch-parameter path (the base ran the compile-time path), lo tiles behind
+    # their raw tiles or in a ring of their own
+    pkg.cu32.tune("ring_raw", 0); pkg.cu32.tune("ring_lo", 0); pkg.cu32.tune("store_bufs", 0)
+    for fixed, paired in [(0, 1), (0, 0), (1, 0)]:
+        pkg.cu32.tune("ring_fixed", fixed); pkg.cu32.tune("ring_paired", paired)
+        for k, f in cases.items():
+            Y = f()
+            assert np.array_equal(Y, base[k]), (tile, "fixed", fixed, "paired", paired, k)
+    pkg.cu32.tune("ring_fixed", 1); pkg.cu32.tune("ring_paired", 1)
 
 
 def test_ring_geometry_that_does_not_fit_is_refused(pkg, cuda):
