@@ -109,8 +109,14 @@ cudaError_t launch_one(const GemmParams& p, int grid_z, cudaStream_t stream) {
   if (q.ring_raw == 0) { q.ring_raw = Cfg::STAGES; q.ring_lo = Cfg::STAGES; }
   if (q.store_bufs == 0) q.store_bufs = 1;
   if (!Cfg::X3) q.ring_lo = q.ring_raw;
-  q.ring_fixed = (p.ring_fixed && q.ring_raw == Cfg::STAGES && q.ring_lo == Cfg::STAGES && q.store_bufs == 1 &&
-                  (!Cfg::X3 || q.ring_paired)) ? 1 : 0;
+  q.ring_fixed = 0;
+  if (p.ring_fixed) {
+    if (q.ring_raw == Cfg::STAGES && q.ring_lo == Cfg::STAGES && q.store_bufs == 1 && (!Cfg::X3 || q.ring_paired) &&
+        !Cfg::SOFTMAX)
+      q.ring_fixed = 1;
+    else if (Cfg::ALT_RAW > 0 && q.ring_raw == Cfg::ALT_RAW && q.ring_lo == Cfg::ALT_LO && q.store_bufs == Cfg::ALT_BUFS)
+      q.ring_fixed = 2;
+  }
   if (q.ring_raw < 2 || q.ring_raw > Cfg::MAX_RING || q.ring_lo < 1 || q.ring_lo > q.ring_raw ||
       q.store_bufs < 1 || q.store_bufs > 2 || Cfg::dyn_smem(q.ring_raw, q.ring_lo, q.store_bufs) > Cfg::MAX_DYN_SMEM)
     return cudaErrorInvalidValue;

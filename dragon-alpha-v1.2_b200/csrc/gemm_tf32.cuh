@@ -88,7 +88,8 @@ struct GemmParams {
   int ring_lo;          // lo slots, 1..ring_raw (FP32-accurate mode only)
   int store_bufs;       // 4 KB store-staging tiles per drain warp, 1 or 2
   int ring_paired;      // equally long rings: lo tiles interleaved with the raw tiles (1) or in a ring of their own (0)
-  int ring_fixed;       // set by the launcher: the rings are the configuration's default, use the compile-time path
+  int ring_fixed;       // set by the launcher: 1 = the rings are the configuration's default, 2 = its below-ridge
+                        // geometry (GemmCfg::ALT_*): use that compile-time path; 0 = the launch parameters
   int arrive_release;   // debugging aid: remote mbarrier arrives carry a cluster-scope release
   int overlap_prev;     // host side only: this launch may start while the previous launch on the stream is still
                         // running (it does not depend on its results - the phases of a strided data gradient)
@@ -141,13 +142,20 @@ struct GemmCfg {
   static constexpr int HI_BYTES = A_BYTES + B_BYTES;   // bytes one k-block brings in by TMA: a raw slot [A][B]
   // Shared memory: [raw ring][lo ring (FP32-accurate mode)][store staging]; the ring lengths are launch
   // parameters.  MAX_DYN_SMEM leaves room for the static barriers inside the 227 KB a CTA may use.
-  static constexpr int MAX_DYN_SMEM = (SOFTMAX_ ? 220 : 226) * 1024;   // the softmax mode keeps 4 KB of row statistics in static shared memory
+  static constexpr int MAX_DYN_SMEM = (SOFTMAX_ ? 216 : 226) * 1024;   // the softmax mode keeps 4 KB of row statistics in static shared memory (once per compiled ring geometry)
   static constexpr int MAX_RING = 8;
   static constexpr int STAGING_TILE = 4096;   // one 32x32 FP32 piece
   // the default, balanced rings: as many (raw + lo) pairs as fit beside one staging tile per drain warp
   static constexpr int PAIR_BYTES = HI_BYTES * (X3 ? 2 : 1);
   static constexpr int STAGES_RAW = (MAX_DYN_SMEM - 1024 - 8 * STAGING_TILE) / PAIR_BYTES;
   static constexpr int STAGES = STAGES_RAW > MAX_RING ? MAX_RING : STAGES_RAW;
+  // the below-ridge geometry (measured on the attention-shaped batched products): 128x64 one-CTA tile 6 raw + 2 lo
+  // slots, 256x256 pair tile 3 + 2 with two staging tiles per drain warp (3 + 2 + 1 with the fused softmax, which
+  // needs the room for its row statistics); 0 = the configuration has none
+  static constexpr bool ALT_OK = X3 && !IM2COL_ && ((BN == 64 && CTAS == 1) || (BN == 256 && CTAS == 2));
+  static constexpr int ALT_RAW = !ALT_OK ? 0 : (BN == 64 ? 6 : 3);
+  static constexpr int ALT_LO = !ALT_OK ? 0 : 2;
+  static constexpr int ALT_BUFS = !ALT_OK ? 0 : (BN == 64 || SOFTMAX_ ? 1 : 2);
   static constexpr int TMEM_NEED = 2 * BN;
   static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
                                    : TMEM_NEED <= 256 ? 256 : 512;
@@ -206,9 +214,13 @@ struct TileWork {
 // tile right behind its raw tile), known at compile time - slot addresses and wrap-arounds fold into constants,
 // which the shared-memory-bound narrower tiles need (measured: 12-15 % on the 256x128 pair tile).  Otherwise the
 // ring geometry comes from the launch parameters.
-template <class Cfg, bool FIXED>
+// A second compile-time geometry serves the shapes below the roofline's ridge (short reductions paced by loads and
+// stores): a long raw ring against the HBM latency with a short lo ring.
+//   RINGS 0 = launch parameters, 1 = balanced default, 2 = the configuration's below-ridge geometry (ALT_*)
+template <class Cfg, int RINGS>
 __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
   using namespace ptx;
+  constexpr bool FIXED = RINGS != 0;
   constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, CW = Cfg::CW;
   constexpr bool X3 = Cfg::X3;
   constexpr bool RELAY = X3 || CTAS == 2;  // MMA waits on the splitters' barrier
@@ -230,12 +242,14 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
   const uint32_t rank = (CTAS == 2) ? cluster_ctarank() : 0u;
 
   // ring geometry (launch parameters, uniform over the grid)
-  const uint32_t R = FIXED ? static_cast<uint32_t>(Cfg::STAGES) : static_cast<uint32_t>(p.ring_raw);
-  const uint32_t L = FIXED ? R : (X3 ? static_cast<uint32_t>(p.ring_lo) : R);
+  const uint32_t R = RINGS == 1 ? static_cast<uint32_t>(Cfg::STAGES) : RINGS == 2 ? static_cast<uint32_t>(Cfg::ALT_RAW)
+                                                                    : static_cast<uint32_t>(p.ring_raw);
+  const uint32_t L = RINGS == 1 ? R : RINGS == 2 ? static_cast<uint32_t>(Cfg::ALT_LO)
+                                                 : (X3 ? static_cast<uint32_t>(p.ring_lo) : R);
   const uint32_t raw_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   // With equally long rings a k-block's lo tiles sit right behind its raw tiles ([raw 0][lo 0][raw 1][lo 1]...);
   // with a shorter lo ring the two rings are separate ([raw 0..R-1][lo 0..L-1]).
-  const bool paired = FIXED ? X3 : (X3 && L == R && p.ring_paired);
+  const bool paired = RINGS == 1 ? X3 : RINGS == 2 ? false : (X3 && L == R && p.ring_paired);
   const uint32_t raw_stride = paired ? 2u * Cfg::HI_BYTES : static_cast<uint32_t>(Cfg::HI_BYTES);
   const uint32_t lo_stride = raw_stride;
   const uint32_t lo_base = paired ? raw_base + Cfg::HI_BYTES : raw_base + R * Cfg::HI_BYTES;
@@ -720,7 +734,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
     const int h = (warp - Cfg::DRAIN_WARP0) >> 2;        // which half of the columns
     uint32_t ch = 0;                                     // chunks drained so far, over all tiles
     uint32_t pc = 0;                                     // 32x32 pieces this warp has sent through TMA stores
-    const uint32_t sbufs = FIXED ? 1u : static_cast<uint32_t>(p.store_bufs);
+    const uint32_t sbufs = RINGS == 1 ? 1u : RINGS == 2 ? static_cast<uint32_t>(Cfg::ALT_BUFS) : static_cast<uint32_t>(p.store_bufs);
     const uint32_t stg0 = stg_base + (warp - Cfg::DRAIN_WARP0) * sbufs * Cfg::STAGING_TILE;
     bool alive = true;
     // Lazy copies: the block this warp stored last (32 rows x CW columns of C) is carried to the further copies
@@ -1144,11 +1158,16 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1) gemm_tf32_kernel(const __grid_constant__ GemmParams p) {
-  if constexpr (Cfg::SOFTMAX) {
-    gemm_tf32_body<Cfg, false>(p);   // always launched with rings of its own
+  if constexpr (Cfg::SOFTMAX) {     // launched with the below-ridge geometry unless a tuning key says otherwise
+    if (p.ring_fixed == 2) gemm_tf32_body<Cfg, 2>(p);
+    else gemm_tf32_body<Cfg, 0>(p);
+  } else if constexpr (Cfg::ALT_RAW > 0) {
+    if (p.ring_fixed == 1) gemm_tf32_body<Cfg, 1>(p);
+    else if (p.ring_fixed == 2) gemm_tf32_body<Cfg, 2>(p);
+    else gemm_tf32_body<Cfg, 0>(p);
   } else {
-    if (p.ring_fixed) gemm_tf32_body<Cfg, true>(p);
-    else gemm_tf32_body<Cfg, false>(p);
+    if (p.ring_fixed == 1) gemm_tf32_body<Cfg, 1>(p);
+    else gemm_tf32_body<Cfg, 0>(p);
   }
 }
 
