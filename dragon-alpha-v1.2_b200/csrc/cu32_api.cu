@@ -157,7 +157,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // small problems pick small tiles.
 static int pick_tile_auto(long long M, int N, long long z) {
   // measured matMul 8192^3 rates per tile shape, TFLOP/s (order of the TileCfg enum)
-  static const double rate[TILE_COUNT] = {115.0, 170.0, 190.0, 190.0, 278.0, 100.0};
+  static const double rate[TILE_COUNT] = {118.0, 170.0, 190.0, 206.0, 278.0, 105.0};
   const double sms = static_cast<double>(device_sm_count());
   int best = TILE_1x128;
   double best_t = 1e300;
