@@ -190,6 +190,20 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
                : "r"(addr));
   return v;
 }
+// The split's accesses: a thread's 16 bytes as two 8-byte accesses 256 bytes apart, so that a warp still covers 512
+// contiguous bytes (chunk = first byte of the warp's 512).  Measured against one 16-byte access per thread: 3-7 %
+// on the shared-memory-bound narrower tiles, nothing on the 256x256 tile; which element a thread holds is
+// irrelevant to the split, which is elementwise.
+__device__ __forceinline__ float4 lds2x64(uint32_t chunk, int lane) {
+  float4 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(chunk + lane * 8));
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.z), "=f"(v.w) : "r"(chunk + 256 + lane * 8));
+  return v;
+}
+__device__ __forceinline__ void sts2x64(uint32_t chunk, int lane, float4 v) {
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(chunk + lane * 8), "f"(v.x), "f"(v.y) : "memory");
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(chunk + 256 + lane * 8), "f"(v.z), "f"(v.w) : "memory");
+}
 __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y),
                "f"(v.z), "f"(v.w)
@@ -210,7 +224,7 @@ struct TileWork {
   bool to_cbuf;  // this tile's output goes to the split-K partial buffers
 };
 
-// FIXED: the rings are the configuration's balanced default (Cfg::STAGES raw slots, as many lo slots, each lo
+// RINGS = 1: the rings are the configuration's balanced default (Cfg::STAGES raw slots, as many lo slots, each lo
 // tile right behind its raw tile), known at compile time - slot addresses and wrap-arounds fold into constants,
 // which the shared-memory-bound narrower tiles need (measured: 12-15 % on the 256x128 pair tile).  Otherwise the
 // ring geometry comes from the launch parameters.
@@ -220,7 +234,6 @@ struct TileWork {
 template <class Cfg, int RINGS>
 __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
   using namespace ptx;
-  constexpr bool FIXED = RINGS != 0;
   constexpr int BN = Cfg::BN, CTAS = Cfg::CTAS, CW = Cfg::CW;
   constexpr bool X3 = Cfg::X3;
   constexpr bool RELAY = X3 || CTAS == 2;  // MMA waits on the splitters' barrier
@@ -651,6 +664,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
       const int st = (warp - Cfg::SPLIT_WARP0) * 32 + lane;
       constexpr int NST = Cfg::SPLIT_WARPS * 32;
       constexpr int NVEC = Cfg::HI_BYTES / 16;
+      static_assert(NVEC % 32 == 0, "a warp's 32 vectors of the split are 512 contiguous bytes inside the slot");
       uint32_t it = 0;
       uint32_t s = 0, ph = 0;     // raw slot = it % R and its phase parity, carried as counters
       uint32_t l = 0;             // lo slot = it % L
@@ -687,7 +701,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
 #pragma unroll
             for (int u = 0; u < G; ++u) {
               const int v = st + u * NST;
-              if (u < PER && v < NVEC) x[0][u] = lds128(hi_base + v * 16);
+              if (u < PER && v < NVEC) x[0][u] = lds2x64(hi_base + (v - lane) * 16, lane);
             }
 #pragma unroll
             for (int b = 0; b < PER; b += G) {
@@ -695,7 +709,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
 #pragma unroll
               for (int u = 0; u < G; ++u) {
                 const int v = st + (b + G + u) * NST;
-                if (b + G + u < PER && v < NVEC) x[cur ^ 1][u] = lds128(hi_base + v * 16);
+                if (b + G + u < PER && v < NVEC) x[cur ^ 1][u] = lds2x64(hi_base + (v - lane) * 16, lane);
               }
 #pragma unroll
               for (int u = 0; u < G; ++u) {
@@ -705,7 +719,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
                   float4 lv;
                   lv.x = rn_tf32(xv.x - trunc_tf32(xv.x)); lv.y = rn_tf32(xv.y - trunc_tf32(xv.y));
                   lv.z = rn_tf32(xv.z - trunc_tf32(xv.z)); lv.w = rn_tf32(xv.w - trunc_tf32(xv.w));
-                  sts128(lo_slot + v * 16, lv);
+                  sts2x64(lo_slot + (v - lane) * 16, lane, lv);
                 }
               }
             }
