@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <atomic>
+#include <vector>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
@@ -33,6 +34,7 @@ static std::atomic<int> g_phase_overlap{1};
 static std::atomic<int> g_rep_lazy{1};
 static std::atomic<int> g_ring_paired{1};
 static std::atomic<int> g_ring_fixed{1};
+static std::atomic<int> g_phase_fused{1};
 
 static void load_env_once() {
   static std::once_flag once;
@@ -636,7 +638,15 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
   }
   int* status = status_word_ptr(&e);
   if (!status) return static_cast<int>(e);
-  int launched = 0;   // phases write disjoint pixels: every phase after the first may overlap the one before it
+  // Every phase with work, heaviest first as the loops run: its tensor maps and the numbers the kernel needs.
+  struct Phase {
+    CUtensorMap tmA, tmB;
+    float* C;
+    long long GM;
+    int nkb, U, V, CFW, conv_pw, conv_ph, tap_base, tap_sy, tap_sx, bmap_order;
+    bool gather;
+  };
+  std::vector<Phase> phs;
   for (int y = 0; y < sh; ++y)
     for (int x = 0; x < sw; ++x) {
       if (y >= FH || x >= FW) continue;
@@ -648,13 +658,11 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       if (U <= 0 || V <= 0) continue;
       const int lower_h = u0 - (CFH - 1), lower_w = v0 - (CFW - 1);
       const int upper_h = lower_h + (U - 1) - (OH - 1), upper_w = lower_w + (V - 1) - (OW - 1);
-      bool gather = g_force_gather.load() != 0 || lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 ||
-                    upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127 || CFH > 256 || CFW > 256;
-      const long long GM = static_cast<long long>(N) * U * V;
-      int tile = pick_tile(GM, IC, 1);
-      const int ctas = tile_ctas(tile), bn = tile_bn(tile);
-      GemmParams p;
-      std::memset(&p, 0, sizeof(p));
+      Phase q;
+      std::memset(&q, 0, sizeof(q));
+      q.gather = g_force_gather.load() != 0 || lower_w < -128 || lower_w > 127 || lower_h < -128 || lower_h > 127 ||
+                 upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127 || CFH > 256 || CFW > 256;
+      q.GM = static_cast<long long>(N) * U * V;
       {
         cuuint64_t dims[4] = {static_cast<cuuint64_t>(OC), static_cast<cuuint64_t>(OW), static_cast<cuuint64_t>(OH),
                               static_cast<cuuint64_t>(N)};
@@ -663,64 +671,96 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
         int lower[2] = {lower_w, lower_h};
         int upper[2] = {upper_w, upper_h};
         cuuint32_t trav[4] = {1, 1, 1, 1};
-        CUresult r = gather ? CUDA_ERROR_INVALID_VALUE
-                            : g_encode_im2col(&p.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dDY), dims, strides,
-                                              lower, upper, 32, 128, trav, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) gather = true;
+        CUresult r = q.gather ? CUDA_ERROR_INVALID_VALUE
+                              : g_encode_im2col(&q.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(dDY), dims, strides,
+                                                lower, upper, 32, 128, trav, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) q.gather = true;
         int drv = 0;   // same driver workaround as in conv_any
         if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
             static_cast<long long>(N) * OH * OW * OC * 4 < 131072)
-          reinterpret_cast<uint64_t*>(&p.tmA)[1] &= ~(1ULL << 21);
+          reinterpret_cast<uint64_t*>(&q.tmA)[1] &= ~(1ULL << 21);
       }
       if (filt_is_cw) {
         // this phase's slot of CW: [CFH][CFW][OC][IC], taps already reversed by ks_remodev2
         const float* base = filt + static_cast<long long>(y * sw + x) * OC * mCFH * mCFW * IC;
-        if (int rc = make_map3(&p.tmB, base, IC, OC, static_cast<uint64_t>(CFH) * CFW, IC,
+        if (int rc = make_map3(&q.tmB, base, IC, OC, static_cast<uint64_t>(CFH) * CFW, IC,
                                static_cast<uint64_t>(OC) * IC, 32, 32, true))
           return rc;
-        p.bmap_order = 1; p.tap_base = 0; p.tap_sy = CFW; p.tap_sx = 1;
+        q.bmap_order = 1; q.tap_base = 0; q.tap_sy = CFW; q.tap_sx = 1;
       } else {
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(IC), static_cast<cuuint64_t>(FH) * FW, static_cast<cuuint64_t>(OC)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(IC) * 4, static_cast<cuuint64_t>(FH) * FW * IC * 4};
         cuuint32_t box[3] = {32, 1, 32};
         cuuint32_t estr[3] = {1, 1, 1};
-        CUresult r = g_encode_tiled(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(filt), dims, strides,
+        CUresult r = g_encode_tiled(&q.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(filt), dims, strides,
                                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return CU32_E_TENSORMAP;
-        p.bmap_order = 0;
-        p.tap_base = (y + (CFH - 1) * sh) * FW + x + (CFW - 1) * sw;
-        p.tap_sy = -sh * FW;
-        p.tap_sx = -sw;
+        q.bmap_order = 0;
+        q.tap_base = (y + (CFH - 1) * sh) * FW + x + (CFW - 1) * sw;
+        q.tap_sy = -sh * FW;
+        q.tap_sx = -sw;
       }
-      p.bias = dBias; p.bias_width = width;
-      p.C = dDX + (static_cast<long long>(u0 * sh + y - ph) * IW + (v0 * sw + x - pw)) * IC;
-      p.Cbuf = nullptr; p.ldc = IC; p.c_stride = 0;
-      p.os_on = 1; p.os_uv = U * V; p.os_v = V;
-      p.os_sn = static_cast<long long>(IH) * IW * IC;
-      p.os_su = static_cast<long long>(sh) * IW * IC;
-      p.os_sv = static_cast<long long>(sw) * IC;
-      p.M = static_cast<int>(GM); p.N = IC;
-      p.conv_icb = (OC + 31) / 32;
-      p.nkb_total = CFH * CFW * p.conv_icb;
-      p.tiles_m = static_cast<int>((GM + 128 * ctas - 1) / (128 * ctas));
-      p.tiles_n = (IC + bn - 1) / bn;
-      p.gz = 1;
-      p.kc = g_kc.load();
-      choose_rings(&p);
-      p.vec4_ok = 1;
-      p.tma_store = 0;
-      p.conv_OW = V; p.conv_OH = U; p.conv_FW = CFW; p.conv_IC = OC;
-      p.conv_sw = 1; p.conv_sh = 1; p.conv_pw = -lower_w; p.conv_ph = -lower_h;
-      p.gather = gather ? 1 : 0; p.g_img = dDY; p.g_H = OH; p.g_W = OW; p.g_N = N;
-      p.status = status;
-      p.overlap_prev = (launched > 0 && g_phase_overlap.load()) ? 1 : 0;
-      e = launch_gemm_kn(tile, true, true, p, 1, st);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      ++launched;
+      q.C = dDX + (static_cast<long long>(u0 * sh + y - ph) * IW + (v0 * sw + x - pw)) * IC;
+      q.nkb = CFH * CFW * ((OC + 31) / 32);
+      q.U = U; q.V = V; q.CFW = CFW; q.conv_pw = -lower_w; q.conv_ph = -lower_h;
+      phs.push_back(q);
     }
+  if (phs.empty()) return static_cast<int>(cudaPeekAtLastError());
+  // One launch for all phases when there are 2..4 of them and tensor maps serve them all: a CTA (pair) then takes
+  // tile j of every phase in turn, so a short phase's drain and stores run under the next phase's MMAs.  Otherwise
+  // one launch per phase; they write disjoint pixels, so every launch after the first may overlap the one before it.
+  bool fuse = g_phase_fused.load() != 0 && phs.size() >= 2 && phs.size() <= 4;
+  for (const Phase& q : phs) fuse = fuse && !q.gather;
+  long long gm_max = 0;
+  for (const Phase& q : phs) gm_max = q.GM > gm_max ? q.GM : gm_max;
+  const size_t launches = fuse ? 1 : phs.size();
+  for (size_t li = 0; li < launches; ++li) {
+    const Phase& q = phs[li];
+    const long long GM = fuse ? gm_max : q.GM;
+    int tile = pick_tile(GM, IC, fuse ? static_cast<long long>(phs.size()) : 1);
+    const int ctas = tile_ctas(tile), bn = tile_bn(tile);
+    GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.tmA = q.tmA; p.tmB = q.tmB;
+    p.bmap_order = q.bmap_order; p.tap_base = q.tap_base; p.tap_sy = q.tap_sy; p.tap_sx = q.tap_sx;
+    p.bias = dBias; p.bias_width = width;
+    p.C = q.C;
+    p.Cbuf = nullptr; p.ldc = IC; p.c_stride = 0;
+    p.os_on = 1; p.os_uv = q.U * q.V; p.os_v = q.V;
+    p.os_sn = static_cast<long long>(IH) * IW * IC;
+    p.os_su = static_cast<long long>(sh) * IW * IC;
+    p.os_sv = static_cast<long long>(sw) * IC;
+    p.M = static_cast<int>(q.GM); p.N = IC;
+    p.conv_icb = (OC + 31) / 32;
+    p.nkb_total = q.nkb;
+    p.tiles_m = static_cast<int>((GM + 128 * ctas - 1) / (128 * ctas));
+    p.tiles_n = (IC + bn - 1) / bn;
+    p.gz = 1;
+    p.kc = g_kc.load();
+    choose_rings(&p);
+    p.vec4_ok = 1;
+    p.tma_store = 0;
+    p.conv_OW = q.V; p.conv_OH = q.U; p.conv_FW = q.CFW; p.conv_IC = OC;
+    p.conv_sw = 1; p.conv_sh = 1; p.conv_pw = q.conv_pw; p.conv_ph = q.conv_ph;
+    p.gather = q.gather ? 1 : 0; p.g_img = dDY; p.g_H = OH; p.g_W = OW; p.g_N = N;
+    p.status = status;
+    if (fuse) {
+      p.n_phases = static_cast<int>(phs.size());
+      for (size_t i = 1; i < phs.size(); ++i) {
+        GemmPhase& x = p.phx[i - 1];
+        const Phase& r = phs[i];
+        x.tmA = r.tmA; x.tmB = r.tmB; x.C = r.C; x.M = static_cast<int>(r.GM); x.nkb = r.nkb;
+        x.OH = r.U; x.OW = r.V; x.FW = r.CFW; x.pw = r.conv_pw; x.ph = r.conv_ph;
+        x.tap_base = r.tap_base; x.tap_sy = r.tap_sy; x.tap_sx = r.tap_sx; x.os_uv = r.U * r.V; x.os_v = r.V;
+      }
+    }
+    p.overlap_prev = (li > 0 && g_phase_overlap.load()) ? 1 : 0;
+    e = launch_gemm_kn(tile, true, true, p, 1, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   return static_cast<int>(cudaPeekAtLastError());
 }
 
@@ -1438,6 +1478,7 @@ int cu32_tune(const char* key, int value) {
   if (!std::strcmp(key, "rep_lazy")) { g_rep_lazy = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "ring_paired")) { g_ring_paired = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "ring_fixed")) { g_ring_fixed = value ? 1 : 0; return CU32_OK; }
+  if (!std::strcmp(key, "phase_fused")) { g_phase_fused = value ? 1 : 0; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { if (value < 0 || value > 1024) return CU32_E_ARG; g_sm_reserve = value; return CU32_OK; }
   return CU32_E_ARG;
 }
@@ -1458,6 +1499,7 @@ int cu32_get_tune(const char* key, int* value) {
   if (!std::strcmp(key, "rep_lazy")) { *value = g_rep_lazy; return CU32_OK; }
   if (!std::strcmp(key, "ring_paired")) { *value = g_ring_paired; return CU32_OK; }
   if (!std::strcmp(key, "ring_fixed")) { *value = g_ring_fixed; return CU32_OK; }
+  if (!std::strcmp(key, "phase_fused")) { *value = g_phase_fused; return CU32_OK; }
   if (!std::strcmp(key, "sm_reserve")) { *value = g_sm_reserve; return CU32_OK; }
   if (!std::strcmp(key, "last_tile")) { *value = g_last_tile; return CU32_OK; }
   return CU32_E_ARG;

@@ -45,6 +45,20 @@
 
 namespace dragon {
 
+// One further phase of a strided data gradient (GemmParams::phx): what differs from phase 0, whose values are the
+// GemmParams fields of the same meaning.
+struct alignas(64) GemmPhase {
+  CUtensorMap tmA;   // im2col map over deltaY with this phase's window corners
+  CUtensorMap tmB;   // this phase's filter slot (or the filter itself)
+  float* C;          // first pixel of the phase in deltaX
+  int M;             // output pixels of the phase (rows)
+  int nkb;           // k-blocks of its reduction
+  int OH, OW, FW;    // conv_OH, conv_OW, conv_FW of the phase
+  int pw, ph;        // conv_pw, conv_ph
+  int tap_base, tap_sy, tap_sx;
+  int os_uv, os_v;
+};
+
 struct GemmParams {
   CUtensorMap tmA;      // K-major A: dims (K, M, batch), box (32, 128, 1)
                         // MN-major A: dims (M, K, batch), box (32, 32, 1)
@@ -117,6 +131,11 @@ struct GemmParams {
   int ztaps;            // > 0: weight gradient, the z index is slice * ztaps + filter tap
   int os_on, os_uv, os_v;
   long long os_sn, os_su, os_sv;
+  // Strided data gradient in one launch: n_phases > 1 phases (at most 4) whose tiles are taken in turn - a CTA (pair)
+  // works through tile j of every phase before it moves to its next j - so the drain and stores of a short
+  // phase's tile run under the MMAs of the next, longer one.  Phase 0 is described by the fields above.
+  int n_phases;
+  GemmPhase phx[3];
 };
 
 enum GemmRole : int { ROLE_TMA = 1, ROLE_SPLIT = 2, ROLE_MMA = 3, ROLE_MMA_TMEM = 4, ROLE_DRAIN = 5, ROLE_SELFTEST = 7 };
@@ -221,6 +240,7 @@ struct TileWork {
   float* out;  // output base for this batch / slice
   int zc;      // batch / slice coordinate in the output tensor map
   int tap;     // weight gradient: filter tap this tile belongs to
+  int phase;   // strided data gradient in one launch: which phase the tile belongs to
   bool to_cbuf;  // this tile's output goes to the split-K partial buffers
 };
 
@@ -271,23 +291,50 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
   // ---- persistent tile loop: this CTA (pair) takes tiles first, first + step, ...
   // Tile ids run over (z, m-group, n, m-in-group); concurrently resident tiles are
   // consecutive ids, i.e. a GROUP x n patch of the output that shares operands in L2.
+  constexpr bool DG = Cfg::IM2COL_A && Cfg::B_MN;     // the data-gradient instantiation
+  const bool phased = DG && p.n_phases > 1;
   const int tiles_mn = p.tiles_m * p.tiles_n;
-  const long long total_tiles = static_cast<long long>(tiles_mn) * p.zcount;
+  const long long total_tiles = static_cast<long long>(tiles_mn) * p.zcount * (phased ? p.n_phases : 1);
   const long long tile_first = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const long long tile_step = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int kc = p.kc;
   // The i-th tile of this CTA (pair), or -1 past the end.  A unit is one tile, except in the softmax mode,
   // where it is the tiles_n tiles that hold whole rows: those are taken one after the other.
-  const int subs = Cfg::SOFTMAX ? p.unit_tiles : 1;
+  // In the phased mode a unit is tile j of every phase, taken one after the other.
+  const int subs = Cfg::SOFTMAX ? p.unit_tiles : (phased ? p.n_phases : 1);
   const long long total_units = total_tiles / subs;
+  const bool grouped = Cfg::SOFTMAX || phased;
   auto tile_at = [&](long long i) -> long long {
-    const long long u = tile_first + (Cfg::SOFTMAX ? i / subs : i) * tile_step;
+    const long long u = tile_first + (grouped ? i / subs : i) * tile_step;
     if (u >= total_units) return -1;
-    return Cfg::SOFTMAX ? u * subs + i % subs : u;
+    return grouped ? u * subs + i % subs : u;
+  };
+  // What a tile's phase changes (phase 0 and every launch without phases: the GemmParams fields themselves).
+  struct PhaseView {
+    const CUtensorMap* tmA; const CUtensorMap* tmB;
+    int M, OH, OW, FW, pw, ph, tap_base, tap_sy, tap_sx, os_uv, os_v;
+  };
+  auto phase_view = [&](int ph) -> PhaseView {
+    PhaseView v;
+    if (DG && ph > 0) {
+      const GemmPhase& x = p.phx[ph - 1];
+      v.tmA = &x.tmA; v.tmB = &x.tmB; v.M = x.M; v.OH = x.OH; v.OW = x.OW; v.FW = x.FW; v.pw = x.pw; v.ph = x.ph;
+      v.tap_base = x.tap_base; v.tap_sy = x.tap_sy; v.tap_sx = x.tap_sx; v.os_uv = x.os_uv; v.os_v = x.os_v;
+    } else {
+      v.tmA = &p.tmA; v.tmB = &p.tmB; v.M = p.M; v.OH = p.conv_OH; v.OW = p.conv_OW; v.FW = p.conv_FW;
+      v.pw = p.conv_pw; v.ph = p.conv_ph; v.tap_base = p.tap_base; v.tap_sy = p.tap_sy; v.tap_sx = p.tap_sx;
+      v.os_uv = p.os_uv; v.os_v = p.os_v;
+    }
+    return v;
   };
 
   auto decode = [&](long long t) -> TileWork {
     constexpr int GROUP = 8;
+    int phase = 0;
+    if (phased) {   // t = (tile inside the phase) * n_phases + phase
+      phase = static_cast<int>(t % p.n_phases);
+      t /= p.n_phases;
+    }
     const int z = static_cast<int>(t / tiles_mn);
     const int r = static_cast<int>(t - static_cast<long long>(z) * tiles_mn);
     const int per_group = GROUP * p.tiles_n;
@@ -300,6 +347,19 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
     w.col0 = tn * BN;
     w.bcol0 = w.col0 + static_cast<int>(rank) * Cfg::BN_CTA;
     w.tap = 0;
+    w.phase = phase;
+    if (phased) {
+      // phases differ in size: a tile past the end of its phase has no work (the test is on the pair's first
+      // row, so both CTAs of a pair agree) and stores nothing (every row is clipped)
+      const int m_ph = phase == 0 ? p.M : p.phx[phase - 1].M;
+      w.kb0 = 0;
+      w.nkb = (tm * CTAS * Cfg::BM < m_ph) ? (phase == 0 ? p.nkb_total : p.phx[phase - 1].nkb) : 0;
+      w.batch = 0;
+      w.out = phase == 0 ? p.C : p.phx[phase - 1].C;
+      w.to_cbuf = false;
+      w.zc = 0;
+      return w;
+    }
     if (p.ztaps > 0) {
       // weight gradient: z = slice * taps + tap; a tap owns p.N (= IC) columns of each output row
       const int slice = z / p.ztaps;
@@ -406,6 +466,7 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
       const uint64_t pol_b = p.l2_hints == 1 ? l2_policy_evict_first() : 0ull;
       for (long long i_tile = 0, t; alive && (t = tile_at(i_tile)) >= 0; ++i_tile) {
         const TileWork w = decode(t);
+        const PhaseView pv = phase_view(w.phase);
         for (int i = 0; i < w.nkb; ++i, ++it, s = (s + 1 == R) ? 0u : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
             if (leader) give_up(ROLE_TMA, s, i);
@@ -423,14 +484,14 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
           if (Cfg::IM2COL_A) {
             const int tap = (w.kb0 + i) / p.conv_icb;
             ic0 = ((w.kb0 + i) - tap * p.conv_icb) * Cfg::BK;
-            fh = tap / p.conv_FW;
-            fw = tap - fh * p.conv_FW;
+            fh = tap / pv.FW;
+            fw = tap - fh * pv.FW;
             k0 = tap * p.conv_IC + ic0;  // position in the filter's (fh, fw, ic) axis
-            const int ohw = p.conv_OH * p.conv_OW;
+            const int ohw = pv.OH * pv.OW;
             n = w.row0 / ohw;
             const int r = w.row0 - n * ohw;
-            oh = r / p.conv_OW;
-            ow = r - oh * p.conv_OW;
+            oh = r / pv.OW;
+            ow = r - oh * pv.OW;
           }
           if (Cfg::IM2COL_B) {
             // the k-block is a run of 32 output pixels starting at pixel k0 = (n, oh, ow); runs wrap over
@@ -502,8 +563,8 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
             if (Cfg::IM2COL_A && p.gather) {
               // the A tile is in place already
             } else if (Cfg::IM2COL_A) {
-              tma_load_im2col_4d(a_dst, &p.tmA, full, ic0, ow * p.conv_sw - p.conv_pw,
-                                 oh * p.conv_sh - p.conv_ph, n, static_cast<uint16_t>(fw),
+              tma_load_im2col_4d(a_dst, pv.tmA, full, ic0, ow * p.conv_sw - pv.pw,
+                                 oh * p.conv_sh - pv.ph, n, static_cast<uint16_t>(fw),
                                  static_cast<uint16_t>(fh), pol_a);
             } else if (Cfg::A_MN) {
 #pragma unroll
@@ -526,11 +587,11 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
             } else if (Cfg::B_MN && Cfg::IM2COL) {
               // data gradient: this k-block is 32 input channels of tap (fh, fw) of the im2col walk;
               // the filter matrix that multiplies it sits at a tap index given by the host
-              const int btap = p.tap_base + p.tap_sy * fh + p.tap_sx * fw;
+              const int btap = pv.tap_base + pv.tap_sy * fh + pv.tap_sx * fw;
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
-                if (p.bmap_order == 0) tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, btap, ic0, pol_b);
-                else                   tma_load_3d(b_dst + j * 4096, &p.tmB, full, w.bcol0 + 32 * j, ic0, btap, pol_b);
+                if (p.bmap_order == 0) tma_load_3d(b_dst + j * 4096, pv.tmB, full, w.bcol0 + 32 * j, btap, ic0, pol_b);
+                else                   tma_load_3d(b_dst + j * 4096, pv.tmB, full, w.bcol0 + 32 * j, ic0, btap, pol_b);
             } else if (Cfg::B_MN) {
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 32; ++j)
@@ -1082,17 +1143,18 @@ __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p) {
           // instruction - whole 128-byte segments instead of 32 scattered 16-byte stores.
           const uint32_t stg = stg0;
           const int row = w.row0 + q * 32 + lane;
+          const PhaseView pv = phase_view(w.phase);
           long long row_off = -1;   // rows >= M have no pixel
-          if (row < p.M) {
-            const int img = row / p.os_uv, r = row - img * p.os_uv;
-            const int u = r / p.os_v, v = r - u * p.os_v;
+          if (row < pv.M) {
+            const int img = row / pv.os_uv, r = row - img * pv.os_uv;
+            const int u = r / pv.os_v, v = r - u * pv.os_v;
             row_off = img * p.os_sn + u * p.os_su + v * p.os_sv;
           }
           const int sub = lane >> 3, chunk = lane & 7;
 #pragma unroll
           for (int g = 0; g < CW / 32; ++g) {
             const int c0 = w.col0 + h * CW + g * 32;
-            if (c0 < p.N && w.row0 + q * 32 < p.M) {   // warp-uniform
+            if (c0 < p.N && w.row0 + q * 32 < pv.M) {   // warp-uniform
 #pragma unroll
               for (int cq = 0; cq < 8; ++cq)
                 sts128(stg + lane * 128 + ((cq ^ (lane & 7)) * 16),

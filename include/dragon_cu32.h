@@ -447,6 +447,8 @@ CU32_API int cu32_batchMatMulT2_softmax(const int64_t* streams, int length, cons
  *   "ring_fixed"    1 = launches whose rings are the tile's default use the kernel path with compile-time ring geometry
  *                   (default); 0 = always the launch-parameter path (diagnostics: same bits)
  *   "ring_paired"   1 = with equally long rings each lo tile sits right behind its raw tile (default); 0 = two separate rings
+ *   "phase_fused"   1 = a strided data gradient with 2 to 4 phases runs them in one launch, a CTA taking tile j of every
+ *                   phase in turn (default); 0 = one launch per phase (same bits)
  *   "rep_lazy"      1 = the replicated entry points store a finished block to C and carry it to the copies while the
  *                   next tile is multiplied (default); 0 = every store is repeated to every copy at once
  *   "sm_reserve" SMs the contraction kernel's persistent grid leaves free, for kernels a host runs beside it on

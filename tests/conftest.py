@@ -60,6 +60,7 @@ def _default_tuning(request):
         p.cu32.tune("phase_overlap", 1)
         p.cu32.tune("rep_lazy", 1)
         p.cu32.tune("ring_fixed", 1)
+        p.cu32.tune("phase_fused", 1)
         p.cu32.tune("ring_paired", 1)
 
 

@@ -462,6 +462,38 @@ def test_strided_deltax(pkg, O, cuda, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tile", [-1, 0, 3])
+def test_strided_phases_in_one_launch_give_the_bits_of_one_launch_per_phase(pkg, O, cuda, tile):
+    """With 2 to 4 phases the kernel takes tile j of every phase in turn inside one launch
+    (cu32_tune("phase_fused", 1), the default); phases of unequal size leave tiles without work at the end of the
+    smaller ones.  Same bits as one launch per phase, with and without the fused bias row, and FP64 parity."""
+    import gpu_util as G
+    rng = np.random.default_rng(29)
+    for (N, IH, IW, IC, OC, FH, FW, sh, sw, ph, pw) in [
+        (1, 33, 33, 128, 64, 3, 3, 2, 2, 1, 1),      # 17x17 = 289 pixels (two 256-row tiles) against 16x16 (one)
+        (3, 57, 57, 64, 96, 3, 3, 2, 2, 1, 1),       # several tiles per CTA pair, phases of 841 / 812 / 784 pixels per image
+        (2, 21, 40, 36, 40, 5, 3, 2, 1, 2, 1),       # two phases only, 5 and 3... taps apart
+        (2, 19, 23, 32, 32, 2, 3, 2, 2, 0, 1),       # a phase with a single tap row
+    ]:
+        OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        W = (rng.standard_normal((OC, FH, FW, IC)) * 0.1).astype(np.float32)
+        want = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)
+        res = {}
+        for fused in (1, 0):
+            pkg.cu32.tune("phase_fused", fused)
+            pkg.cu32.tune("tile", tile)
+            res[fused] = [_run_strided(pkg, nm, dY, W, IH, IW, sh, sw, ph, pw) for nm in ("crossAdd", "kernelSplit")]
+        pkg.cu32.tune("phase_fused", 1)
+        pkg.cu32.tune("tile", -1)
+        for a, b in zip(res[1], res[0]):
+            assert np.array_equal(a, b), (tile, N, IH, IW, sh, sw)
+        assert np.array_equal(res[1][0], res[1][1])
+        rep = O.report(res[1][0], want)
+        assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (tile, rep)
+
+
+@pytest.mark.gpu
 def test_strided_entry_points_give_the_same_bits(pkg, O, cuda):
     rng = np.random.default_rng(21)
     N, IH, IW, IC, OC, FH, FW, ph, pw = 3, 12, 14, 24, 40, 3, 3, 1, 1
