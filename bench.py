@@ -387,7 +387,8 @@ class Workload:
             self.cw = torch.zeros(sd * sd * OC * CF * CF * IC, device="cuda")
             ddY, dW, dDX = self.dev_in[0], self.dev_in[1], self.out
             dx = pkg.cu32.Cuda_dconv3D_deltaX
-            self.kernels_per_step = 1 + sd * sd
+            # the filter rearrangement plus the gradient: its sd*sd phases run in one launch when there are at most four
+            self.kernels_per_step = 1 + (1 if sd * sd <= 4 and pkg.cu32.get_tune("phase_fused") else sd * sd)
 
             def launch():
                 s = st()
