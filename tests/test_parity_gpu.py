@@ -362,6 +362,44 @@ def test_conv_gemmr(pkg, O, cuda, case):
         assert O.frob_rel(Y, Yref) <= 2e-6
 
 
+# Feature-map and filter geometries the reference's own convolution test lists
+# (test/cuda/conv3D/Cuda_conv3D_test.java:157-171, :183-189), at a batch the FP64 oracle finishes in a second or two;
+# inputs as in that test: uniform [0, 1) (Vector.random_float_vector).
+REF_TEST_CONV = [
+    # N, IH, IW, IC, OC, FH, FW, ph, pw
+    (1, 64, 64, 64, 64, 7, 7, 3, 3),
+    (1, 64, 64, 64, 64, 9, 9, 4, 4),
+    (1, 32, 32, 64, 64, 8, 8, 4, 4),
+    (2, 32, 32, 64, 64, 1, 7, 0, 3),
+    (2, 16, 16, 256, 256, 5, 5, 2, 2),
+    (2, 16, 16, 128, 128, 3, 3, 1, 1),
+    (4, 8, 8, 128, 256, 3, 3, 1, 1),
+    (4, 8, 8, 256, 256, 5, 5, 2, 2),
+    (1, 128, 128, 4, 64, 3, 3, 1, 1),        # the 3-channel input of that list, padded to 4 channels by the engine
+    (2, 4, 4, 1024, 1024, 3, 3, 1, 1),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", REF_TEST_CONV)
+def test_conv_geometries_of_the_reference_test(pkg, O, cuda, case):
+    N, IH, IW, IC, OC, FH, FW, ph, pw = case
+    rng = np.random.default_rng(IH * 131 + FH)
+    X = rng.random((N, IH, IW, IC), dtype=np.float32)
+    W = rng.random((OC, FH, FW, IC), dtype=np.float32)
+    if IC == 4:
+        X[..., 3] = 0.0
+        W[..., 3] = 0.0
+    OH, OW = IH + 2 * ph - FH + 1, IW + 2 * pw - FW + 1
+    Y64 = O.f64.conv3D(X, W, OH, OW, 1, 1, ph, pw)
+    Y = G.conv(pkg, "conv3D_GemmR", X, W, 1, 1, ph, pw)
+    assert_accurate(O, Y, Y64, f"conv {case}")
+    # the reference test's own gate: its CPU loop's result within 1e-3 relative for >= 99 % of the elements
+    # (Cuda_conv3D/test.cuh:38-57, :913) - checked here against FP64, which that loop approximates
+    rel = np.abs(Y - Y64) / np.maximum(np.abs(Y64), 1e-30)
+    assert np.mean(rel <= 1e-3) >= 0.99
+
+
 def test_conv_entry_point_aliases(pkg, O, cuda):
     rng = np.random.default_rng(18)
     X = rng.standard_normal((4, 12, 12, 16)).astype(np.float32)
