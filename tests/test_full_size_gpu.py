@@ -212,3 +212,53 @@ def test_remainder_sweep_every_multiple_of_four(pkg, O, cuda, form):
         assert float(worst.item()) <= FROB_TOL, (form, K, float(worst.item()))
         out.host((DMAX * DMAX,))   # canaries
         G.check_status(pkg)
+
+
+@pytest.mark.parametrize("form", ["AB", "T1", "T2"])
+def test_batched_remainder_sweep_of_the_reference_test(pkg, O, cuda, form):
+    """The reference's batched test sweeps K = 7..9, N = 1..82, M = 1..96 at batch 5 x 3
+    (test/cuda/matMul/Cuda_batchMatMul_test.java:120-123) through the engine, which pads every tensor's last
+    dimension to a multiple of 4 with zeros and leaves the others as they are.  Here the same sweep as the natives
+    see it: every row count, the padded extents as pitches (AK, AN, CM), the true ones as logical sizes (BK, CN, BM);
+    each product verified on the device against an FP64 product, pad columns of C asserted zero."""
+    bm = pkg.cu32.Cuda_batchMatMul
+    s = [G.stream()]
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    Batch = 15
+    pad4 = lambda x: (x + 3) // 4 * 4
+    out = G.Out(Batch * 84 * 96)
+    worst = torch.zeros((), device="cuda", dtype=torch.float64)
+    bad = torch.zeros((), device="cuda", dtype=torch.int64)
+    for K in (7, 8, 9):
+        Kp = pad4(K)
+        for N in range(1, 83, 3 if form != "AB" else 1):
+            Np = pad4(N)
+            for M in range(1, 97, 5):
+                Mp = pad4(M)
+                if form == "AB":      # A[b][N][Kp] (zeros beyond K), B[b][K][Mp] (zeros beyond M)
+                    A = torch.rand((Batch, N, Kp), device="cuda", generator=g); A[:, :, K:] = 0
+                    B = torch.rand((Batch, K, Mp), device="cuda", generator=g); B[:, :, M:] = 0
+                    C = out.view[:Batch * N * Mp].view(Batch, N, Mp); C.fill_(float("nan"))
+                    bm.batchMatMul(s, 1, A.data_ptr(), B.data_ptr(), C.data_ptr(), Batch, N, Mp, K, Kp)
+                    ref = A.double() @ torch.nn.functional.pad(B.double(), (0, 0, 0, Kp - K))
+                elif form == "T1":    # A[b][K][Np] (zeros beyond N), B[b][K][Mp]; C[b][N][Mp]
+                    A = torch.rand((Batch, K, Np), device="cuda", generator=g); A[:, :, N:] = 0
+                    B = torch.rand((Batch, K, Mp), device="cuda", generator=g); B[:, :, M:] = 0
+                    C = out.view[:Batch * N * Mp].view(Batch, N, Mp); C.fill_(float("nan"))
+                    bm.batchMatMulT1(s, 1, A.data_ptr(), B.data_ptr(), C.data_ptr(), Batch, N, Np, Mp, K)
+                    ref = A.double().transpose(1, 2)[:, :N, :] @ B.double()
+                else:                 # A[b][N][Kp], B[b][M][Kp] (zeros beyond K); C[b][N][Mp], columns M.. zero
+                    A = torch.rand((Batch, N, Kp), device="cuda", generator=g); A[:, :, K:] = 0
+                    B = torch.rand((Batch, M, Kp), device="cuda", generator=g); B[:, :, K:] = 0
+                    C = out.view[:Batch * N * Mp].view(Batch, N, Mp); C.fill_(float("nan"))
+                    bm.batchMatMulT2(s, 1, A.data_ptr(), B.data_ptr(), C.data_ptr(), Batch, N, Mp, M, Kp)
+                    ref = torch.nn.functional.pad(A.double() @ B.double().transpose(1, 2), (0, Mp - M))
+                    bad += (C[:, :, M:] != 0).sum()
+                err = (C.double() - ref).norm() / ref.norm()
+                worst = torch.maximum(worst, torch.nan_to_num(err, nan=1.0))
+                bad += (~torch.isfinite(C)).sum()
+    assert int(bad.item()) == 0, form
+    assert float(worst.item()) <= FROB_TOL, (form, float(worst.item()))
+    out.host((Batch * 84 * 96,))   # canaries
+    G.check_status(pkg)
+
