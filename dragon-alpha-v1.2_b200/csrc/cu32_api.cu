@@ -541,7 +541,10 @@ static int deconv_s1_any(const int64_t* streams, int length, const float* dDY, i
   if (!dDY || !dW || !dDX) return CU32_E_NULL;
   if (FH <= 0 || FW <= 0 || ph < 0 || pw < 0 || IC <= 0 || OC <= 0) return CU32_E_DIM;
   if ((IC & 3) || (OC & 3)) return CU32_E_ALIGN;
-  if (IH != OH - 1 + FH - 2 * ph || IW != OW - 1 + FW - 2 * pw) return CU32_E_DIM;
+  // Any pair of extents is served, as by the reference's kernels (its own test pairs IH = OH = 64 with an 8x8
+  // filter and padding 4): deltaY rows the sum would need outside [0, OH) count as zeros, rows it never needs are
+  // never read.
+  if (IH <= 0 || IW <= 0 || OH <= 0 || OW <= 0) return CU32_E_DIM;
   // padding beyond the filter reach makes the equivalent forward padding negative (the outermost pixels of deltaY
   // are never used); conv_any takes it as it is
   return conv_any(true, streams, length, dDY, OH, OW, dW, FH, FW, dDX, IH, IW, N, /*in*/ OC, /*out*/ IC, 1, 1,
@@ -619,8 +622,7 @@ static int deconv_strided_any(const int64_t* streams, int length, const float* d
       sw <= 0 || ph < 0 || pw < 0)
     return CU32_E_DIM;
   if ((IC & 3) || (OC & 3) || !aligned16(dDY) || !aligned16(filt) || !aligned16(dDX)) return CU32_E_ALIGN;
-  if (IH + 2 * ph < FH || IW + 2 * pw < FW || OH != (IH + 2 * ph - FH) / sh + 1 || OW != (IW + 2 * pw - FW) / sw + 1)
-    return CU32_E_DIM;
+  // extents are taken as given (see deconv_s1_any): what lies outside deltaY counts as zeros
   if (static_cast<long long>(N) * IH * IW * IC >= (1LL << 31) || static_cast<long long>(N) * OH * OW * OC >= (1LL << 31))
     return CU32_E_DIM;
   if (static_cast<long long>(sh) * sw > 4096) return CU32_E_DIM;   // one launch per phase

@@ -244,7 +244,9 @@ CU32_API int cu32_conv3D_Im2col_WinogradR_s16_texture_SGM(int useTexture, const 
  * engine-cuda-base/Cuda_dconv3D_deltaX/Cuda_dconv3D_deltaX/):
  *   deltaX[n,ih,iw,ic] = sum_{fh,fw,oc} deltaY[n, ih+ph-fh, iw+pw-fw, oc] * W[oc,fh,fw,ic], zero outside deltaY;
  *   deltaY[N,OH,OW,OC], W[OC,FH,FW,IC] (the forward filter, unchanged), deltaX[N,IH,IW,IC],
- *   IH = OH - 1 + FH - 2*ph (and likewise for the width); IC % 4 == 0, OC % 4 == 0.
+ *   IC % 4 == 0, OC % 4 == 0.  The forward convolution gives IH = OH - 1 + FH - 2*ph (likewise the width), but
+ *   any pair of extents is served, as by the reference (its own test pairs IH = OH = 64 with an 8x8 filter,
+ *   padding 4: test/cuda/conv3D/Cuda_conv3D_dX_test.java:178,216): the sum simply runs over the rows that exist.
  * It runs as a forward implicit GEMM over deltaY with padding (FH-1-ph, FW-1-pw) and the filter taps
  * reversed, W being read where it lies.  (Strides > 1: next section.)
  *   cu32_dconv3D_deltaX_s1[_texture][_SGM]   replace JNI dconv3D_deltaX_s1 (A.cu:21-42), _s1_SGM (:45-94),
@@ -352,7 +354,8 @@ CU32_API int cu32_dconv3D_deltaW_Im2col_WinogradV2_SHW_s16_texture(const int64_t
 
 /* ------------------------------------------------------------------ Cuda_dconv3D_deltaX, any stride
  * deltaX[n,ih,iw,ic] = sum over (oh,ow,fh,fw,oc) with oh*sh - ph + fh == ih and ow*sw - pw + fw == iw of
- * deltaY[n,oh,ow,oc] * W[oc,fh,fw,ic];  OH = (IH + 2*ph - FH) / sh + 1 (likewise OW).  Computed as sh*sw stride-1
+ * deltaY[n,oh,ow,oc] * W[oc,fh,fw,ic];  the forward convolution gives OH = (IH + 2*ph - FH) / sh + 1 (likewise OW),
+ * any other pair of extents is served as well (the sum runs over the rows that exist).  Computed as sh*sw stride-1
  * sub-problems, one per residue of (ih + ph, iw + pw) modulo the stride, each a launch of the contraction kernel
  * whose output rows are the strided pixels of that residue class.
  *   cu32_ks_remode / cu32_ks_remodev2   replace JNI ks_remode (A.cu:280-291) and ks_remodev2 (:294-306): the filter

@@ -81,7 +81,7 @@ def test_deltax_argument_errors_without_gpu(pkg):
     ok = 0x10000
     f = lib.cu32_dconv3D_deltaX_s1
     #           dY  OH OW  W  FH FW  dX  IH IW  N  IC OC ph pw
-    assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 9, 8, 2, 8, 8, 1, 1) == -2      # IH inconsistent with OH, FH, ph
+    assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 0, 8, 2, 8, 8, 1, 1) == -2      # no rows
     assert f(s, 1, None, 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 1, 1) == -1
     assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 6, 8, 1, 1) == -4      # IC % 4
     assert f(s, 1, P(ok), 8, 8, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 6, 1, 1) == -4      # OC % 4
@@ -379,7 +379,7 @@ def test_strided_argument_errors_without_gpu(pkg):
     ok = 0x10000
     f = lib.cu32_dconv3D_deltaX_crossAdd
     #           dY  OH OW  W  FH FW  dX  IH IW  N  IC OC sh sw ph pw
-    assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 9, 8, 2, 8, 8, 2, 2, 1, 1) == -2   # OH inconsistent with IH
+    assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 0, 8, 2, 8, 8, 2, 2, 1, 1) == -2   # no rows
     assert f(s, 1, None, 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 2, 2, 1, 1) == -1
     assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 6, 8, 2, 2, 1, 1) == -4   # IC % 4
     assert f(s, 1, P(ok), 4, 4, P(ok), 3, 3, P(ok), 8, 8, 2, 8, 8, 0, 2, 1, 1) == -2   # stride 0
@@ -491,6 +491,35 @@ def test_strided_phases_in_one_launch_give_the_bits_of_one_launch_per_phase(pkg,
         assert np.array_equal(res[1][0], res[1][1])
         rep = O.report(res[1][0], want)
         assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (tile, rep)
+
+
+@pytest.mark.gpu
+def test_extents_that_no_forward_convolution_gives(pkg, O, cuda):
+    """The reference's data-gradient kernels take (IH, IW) and (OH, OW) as given; its own test pairs IH = OH = 64
+    with an 8x8 filter and padding 4 (Cuda_conv3D_dX_test.java:178, :216), which no forward convolution produces.
+    Rows of deltaY the sum would need outside [0, OH) count as zeros, rows it never reaches are never read:
+    FP64 parity and the reference's check loop, stride 1 and strided entry points."""
+    rng = np.random.default_rng(41)
+    for (N, IH, IW, OH, OW, IC, OC, FH, FW, sh, sw, ph, pw) in [
+        (2, 16, 16, 16, 16, 16, 24, 8, 8, 1, 1, 4, 4),     # the reference test's pairing, scaled down
+        (2, 12, 9, 9, 9, 8, 8, 3, 3, 1, 1, 1, 1),          # deltaX taller than the forward input
+        (2, 7, 9, 9, 9, 8, 8, 3, 3, 1, 1, 1, 1),           # and shorter
+        (2, 19, 17, 8, 8, 16, 8, 3, 3, 2, 2, 1, 1),        # strided: forward gives OH = 10 and 9
+        (1, 12, 12, 8, 7, 8, 12, 5, 5, 2, 2, 2, 2),        # strided: forward gives 6
+        (2, 9, 10, 5, 4, 8, 8, 3, 2, 3, 2, 0, 1),
+    ]:
+        dY = rng.random((N, OH, OW, OC), dtype=np.float32)
+        W = rng.random((OC, FH, FW, IC), dtype=np.float32)
+        want = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw)
+        loop = O.ref_loops.deconv3D_deltaX_img2col(dY, W, IH, IW, sh, sw, ph, pw)
+        got = [_run_strided(pkg, nm, dY, W, IH, IW, sh, sw, ph, pw) for nm in ("crossAdd", "kernelSplit")]
+        if sh == 1 and sw == 1:
+            got.append(_run(pkg, "dconv3D_deltaX_s1", dY, W, IH, IW, ph, pw))
+        for g in got:
+            rep = O.report(g, want)
+            assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, ((N, IH, IW, OH, OW, FH, FW, sh, sw, ph, pw), rep)
+            assert O.frob_rel(g, loop) <= 2e-6
+            assert np.array_equal(g, got[0])
 
 
 @pytest.mark.gpu

@@ -178,8 +178,8 @@ def test_jni_deltax_on_gpu(pkg, O, cuda):
     assert w(jni.env, None, 1, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out2.ptr, IH, IW, N, IC, OC,
              p, p) == 1
     assert np.array_equal(out2.host((N, IH, IW, IC)), base)
-    # inconsistent geometry becomes a CudaException(-2), nothing is launched
-    f(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out.ptr, IH + 1, IW, N, IC, OC, p, p)
+    # an impossible geometry becomes a CudaException(-2), nothing is launched
+    f(jni.env, None, ARRAY_HANDLE, 1, ddY.data_ptr(), IH, IW, dW.data_ptr(), F, F, out.ptr, 0, IW, N, IC, OC, p, p)
     assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
     G.check_status(pkg)
 
