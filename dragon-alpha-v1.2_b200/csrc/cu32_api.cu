@@ -788,8 +788,7 @@ static int deconvW_any(const int64_t* streams, int length, int GridZ, const floa
     return CU32_E_DIM;
   if ((IC & 3) || (OC & 3) || !aligned16(dX) || !aligned16(dDY) || !aligned16(dDW) || (dBuf && !aligned16(dBuf)))
     return CU32_E_ALIGN;
-  if (IH + 2 * ph < FH || IW + 2 * pw < FW || OH != (IH + 2 * ph - FH) / sh + 1 || OW != (IW + 2 * pw - FW) / sw + 1)
-    return CU32_E_DIM;
+  // extents are taken as given, as by the reference (see deconv_s1_any): input pixels outside X count as zeros
   const long long GK = static_cast<long long>(N) * OH * OW;
   const long long taps = static_cast<long long>(FH) * FW;
   if (GK >= (1LL << 31) - 64 || static_cast<long long>(N) * IH * IW * IC >= (1LL << 31) || GK * OC >= (1LL << 40) ||

@@ -62,7 +62,7 @@ def test_deltaw_argument_errors_without_gpu(pkg):
     #              GZ   X  IH IW  dY  OH OW  dW   buf  FH FW N  IC OC sh sw ph pw
     assert f(s, 1, 2, P(ok), 8, 8, P(ok), 8, 8, P(ok), None, 3, 3, 2, 8, 8, 1, 1, 1, 1) == -1     # GridZ > 1 needs the buffer
     assert f(s, 1, 0, P(ok), 8, 8, P(ok), 8, 8, P(ok), P(ok), 3, 3, 2, 8, 8, 1, 1, 1, 1) == -8
-    assert f(s, 1, 1, P(ok), 8, 8, P(ok), 7, 8, P(ok), P(ok), 3, 3, 2, 8, 8, 1, 1, 1, 1) == -2    # OH inconsistent
+    assert f(s, 1, 1, P(ok), 8, 8, P(ok), 0, 8, P(ok), P(ok), 3, 3, 2, 8, 8, 1, 1, 1, 1) == -2    # no rows
     assert f(s, 1, 1, P(ok), 8, 8, P(ok), 8, 8, P(ok), P(ok), 3, 3, 2, 6, 8, 1, 1, 1, 1) == -4    # IC % 4
     assert f(s, 0, 1, P(ok), 8, 8, P(ok), 8, 8, P(ok), P(ok), 3, 3, 2, 8, 8, 1, 1, 1, 1) == -3
     assert lib.cu32_dconv3D_deltaW(s, 1, None, 8, 8, P(ok), 8, 8, P(ok), 3, 3, 2, 8, 8, 1, 1, 1, 1) == -1
@@ -138,6 +138,27 @@ def test_deltaw(pkg, O, cuda, case):
         loop = O.ref_loops.deconv3D_deltaW_naive(X, dY, FH, FW, sh, sw, ph, pw)
         assert O.frob_rel(got, loop) <= 1e-6
         assert O.same_percent(np.abs(got), np.abs(loop), 1e-3) >= 0.999     # the gate of the reference's own Java test
+
+
+@pytest.mark.gpu
+def test_deltaw_extents_that_no_forward_convolution_gives(pkg, O, cuda):
+    """(IH, IW) and (OH, OW) are taken as given, as by the reference's natives (its tests pass both): input pixels
+    outside X count as zeros.  FP64 parity, plain and split-K."""
+    rng = np.random.default_rng(43)
+    for (N, IH, IW, OH, OW, IC, OC, FH, FW, sh, sw, ph, pw) in [
+        (2, 16, 16, 16, 16, 16, 24, 8, 8, 1, 1, 4, 4),     # the data-gradient test's pairing of the reference
+        (2, 12, 9, 9, 9, 8, 8, 3, 3, 1, 1, 1, 1),
+        (2, 7, 9, 9, 9, 8, 8, 3, 3, 1, 1, 1, 1),
+        (2, 19, 17, 8, 8, 16, 8, 3, 3, 2, 2, 1, 1),
+        (1, 12, 12, 8, 7, 8, 12, 5, 5, 2, 2, 2, 2),
+    ]:
+        X = rng.standard_normal((N, IH, IW, IC)).astype(np.float32)
+        dY = rng.standard_normal((N, OH, OW, OC)).astype(np.float32)
+        want = O.f64.deconv3D_deltaW(X, dY, FH, FW, sh, sw, ph, pw)
+        for entry, GZ in (("dconv3D_deltaW", 1), ("dconv3D_deltaW_GemmSK", 3)):
+            got = _run(pkg, entry, X, dY, FH, FW, sh, sw, ph, pw, GZ=GZ)
+            rep = O.report(got, want)
+            assert np.isfinite(got).all() and rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, ((IH, OH, FH, sh, ph), entry, rep)
 
 
 @pytest.mark.gpu

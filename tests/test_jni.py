@@ -271,8 +271,8 @@ def test_jni_deltaw_on_gpu(pkg, O, cuda):
              buf.data_ptr(), F, F, N, IC, OC, p, p, 6) == 1
     sm(jni.env, None, G.stream(), buf.data_ptr(), out2.ptr, GZ - 1, size)
     assert np.array_equal(out2.host((OC, F, F, IC)), base)
-    # inconsistent geometry becomes a CudaException(-2)
-    f(jni.env, None, ARRAY_HANDLE, 1, GZ, dX_.data_ptr(), IH, IW, ddY.data_ptr(), IH + 1, IW, out.ptr, buf.data_ptr(), F, F,
+    # an impossible geometry becomes a CudaException(-2)
+    f(jni.env, None, ARRAY_HANDLE, 1, GZ, dX_.data_ptr(), IH, IW, ddY.data_ptr(), 0, IW, out.ptr, buf.data_ptr(), F, F,
       N, IC, OC, 1, 1, p, p)
     assert ("NewObjectA", 0x1111, 0x2222, -2) in jni.log and jni.thrown == 0x3333
     G.check_status(pkg)
