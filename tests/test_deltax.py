@@ -699,3 +699,43 @@ def test_deltax_biased_is_the_unbiased_native_followed_by_the_bias_kernel(pkg, O
     assert np.array_equal(fused, want)
     if width < IC:
         assert not fused[..., width:].any()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("geom", [(3, 3, 1, 1, 1, 1), (4, 4, 2, 2, 1, 1), (5, 5, 2, 2, 2, 2)])
+def test_transposed_convolution_channel_sweep_of_the_reference_test(pkg, O, cuda, geom):
+    """The reference's transposed-convolution test sweeps the output channels 1..128 on a 4 x 16 x 16 x 16 input for
+    3x3 stride 1, 4x4 stride 2 and 5x5 stride 2 (test/cuda/conv3D/Cuda_deconv3D_biased_test.java:83-114).  The engine
+    pads the channel count to a multiple of 4 and passes the true count as the bias width; here every padded count
+    4..128 with a true width 0 to 3 below it, FP64 parity of the fused native, pad channels zero.  (The transposed convolution's input is the data gradient's deltaY, its output deltaX.)"""
+    import gpu_util as G
+    FH, FW, sh, sw, ph, pw = geom
+    N, OH, OW, OC = 4, 16, 16, 16                      # the transposed convolution's input
+    IH, IW = (OH - 1) * sh + FH - 2 * ph, (OW - 1) * sw + FW - 2 * pw
+    rng = np.random.default_rng(71)
+    dY = rng.random((N, OH, OW, OC), dtype=np.float32)
+    dx = pkg.cu32.Cuda_dconv3D_deltaX
+    ddY = G.dev(dY)
+    for IC in range(4, 129, 4):                        # the transposed convolution's output channels, padded
+        width = IC - (IC // 4) % 4
+        W = rng.random((OC, FH, FW, IC), dtype=np.float32)
+        W[..., width:] = 0.0
+        bias = rng.random(IC, dtype=np.float32)
+        want = O.f64.deconv3D_deltaX(dY, W, IH, IW, sh, sw, ph, pw) + bias.astype(np.float64)
+        want[..., width:] = 0.0
+        out = G.Out(N * IH * IW * IC)
+        dB = G.dev(bias)
+        if sh == 1:
+            dW = G.dev(W)
+            dx.dconv3D_deltaX_s1_biased([G.stream()], 1, ddY.data_ptr(), OH, OW, dW.data_ptr(), FH, FW, out.ptr, IH, IW, N,
+                                        IC, OC, ph, pw, dB.data_ptr(), width)
+        else:
+            dCW = _remode_dev(pkg, W, sh, sw)
+            dx.dconv3D_deltaX_ksImsR_biased([G.stream()], 1, ddY.data_ptr(), OH, OW, dCW.data_ptr(), FH, FW, out.ptr, IH, IW,
+                                            N, IC, OC, sh, sw, ph, pw, dB.data_ptr(), width)
+        got = out.host((N, IH, IW, IC))
+        G.check_status(pkg)
+        assert not got[..., width:].any(), (geom, IC, width)
+        rep = O.report(got, want)
+        assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (geom, IC, rep)
+
