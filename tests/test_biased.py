@@ -158,6 +158,41 @@ def test_conv_biased_equals_two_step_sequence(pkg, O, cuda, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("geom", [(3, 3, 1, 1, 1, 1), (4, 4, 2, 2, 1, 1), (5, 5, 2, 2, 2, 2)])
+def test_conv_biased_channel_sweep_of_the_reference_test(pkg, O, cuda, geom):
+    """The reference's biased-convolution test sweeps the output channels 1..128 on a 4 x 16 x 16 x 16 input for
+    3x3 stride 1, 4x4 stride 2 and 5x5 stride 2 (test/cuda/conv3D/Cuda_conv3D_biased_test.java:68-99); the engine pads
+    the count to a multiple of 4 and passes the true count as the bias width.  Every padded count 4..128 with a true
+    width 0 to 3 below it: FP64 parity of the fused native, pad channels zero."""
+    import gpu_util as G
+    torch = cuda
+    FH, FW, sh, sw, ph, pw = geom
+    N, IH, IW, IC = 4, 16, 16, 16
+    OH, OW = (IH + 2 * ph - FH) // sh + 1, (IW + 2 * pw - FW) // sw + 1
+    rng = np.random.default_rng(73)
+    X = rng.random((N, IH, IW, IC), dtype=np.float32)
+    dX = G.dev(X)
+    for OC in range(4, 129, 4):
+        width = OC - (OC // 4) % 4
+        W = rng.random((OC, FH, FW, IC), dtype=np.float32)
+        W[width:] = 0.0
+        bias = rng.random(OC, dtype=np.float32)
+        want = O.f64.conv3D(X, W, OH, OW, sh, sw, ph, pw) + bias.astype(np.float64)
+        want[..., width:] = 0.0
+        dW, dbias = G.dev(W), G.dev(bias)
+        dCW = torch.empty(W.size, device="cuda")
+        pkg.cu32.Cuda_conv3D.kernel_remode(G.stream(), dW.data_ptr(), dCW.data_ptr(), FH, FW, OC, IC)
+        out = G.Out(N * OH * OW * OC)
+        pkg.cu32.Cuda_conv3D.conv3D_GemmR_biased([G.stream()], 1, dX.data_ptr(), IH, IW, dW.data_ptr(), dCW.data_ptr(), FH, FW,
+                                                 out.ptr, OH, OW, N, IC, OC, sh, sw, ph, pw, dbias.data_ptr(), width)
+        got = out.host((N, OH, OW, OC))
+        G.check_status(pkg)
+        assert not got[..., width:].any(), (geom, OC, width)
+        rep = O.report(got, want)
+        assert rep["frob"] <= 1e-6 and rep["elem"] <= 1e-4, (geom, OC, rep)
+
+
+@pytest.mark.gpu
 def test_bias_kernel_restatement_against_reference_kernel(pkg, O, cuda):
     """Pins the restated linear_dual2D_row: the reference's own kernel, compiled from the reference tree for
     sm_100a (oracle/_ref/libref_function.so), gives the same bits on the same inputs."""
