@@ -158,6 +158,42 @@ def test_conv_biased_equals_two_step_sequence(pkg, O, cuda, case):
 
 
 @pytest.mark.gpu
+def test_fullconnect_sweep_of_the_reference_test(pkg, O, cuda):
+    """The reference's fully-connected test compares fullconnect(X, W) followed by add_row with fullconnect(X, W, B)
+    for every X of 1..128 x 1..128 (test/cuda/Cuda_fullconect_test.java:47-49), demanding identical values.  Here the
+    same comparison at the native level for every padded extent 4..128: the fused native against the plain native
+    followed by one FP32 add of the bias on the device, bit for bit, pad columns zero."""
+    import gpu_util as G
+    torch = cuda
+    mm = pkg.cu32.Cuda_matMul
+    s = [G.stream()]
+    g = torch.Generator(device="cuda").manual_seed(75)
+    X = torch.randn(128 * 128, device="cuda", generator=g)
+    Wt = torch.randn(128 * 128, device="cuda", generator=g)
+    Bv = torch.randn(128, device="cuda", generator=g)
+    plain = torch.empty(128 * 128, device="cuda")
+    fused = G.Out(128 * 128)
+    bad = torch.zeros((), device="cuda", dtype=torch.int64)
+    for N in range(4, 129, 4):
+        for M in range(4, 129, 4):            # K = M, as in the reference test (W is IW x IW)
+            width = M - (N // 4) % 4          # true widths 0 to 3 below the padded one
+            A = X[:N * M].view(N, M)
+            W = Wt[:M * M].view(M, M).clone()
+            W[:, width:] = 0                  # the engine keeps pad columns of the weights at zero
+            C = plain[:N * M].view(N, M)
+            F = fused.view[:N * M].view(N, M)
+            F.fill_(float("nan"))
+            mm.matMul(s, 1, A.data_ptr(), W.data_ptr(), C.data_ptr(), N, M, M)
+            mm.matMul_biased(s, 1, A.data_ptr(), W.data_ptr(), F.data_ptr(), Bv.data_ptr(), N, M, M, width)
+            want = C + Bv[:M]
+            want[:, width:] = 0
+            bad += (F != want).sum()
+    assert int(bad.item()) == 0
+    fused.host((128 * 128,))   # canaries
+    G.check_status(pkg)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("geom", [(3, 3, 1, 1, 1, 1), (4, 4, 2, 2, 1, 1), (5, 5, 2, 2, 2, 2)])
 def test_conv_biased_channel_sweep_of_the_reference_test(pkg, O, cuda, geom):
     """The reference's biased-convolution test sweeps the output channels 1..128 on a 4 x 16 x 16 x 16 input for
