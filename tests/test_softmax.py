@@ -101,6 +101,42 @@ def test_fused_scores_softmax(pkg, O, cuda, case):
 
 
 @pytest.mark.gpu
+def test_fused_scores_width_sweep_of_the_reference_test(pkg, O, cuda):
+    """The reference's softmax test sweeps heights 2..20 x widths 2..256, heights 100..105 x widths 40..64 and
+    1024 x 1024 (test/cuda/function/Cuda_function_softmax_test.java:60-66), inputs in [0, 0.7).  Here every width of
+    that sweep (the engine's pitch = the width rounded up to 4) for a few of its heights, as the row length of the
+    fused scores; verified on the device against the FP64 softmax of the FP64 scores: rows sum to 1, pad columns are
+    zero, relative Frobenius error <= 1e-6."""
+    import gpu_util as G
+    torch = cuda
+    g = torch.Generator(device="cuda").manual_seed(77)
+    Batch, K = 3, 64
+    alpha = 1.0 / 8.0
+    worst = torch.zeros((), device="cuda", dtype=torch.float64)
+    bad = torch.zeros((), device="cuda", dtype=torch.int64)
+    out = G.Out(Batch * 105 * 1024)
+    cases = [(h, w) for h in (2, 7, 20) for w in range(2, 257)] + [(h, w) for h in (100, 105) for w in range(40, 65)]
+    cases.append((64, 1024))      # rows longer than the two TMEM buffers: the two-step path
+    for (h, w) in cases:
+        CM = (w + 3) // 4 * 4
+        Q = torch.rand((Batch, h, K), device="cuda", generator=g) * 0.7
+        Kt = torch.rand((Batch, w, K), device="cuda", generator=g) * 0.7
+        P = out.view[:Batch * h * CM].view(Batch, h, CM)
+        P.fill_(float("nan"))
+        pkg.cu32.Cuda_batchMatMul.batchMatMulT2_softmax([G.stream()], 1, Q.data_ptr(), Kt.data_ptr(), P.data_ptr(), Batch, h, CM,
+                                                       w, K, alpha)
+        ref = torch.softmax((Q.double() @ Kt.double().transpose(1, 2)) * alpha, dim=-1)
+        err = (P[:, :, :w].double() - ref).norm() / ref.norm()
+        worst = torch.maximum(worst, torch.nan_to_num(err, nan=1.0))
+        bad += (P[:, :, w:] != 0).sum() + (~torch.isfinite(P)).sum()
+        bad += ((P[:, :, :w].double().sum(-1) - 1.0).abs() > 2e-6).sum()
+    assert int(bad.item()) == 0
+    assert float(worst.item()) <= 1e-6, float(worst.item())
+    out.host((Batch * 105 * 1024,))   # canaries
+    G.check_status(pkg)
+
+
+@pytest.mark.gpu
 def test_fused_scores_softmax_against_the_reference_kernels(pkg, O, cuda):
     """The reference's own kernels on this GPU: linear2D, row_max, row_softmax, div2D_field on this library's
     unscaled product (the product itself is compared with the reference elsewhere)."""
